@@ -1,0 +1,122 @@
+/*
+ * tl_b200.h — C ABI of libtl_b200.so, the sm_100a kernel library behind the
+ * `T.ppl_*` operator path.
+ *
+ * The reference binds ONE generated symbol per compiled program,
+ *     extern "C" int tilelang_tpu_run(void** args)
+ * (src/tl_templates/tpu/main_template.cpp:39, bound with ctypes in
+ * tilelang/jit/adapter/cython/adapter.py:213-216), with all sizes baked in at
+ * code-generation time.  This library is pre-built instead, so every entry
+ * point takes the sizes explicitly.  Conventions shared by all entry points:
+ *
+ *   - every pointer is a DEVICE pointer on the current CUDA device; the library
+ *     never allocates, frees or copies user tensors and never synchronises;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - the return value is 0 on success or a negative TL_B200_E* code; the
+ *     message for the calling thread is available from tl_b200_last_error()
+ *     (same shape as the `init()/call()/get_last_error()` convention of the
+ *     reference's CUDA host wrappers, tilelang/jit/adapter/wrapper.py:22-42);
+ *   - all tensors are dense row-major unless a stride argument says otherwise.
+ */
+#ifndef TL_B200_H_
+#define TL_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TL_B200_VERSION 100
+
+/* error codes */
+#define TL_B200_OK 0
+#define TL_B200_EINVAL (-1)   /* bad argument (null pointer, size, alignment, dtype) */
+#define TL_B200_ECUDA (-2)    /* a CUDA runtime/driver call failed */
+#define TL_B200_EUNSUP (-3)   /* valid request this build has no kernel for */
+#define TL_B200_EDEVICE (-4)  /* a kernel reported an error through its status word */
+
+/* element types (values are part of the ABI) */
+#define TL_F32 0
+#define TL_F16 1
+#define TL_BF16 2
+#define TL_E4M3 3
+#define TL_I32 4
+#define TL_U32 5
+
+/* ---- library management ---------------------------------------------------
+ * Replaces init()/post() of the generated host (main_template.cpp:14-37).    */
+int tl_b200_init(int device);
+int tl_b200_version(void);
+const char* tl_b200_last_error(void);
+/* Number of kernels this library has launched in the calling process. */
+int64_t tl_b200_launch_count(void);
+
+/* ---- RMSNorm program ------------------------------------------------------
+ * y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) (* weight[:] if weight != NULL),
+ * fp32 arithmetic, one rounding to `dtype` at the end.
+ * Replaces the program tpu_demo/rms_norm/rms_norm_bf16.py:9-35 (ppl_copy, ppl_mul,
+ * ppl_reduce_sum, ppl_mul_C, ppl_add_C, ppl_rsqrt chain; eps 1e-12, no weight).  */
+int tl_b200_rmsnorm(const void* x, const void* weight, void* y, int64_t rows, int64_t cols,
+                    float eps, int dtype, void* stream);
+
+/* ---- RoPE program (interleaved pairs) --------------------------------------
+ * out[r,2i]   = x[r,2i]*cos[t,2i]   + (-x[r,2i+1])*sin[t,2i]
+ * out[r,2i+1] = x[r,2i+1]*cos[t,2i+1] + x[r,2i]*sin[t,2i+1],   t = r / rows_per_table_row,
+ * every product and the sum rounded to `dtype` as the reference's tile ops do.
+ * Replaces tpu_demo/tpu_test_rope_bf16.py:5-51 (ppl_mul, ppl_mul_C, ppl_rope_add,
+ * src/target/codegen_ppl.cc:1809-1848).  rows_per_table_row = 1 is the reference's
+ * full-size-table form; = heads broadcasts one table row over the heads of a token. */
+int tl_b200_rope(const void* x, const void* cos_tab, const void* sin_tab, void* out, int64_t rows,
+                 int64_t width, int64_t rows_per_table_row, int dtype, void* stream);
+
+/* ---- SwiGLU program --------------------------------------------------------
+ * out = up * gate / (1 + exp(-gate)), fp32 arithmetic, one rounding at the end.
+ * Replaces tpu_demo/tpu_test_swiglu_bf16.py:5-54.                                 */
+int tl_b200_swiglu(const void* gate, const void* up, void* out, int64_t n_elems, int dtype,
+                   void* stream);
+
+/* ---- row reductions --------------------------------------------------------
+ * y[r] = sum or max over x[r, 0:cols];  op 0 = sum (ppl_reduce_sum,
+ * codegen_ppl.cc:1554-1792), op 1 = max (ppl_reduce_max, :1352-1553).
+ * Accumulation in fp32; output in `dtype`.  Programs: tpu_demo/tpu_test_reduce_sum.py,
+ * tpu_demo/tpu_test_reduce_max.py.                                                 */
+int tl_b200_reduce_rows(const void* x, void* y, int64_t rows, int64_t cols, int op, int dtype,
+                        void* stream);
+
+/* ---- elementwise tile ops --------------------------------------------------
+ * Unary: op 0 = sigmoid (ppl_sigmoid, codegen_ppl.cc:1321-1351), 1 = exp (ppl_exp2,
+ * natural exponential, :1294-1320), 2 = rsqrt (ppl_rsqrt, :1793-1807), 3 = copy/cast
+ * (ppl_copy with differing dtypes, round-to-nearest-even, :1138-1151).              */
+int tl_b200_unary(const void* x, void* y, int64_t n_elems, int op, int in_dtype, int out_dtype,
+                  void* stream);
+/* Binary: out = a (op) b with op 0 add, 1 sub, 2 mul, 3 div (ppl_add/subtract/mul/div,
+ * codegen_ppl.cc:891-913,1280-1287).  b_mode 0: b has the shape of a; 1: b is (rows,1)
+ * and broadcasts across columns (:868-889); 2: b is ignored and `scalar` is used
+ * (ppl_mul_C / ppl_add_C, :917-957).  fp32 arithmetic, rounded to `dtype`.          */
+int tl_b200_binary(const void* a, const void* b, void* out, int64_t rows, int64_t cols, int op,
+                   int b_mode, float scalar, int dtype, void* stream);
+
+/* ---- gather ----------------------------------------------------------------
+ * out[i,:] = param[index[i],:] for i < n_index; index is uint32; rows whose index is
+ * >= param_rows are written as zeros (never read out of bounds).  row_bytes is the
+ * byte length of one row.  Replaces ppl_gather (customize.py:352-356,
+ * codegen_ppl.cc:1849-1877); program tpu_demo/tpu_test_gather_fp32.py.             */
+int tl_b200_gather_rows(const void* param, const uint32_t* index, void* out, int64_t n_index,
+                        int64_t row_bytes, int64_t param_rows, void* stream);
+
+/* ---- top-k -----------------------------------------------------------------
+ * For each of `rows` independent arrays of `length` elements (row stride = length):
+ * the k largest (descending != 0) or smallest values, sorted, with their int32 source
+ * positions; ties are ordered by lower index first.  Results go to the first k entries
+ * of each row of out_vals / out_idx, whose row stride is out_stride elements (the
+ * reference passes length-sized output buffers, tpu_demo/tpu_test_topk_fp32.py:11-13).
+ * dtype: TL_F32, TL_I32 or TL_U32 (codegen_ppl.cc:1898-1903).  Replaces ppl_topk
+ * (customize.py:358-362, codegen_ppl.cc:1878-1907).                                */
+int tl_b200_topk(const void* src, void* out_vals, int32_t* out_idx, int64_t rows, int64_t length,
+                 int k, int descending, int64_t out_stride, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TL_B200_H_ */

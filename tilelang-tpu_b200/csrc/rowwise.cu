@@ -1,0 +1,547 @@
+// HBM-bound programs: RMSNorm, interleaved RoPE, SwiGLU, row reductions and the elementwise
+// tile ops.  All of them make one pass over their inputs with 16-byte accesses; nothing here
+// touches tensor cores.
+#include "common.cuh"
+
+namespace tl {
+
+constexpr int kThreads = 256;
+
+// =================================================================================
+// RMSNorm.  THREADS_PER_ROW threads own one row and keep it in registers between the
+// sum-of-squares pass and the scaling pass, so every element is read once and written once.
+// =================================================================================
+template <typename T, int TPR, int VPT>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, int64_t rows,
+               int nvec, float inv_cols, float eps) {
+  constexpr int VN = Vec16<T>::N;
+  constexpr int ROWS_PER_CTA = kThreads / TPR;
+  __shared__ float partial[kThreads / 32];
+
+  const int lane_in_row = threadIdx.x % TPR;
+  const int row_in_cta = threadIdx.x / TPR;
+  const int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + row_in_cta;
+  const bool live = row < rows;
+
+  Vec16<T> v[VPT];
+  float ss = 0.f;
+  if (live) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x) + row * nvec;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c = lane_in_row + i * TPR;
+      if (c < nvec) v[i].raw = ld_stream16(xr + c);
+    }
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      int c = lane_in_row + i * TPR;
+      if (c < nvec) {
+#pragma unroll
+        for (int j = 0; j < VN; ++j) {
+          float f = to_f32(v[i].e[j]);
+          ss = fmaf(f, f, ss);
+        }
+      }
+    }
+  }
+  ss = warp_sum(ss);
+  if constexpr (TPR > 32) {
+    constexpr int WPR = TPR / 32;  // warps per row
+    const int warp = threadIdx.x / 32;
+    if ((threadIdx.x & 31) == 0) partial[warp] = ss;
+    __syncthreads();
+    ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < WPR; ++k) ss += partial[row_in_cta * WPR + k];
+  }
+  if (!live) return;
+  const float r = rsqrtf(ss * inv_cols + eps);
+  uint4* yr = reinterpret_cast<uint4*>(y) + row * nvec;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    int c = lane_in_row + i * TPR;
+    if (c < nvec) {
+      Vec16<T> o;
+      if (w != nullptr) {
+        Vec16<T> wv;
+        wv.raw = ld_cached16(reinterpret_cast<const uint4*>(w) + c);
+#pragma unroll
+        for (int j = 0; j < VN; ++j) o.e[j] = from_f32<T>(to_f32(v[i].e[j]) * r * to_f32(wv.e[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < VN; ++j) o.e[j] = from_f32<T>(to_f32(v[i].e[j]) * r);
+      }
+      st_stream16(yr + c, o.raw);
+    }
+  }
+}
+
+// Any width, any alignment: one CTA per row, two scalar passes (the second one hits L2).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rmsnorm_generic_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                       int64_t cols, float inv_cols, float eps) {
+  __shared__ float partial[kThreads / 32];
+  const T* xr = x + (int64_t)blockIdx.x * cols;
+  T* yr = y + (int64_t)blockIdx.x * cols;
+  float ss = 0.f;
+  for (int64_t c = threadIdx.x; c < cols; c += kThreads) {
+    float f = to_f32(xr[c]);
+    ss = fmaf(f, f, ss);
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x / 32] = ss;
+  __syncthreads();
+  ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < kThreads / 32; ++k) ss += partial[k];
+  const float r = rsqrtf(ss * inv_cols + eps);
+  for (int64_t c = threadIdx.x; c < cols; c += kThreads) {
+    float f = to_f32(xr[c]) * r;
+    if (w != nullptr) f *= to_f32(w[c]);
+    yr[c] = from_f32<T>(f);
+  }
+}
+
+template <typename T, int TPR, int VPT>
+static int launch_rmsnorm(const void* x, const void* w, void* y, int64_t rows, int nvec, float inv_cols,
+                          float eps, cudaStream_t s) {
+  constexpr int RPC = kThreads / TPR;
+  int64_t grid = (rows + RPC - 1) / RPC;
+  rmsnorm_kernel<T, TPR, VPT><<<(unsigned)grid, kThreads, 0, s>>>(
+      (const T*)x, (const T*)w, (T*)y, rows, nvec, inv_cols, eps);
+  TL_LAUNCH_CHECK("rmsnorm_kernel");
+  return TL_B200_OK;
+}
+
+template <typename T>
+static int rmsnorm_dispatch(const void* x, const void* w, void* y, int64_t rows, int64_t cols, float eps,
+                            cudaStream_t s) {
+  constexpr int VN = Vec16<T>::N;
+  const float inv_cols = 1.0f / (float)cols;
+  const bool vec_ok = cols % VN == 0 && aligned16(x) && aligned16(y) && (w == nullptr || aligned16(w));
+  const int64_t nvec = cols / VN;
+  if (vec_ok && nvec <= 2048 && rows < (1ll << 31)) {
+    const int nv = (int)nvec;
+    if (nv <= 32) return launch_rmsnorm<T, 32, 1>(x, w, y, rows, nv, inv_cols, eps, s);
+    if (nv <= 64) return launch_rmsnorm<T, 32, 2>(x, w, y, rows, nv, inv_cols, eps, s);
+    if (nv <= 128) return launch_rmsnorm<T, 32, 4>(x, w, y, rows, nv, inv_cols, eps, s);
+    if (nv <= 256) return launch_rmsnorm<T, 256, 1>(x, w, y, rows, nv, inv_cols, eps, s);
+    if (nv <= 512) return launch_rmsnorm<T, 256, 2>(x, w, y, rows, nv, inv_cols, eps, s);
+    if (nv <= 1024) return launch_rmsnorm<T, 256, 4>(x, w, y, rows, nv, inv_cols, eps, s);
+    return launch_rmsnorm<T, 256, 8>(x, w, y, rows, nv, inv_cols, eps, s);
+  }
+  TL_REQUIRE(rows < (1ll << 31), "rmsnorm: rows %lld too large", (long long)rows);
+  rmsnorm_generic_kernel<T><<<(unsigned)rows, kThreads, 0, s>>>((const T*)x, (const T*)w, (T*)y, cols,
+                                                                inv_cols, eps);
+  TL_LAUNCH_CHECK("rmsnorm_generic_kernel");
+  return TL_B200_OK;
+}
+
+// =================================================================================
+// RoPE on interleaved pairs.  One 16-byte vector holds whole (even, odd) pairs, so a thread
+// needs no neighbour's data.  Intermediate products are rounded to T exactly where the
+// reference's tile ops round them (ppl_mul, ppl_mul_C, ppl_rope_add all work in tile dtype).
+// =================================================================================
+template <typename T> __device__ __forceinline__ float rnd(float v) { return to_f32(from_f32<T>(v)); }
+
+template <typename T, int UNROLL>
+__global__ void __launch_bounds__(kThreads)
+rope_kernel(const T* __restrict__ x, const T* __restrict__ cos_tab, const T* __restrict__ sin_tab,
+            T* __restrict__ out, int64_t total_vec, int vec_per_row, int64_t rows_per_table_row) {
+  constexpr int VN = Vec16<T>::N;
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  const uint4* xv = reinterpret_cast<const uint4*>(x);
+  const uint4* cv = reinterpret_cast<const uint4*>(cos_tab);
+  const uint4* sv = reinterpret_cast<const uint4*>(sin_tab);
+  uint4* ov = reinterpret_cast<uint4*>(out);
+  for (int64_t base = (int64_t)blockIdx.x * kThreads + threadIdx.x; base < total_vec;
+       base += stride * UNROLL) {
+    Vec16<T> xa[UNROLL], ca[UNROLL], sa[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      int64_t i = base + u * stride;
+      if (i < total_vec) {
+        int64_t row = i / vec_per_row;
+        int col = (int)(i - row * vec_per_row);
+        int64_t t = (row / rows_per_table_row) * vec_per_row + col;
+        xa[u].raw = ld_stream16(xv + i);
+        ca[u].raw = ld_cached16(cv + t);
+        sa[u].raw = ld_cached16(sv + t);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      int64_t i = base + u * stride;
+      if (i < total_vec) {
+        Vec16<T> o;
+#pragma unroll
+        for (int p = 0; p < VN; p += 2) {
+          float xe = to_f32(xa[u].e[p]), xo = to_f32(xa[u].e[p + 1]);
+          float ce = to_f32(ca[u].e[p]), co = to_f32(ca[u].e[p + 1]);
+          float se = to_f32(sa[u].e[p]), so = to_f32(sa[u].e[p + 1]);
+          // out[2i]   = (x*cos)[2i]   + (-x*sin)[2i+1]
+          // out[2i+1] = (x*cos)[2i+1] + ( x*sin)[2i]
+          float ev = rnd<T>(rnd<T>(xe * ce) + rnd<T>((-xo) * so));
+          float od = rnd<T>(rnd<T>(xo * co) + rnd<T>(xe * se));
+          o.e[p] = from_f32<T>(ev);
+          o.e[p + 1] = from_f32<T>(od);
+        }
+        st_stream16(ov + i, o.raw);
+      }
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rope_generic_kernel(const T* __restrict__ x, const T* __restrict__ cos_tab, const T* __restrict__ sin_tab,
+                    T* __restrict__ out, int64_t total_pairs, int64_t half_width,
+                    int64_t rows_per_table_row) {
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < total_pairs; i += stride) {
+    int64_t row = i / half_width;
+    int64_t p = i - row * half_width;
+    int64_t xi = row * half_width * 2 + 2 * p;
+    int64_t ti = (row / rows_per_table_row) * half_width * 2 + 2 * p;
+    float xe = to_f32(x[xi]), xo = to_f32(x[xi + 1]);
+    float ce = to_f32(cos_tab[ti]), co = to_f32(cos_tab[ti + 1]);
+    float se = to_f32(sin_tab[ti]), so = to_f32(sin_tab[ti + 1]);
+    out[xi] = from_f32<T>(rnd<T>(xe * ce) + rnd<T>((-xo) * so));
+    out[xi + 1] = from_f32<T>(rnd<T>(xo * co) + rnd<T>(xe * se));
+  }
+}
+
+static unsigned elementwise_grid(int64_t work_items, int per_cta) {
+  int64_t need = (work_items + per_cta - 1) / per_cta;
+  int64_t cap = (int64_t)sm_count() * 8;  // 8 CTAs of 256 threads fill an SM
+  if (need < 1) need = 1;
+  return (unsigned)(need < cap ? need : cap);
+}
+
+template <typename T>
+static int rope_dispatch(const void* x, const void* c, const void* sn, void* out, int64_t rows, int64_t width,
+                         int64_t rptr, cudaStream_t s) {
+  constexpr int VN = Vec16<T>::N;
+  const bool vec_ok = width % VN == 0 && aligned16(x) && aligned16(c) && aligned16(sn) && aligned16(out) &&
+                      width / VN < (1ll << 31);
+  if (vec_ok) {
+    constexpr int UNROLL = 4;
+    int64_t total_vec = rows * (width / VN);
+    unsigned grid = elementwise_grid(total_vec, kThreads * UNROLL);
+    rope_kernel<T, UNROLL><<<grid, kThreads, 0, s>>>((const T*)x, (const T*)c, (const T*)sn, (T*)out,
+                                                     total_vec, (int)(width / VN), rptr);
+    TL_LAUNCH_CHECK("rope_kernel");
+  } else {
+    int64_t total_pairs = rows * (width / 2);
+    unsigned grid = elementwise_grid(total_pairs, kThreads);
+    rope_generic_kernel<T><<<grid, kThreads, 0, s>>>((const T*)x, (const T*)c, (const T*)sn, (T*)out,
+                                                     total_pairs, width / 2, rptr);
+    TL_LAUNCH_CHECK("rope_generic_kernel");
+  }
+  return TL_B200_OK;
+}
+
+// =================================================================================
+// SwiGLU: out = up * gate / (1 + exp(-gate)).
+// =================================================================================
+template <typename T> __device__ __forceinline__ float silu_mul(float g, float u) {
+  if constexpr (sizeof(T) == 4) {
+    return u * (g / (1.0f + expf(-g)));
+  } else {
+    // 16-bit outputs keep 8-11 significant bits; the fast exponential and division
+    // are far inside that.
+    return u * __fdividef(g, 1.0f + __expf(-g));
+  }
+}
+
+template <typename T, int UNROLL>
+__global__ void __launch_bounds__(kThreads)
+swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out, int64_t nvec,
+              int64_t n_elems) {
+  constexpr int VN = Vec16<T>::N;
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  const int64_t tid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+  const uint4* gv = reinterpret_cast<const uint4*>(gate);
+  const uint4* uv = reinterpret_cast<const uint4*>(up);
+  uint4* ov = reinterpret_cast<uint4*>(out);
+  for (int64_t base = tid; base < nvec; base += stride * UNROLL) {
+    Vec16<T> g[UNROLL], u[UNROLL];
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+      int64_t i = base + k * stride;
+      if (i < nvec) {
+        g[k].raw = ld_stream16(gv + i);
+        u[k].raw = ld_stream16(uv + i);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < UNROLL; ++k) {
+      int64_t i = base + k * stride;
+      if (i < nvec) {
+        Vec16<T> o;
+#pragma unroll
+        for (int j = 0; j < VN; ++j) o.e[j] = from_f32<T>(silu_mul<T>(to_f32(g[k].e[j]), to_f32(u[k].e[j])));
+        st_stream16(ov + i, o.raw);
+      }
+    }
+  }
+  // ragged tail (fewer than one vector)
+  for (int64_t i = nvec * VN + tid; i < n_elems; i += stride)
+    out[i] = from_f32<T>(silu_mul<T>(to_f32(gate[i]), to_f32(up[i])));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+swiglu_scalar_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out, int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride)
+    out[i] = from_f32<T>(silu_mul<T>(to_f32(gate[i]), to_f32(up[i])));
+}
+
+template <typename T>
+static int swiglu_dispatch(const void* g, const void* u, void* o, int64_t n, cudaStream_t s) {
+  constexpr int VN = Vec16<T>::N;
+  if (aligned16(g) && aligned16(u) && aligned16(o)) {
+    constexpr int UNROLL = 4;
+    int64_t nvec = n / VN;
+    unsigned grid = elementwise_grid(nvec, kThreads * UNROLL);
+    swiglu_kernel<T, UNROLL><<<grid, kThreads, 0, s>>>((const T*)g, (const T*)u, (T*)o, nvec, n);
+    TL_LAUNCH_CHECK("swiglu_kernel");
+  } else {
+    unsigned grid = elementwise_grid(n, kThreads);
+    swiglu_scalar_kernel<T><<<grid, kThreads, 0, s>>>((const T*)g, (const T*)u, (T*)o, n);
+    TL_LAUNCH_CHECK("swiglu_scalar_kernel");
+  }
+  return TL_B200_OK;
+}
+
+// =================================================================================
+// Row reductions: sum or max over the columns of each row, fp32 accumulation.
+// TPR threads (a warp or the whole CTA) walk one row.
+// =================================================================================
+template <typename T, int TPR, bool IS_MAX, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int64_t cols) {
+  constexpr int VN = Vec16<T>::N;
+  constexpr int ROWS_PER_CTA = kThreads / TPR;
+  __shared__ float partial[kThreads / 32];
+  const int lane_in_row = threadIdx.x % TPR;
+  const int row_in_cta = threadIdx.x / TPR;
+  const int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + row_in_cta;
+  const bool live = row < rows;
+  float acc = IS_MAX ? -INFINITY : 0.f;
+  if (live) {
+    const T* xr = x + row * cols;
+    int64_t done = 0;
+    if constexpr (VEC) {
+      const int64_t nvec = cols / VN;
+      const uint4* xv = reinterpret_cast<const uint4*>(xr);
+      for (int64_t c = lane_in_row; c < nvec; c += TPR) {
+        Vec16<T> v;
+        v.raw = ld_stream16(xv + c);
+#pragma unroll
+        for (int j = 0; j < VN; ++j) {
+          float f = to_f32(v.e[j]);
+          acc = IS_MAX ? fmaxf(acc, f) : acc + f;
+        }
+      }
+      done = nvec * VN;
+    }
+    for (int64_t c = done + lane_in_row; c < cols; c += TPR) {
+      float f = to_f32(xr[c]);
+      acc = IS_MAX ? fmaxf(acc, f) : acc + f;
+    }
+  }
+  acc = IS_MAX ? warp_max(acc) : warp_sum(acc);
+  if constexpr (TPR > 32) {
+    constexpr int WPR = TPR / 32;
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x / 32] = acc;
+    __syncthreads();
+    acc = IS_MAX ? -INFINITY : 0.f;
+#pragma unroll
+    for (int k = 0; k < WPR; ++k) {
+      float p = partial[row_in_cta * WPR + k];
+      acc = IS_MAX ? fmaxf(acc, p) : acc + p;
+    }
+  }
+  if (live && lane_in_row == 0) y[row] = from_f32<T>(acc);
+}
+
+template <typename T, bool IS_MAX>
+static int reduce_dispatch(const void* x, void* y, int64_t rows, int64_t cols, cudaStream_t s) {
+  constexpr int VN = Vec16<T>::N;
+  const bool vec = aligned16(x) && cols % VN == 0;
+  const bool wide = cols * (int64_t)sizeof(T) > 4096;  // beyond 4 KB a whole CTA walks the row
+  const int rpc = wide ? 1 : kThreads / 32;
+  int64_t grid = (rows + rpc - 1) / rpc;
+  TL_REQUIRE(grid < (1ll << 31), "reduce_rows: too many rows (%lld)", (long long)rows);
+#define TL_RED(TPR, V)                                                                        \
+  reduce_rows_kernel<T, TPR, IS_MAX, V><<<(unsigned)grid, kThreads, 0, s>>>((const T*)x, (T*)y, rows, cols)
+  if (wide) { if (vec) TL_RED(256, true); else TL_RED(256, false); }
+  else      { if (vec) TL_RED(32, true);  else TL_RED(32, false); }
+#undef TL_RED
+  TL_LAUNCH_CHECK("reduce_rows_kernel");
+  return TL_B200_OK;
+}
+
+// =================================================================================
+// Elementwise tile ops (scalar indexing; these back the generic per-op path, not a
+// bandwidth headline).
+// =================================================================================
+template <typename TI, typename TO, int OP>
+__global__ void __launch_bounds__(kThreads)
+unary_kernel(const TI* __restrict__ x, TO* __restrict__ y, int64_t n) {
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+    float f = to_f32(x[i]);
+    float r;
+    if constexpr (OP == 0) r = 1.0f / (1.0f + expf(-f));
+    else if constexpr (OP == 1) r = expf(f);
+    else if constexpr (OP == 2) r = 1.0f / sqrtf(f);
+    else r = f;
+    y[i] = from_f32<TO>(r);
+  }
+}
+
+template <typename T, int OP, int BMODE>
+__global__ void __launch_bounds__(kThreads)
+binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out, int64_t n, int64_t cols,
+              float scalar) {
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+    float av = to_f32(a[i]);
+    float bv;
+    if constexpr (BMODE == 0) bv = to_f32(b[i]);
+    else if constexpr (BMODE == 1) bv = to_f32(b[i / cols]);
+    else bv = to_f32(from_f32<T>(scalar));  // scalar is first cast to the tile dtype
+    float r;
+    if constexpr (OP == 0) r = av + bv;
+    else if constexpr (OP == 1) r = av - bv;
+    else if constexpr (OP == 2) r = av * bv;
+    else r = av / bv;
+    out[i] = from_f32<T>(r);
+  }
+}
+
+template <typename TI, typename TO>
+static int unary_dispatch(const void* x, void* y, int64_t n, int op, cudaStream_t s) {
+  unsigned grid = elementwise_grid(n, kThreads * 4);
+  switch (op) {
+    case 0: unary_kernel<TI, TO, 0><<<grid, kThreads, 0, s>>>((const TI*)x, (TO*)y, n); break;
+    case 1: unary_kernel<TI, TO, 1><<<grid, kThreads, 0, s>>>((const TI*)x, (TO*)y, n); break;
+    case 2: unary_kernel<TI, TO, 2><<<grid, kThreads, 0, s>>>((const TI*)x, (TO*)y, n); break;
+    case 3: unary_kernel<TI, TO, 3><<<grid, kThreads, 0, s>>>((const TI*)x, (TO*)y, n); break;
+    default: return fail(TL_B200_EINVAL, "unary: unknown op %d", op);
+  }
+  TL_LAUNCH_CHECK("unary_kernel");
+  return TL_B200_OK;
+}
+
+template <typename TI>
+static int unary_out(const void* x, void* y, int64_t n, int op, int out_dtype, cudaStream_t s) {
+  switch (out_dtype) {
+    case TL_F32: return unary_dispatch<TI, float>(x, y, n, op, s);
+    case TL_F16: return unary_dispatch<TI, __half>(x, y, n, op, s);
+    case TL_BF16: return unary_dispatch<TI, __nv_bfloat16>(x, y, n, op, s);
+    default: return fail(TL_B200_EINVAL, "unary: unsupported output dtype %d", out_dtype);
+  }
+}
+
+template <typename T, int OP>
+static int binary_mode(const void* a, const void* b, void* o, int64_t n, int64_t cols, int b_mode, float sc,
+                       cudaStream_t s) {
+  unsigned grid = elementwise_grid(n, kThreads * 4);
+  switch (b_mode) {
+    case 0: binary_kernel<T, OP, 0><<<grid, kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)o, n, cols, sc); break;
+    case 1: binary_kernel<T, OP, 1><<<grid, kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)o, n, cols, sc); break;
+    case 2: binary_kernel<T, OP, 2><<<grid, kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)o, n, cols, sc); break;
+    default: return fail(TL_B200_EINVAL, "binary: unknown b_mode %d", b_mode);
+  }
+  TL_LAUNCH_CHECK("binary_kernel");
+  return TL_B200_OK;
+}
+
+template <typename T>
+static int binary_op(const void* a, const void* b, void* o, int64_t n, int64_t cols, int op, int b_mode,
+                     float sc, cudaStream_t s) {
+  switch (op) {
+    case 0: return binary_mode<T, 0>(a, b, o, n, cols, b_mode, sc, s);
+    case 1: return binary_mode<T, 1>(a, b, o, n, cols, b_mode, sc, s);
+    case 2: return binary_mode<T, 2>(a, b, o, n, cols, b_mode, sc, s);
+    case 3: return binary_mode<T, 3>(a, b, o, n, cols, b_mode, sc, s);
+    default: return fail(TL_B200_EINVAL, "binary: unknown op %d", op);
+  }
+}
+
+}  // namespace tl
+
+using namespace tl;
+
+#define TL_FLOAT_DISPATCH(dtype, CALL)                                         \
+  switch (dtype) {                                                             \
+    case TL_F32: { using T = float; return CALL; }                             \
+    case TL_F16: { using T = __half; return CALL; }                            \
+    case TL_BF16: { using T = __nv_bfloat16; return CALL; }                    \
+    default: return fail(TL_B200_EINVAL, "%s: unsupported dtype %d", __func__, dtype); \
+  }
+
+extern "C" {
+
+int tl_b200_rmsnorm(const void* x, const void* weight, void* y, int64_t rows, int64_t cols, float eps,
+                    int dtype, void* stream) {
+  TL_REQUIRE(rows >= 0 && cols >= 0, "rmsnorm: negative size");
+  if (rows == 0 || cols == 0) return TL_B200_OK;
+  TL_REQUIRE(x && y, "rmsnorm: null tensor pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  TL_FLOAT_DISPATCH(dtype, rmsnorm_dispatch<T>(x, weight, y, rows, cols, eps, s));
+}
+
+int tl_b200_rope(const void* x, const void* cos_tab, const void* sin_tab, void* out, int64_t rows,
+                 int64_t width, int64_t rows_per_table_row, int dtype, void* stream) {
+  TL_REQUIRE(rows >= 0 && width >= 0, "rope: negative size");
+  TL_REQUIRE(width % 2 == 0, "rope: width %lld must be even", (long long)width);
+  TL_REQUIRE(rows_per_table_row >= 1, "rope: rows_per_table_row must be >= 1");
+  if (rows == 0 || width == 0) return TL_B200_OK;
+  TL_REQUIRE(x && cos_tab && sin_tab && out, "rope: null tensor pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  TL_FLOAT_DISPATCH(dtype, rope_dispatch<T>(x, cos_tab, sin_tab, out, rows, width, rows_per_table_row, s));
+}
+
+int tl_b200_swiglu(const void* gate, const void* up, void* out, int64_t n_elems, int dtype, void* stream) {
+  TL_REQUIRE(n_elems >= 0, "swiglu: negative size");
+  if (n_elems == 0) return TL_B200_OK;
+  TL_REQUIRE(gate && up && out, "swiglu: null tensor pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  TL_FLOAT_DISPATCH(dtype, swiglu_dispatch<T>(gate, up, out, n_elems, s));
+}
+
+int tl_b200_reduce_rows(const void* x, void* y, int64_t rows, int64_t cols, int op, int dtype, void* stream) {
+  TL_REQUIRE(rows >= 0 && cols >= 0, "reduce_rows: negative size");
+  TL_REQUIRE(op == 0 || op == 1, "reduce_rows: op must be 0 (sum) or 1 (max)");
+  if (rows == 0) return TL_B200_OK;
+  TL_REQUIRE(x && y, "reduce_rows: null tensor pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (op == 0) { TL_FLOAT_DISPATCH(dtype, (reduce_dispatch<T, false>(x, y, rows, cols, s))); }
+  TL_FLOAT_DISPATCH(dtype, (reduce_dispatch<T, true>(x, y, rows, cols, s)));
+}
+
+int tl_b200_unary(const void* x, void* y, int64_t n_elems, int op, int in_dtype, int out_dtype, void* stream) {
+  TL_REQUIRE(n_elems >= 0, "unary: negative size");
+  if (n_elems == 0) return TL_B200_OK;
+  TL_REQUIRE(x && y, "unary: null tensor pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  TL_FLOAT_DISPATCH(in_dtype, unary_out<T>(x, y, n_elems, op, out_dtype, s));
+}
+
+int tl_b200_binary(const void* a, const void* b, void* out, int64_t rows, int64_t cols, int op, int b_mode,
+                   float scalar, int dtype, void* stream) {
+  TL_REQUIRE(rows >= 0 && cols >= 0, "binary: negative size");
+  if (rows == 0 || cols == 0) return TL_B200_OK;
+  TL_REQUIRE(a && out && (b || b_mode == 2), "binary: null tensor pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  TL_FLOAT_DISPATCH(dtype, binary_op<T>(a, b, out, rows * cols, cols, op, b_mode, scalar, s));
+}
+
+}  // extern "C"

@@ -1,0 +1,179 @@
+"""Operator-level entry points over the C ABI: CUDA tensors in, outputs written in place.
+
+Each function corresponds to one reference program (the `tpu_demo` kernels built from
+`T.ppl_*` intrinsics); the JIT front end binds matched programs to these.  Tensors must live on
+the current CUDA device; torch is used only for device memory and the current stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _native as N
+
+_DTYPES = {
+    torch.float32: N.TL_F32,
+    torch.float16: N.TL_F16,
+    torch.bfloat16: N.TL_BF16,
+    torch.int32: N.TL_I32,
+    torch.uint32: N.TL_U32,
+}
+if hasattr(torch, "float8_e4m3fn"):
+    _DTYPES[torch.float8_e4m3fn] = N.TL_E4M3
+
+_initialised_devices: set[int] = set()
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPES[dt]
+    except KeyError:
+        raise ValueError(f"dtype {dt} is not supported by the b200 kernel library") from None
+
+
+def _prepare(*tensors: torch.Tensor) -> int:
+    """Common argument checks; returns the raw handle of the current stream."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise ValueError("b200 ops take CUDA tensors (there is no CPU path)")
+        if not t.is_contiguous():
+            raise ValueError("b200 ops take contiguous tensors")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise ValueError(f"tensors on different devices: {dev} and {t.device}")
+    index = dev.index if dev is not None and dev.index is not None else torch.cuda.current_device()
+    if index != torch.cuda.current_device():
+        raise ValueError(f"tensors are on cuda:{index} but the current device is "
+                         f"cuda:{torch.cuda.current_device()}")
+    if index not in _initialised_devices:
+        N.check(N.load().tl_b200_init(index), "tl_b200_init")
+        _initialised_devices.add(index)
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def launch_count() -> int:
+    return int(N.load().tl_b200_launch_count())
+
+
+def rmsnorm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor | None = None, eps: float = 1e-12) -> int:
+    """y = x * rsqrt(mean(x^2, -1) + eps) [* weight]; x, y are (rows, cols)."""
+    if x.dim() != 2 or x.shape != y.shape or x.dtype != y.dtype:
+        raise ValueError("rmsnorm: x and y must be 2-D with equal shape and dtype")
+    if weight is not None and (weight.numel() != x.shape[1] or weight.dtype != x.dtype):
+        raise ValueError("rmsnorm: weight must have cols elements of x's dtype")
+    s = _prepare(x, y, weight)
+    return N.check(N.load().tl_b200_rmsnorm(_ptr(x), _ptr(weight), _ptr(y), x.shape[0], x.shape[1],
+                                           float(eps), dtype_code(x.dtype), s), "tl_b200_rmsnorm")
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: torch.Tensor) -> int:
+    """Interleaved-pair rotation.  x/out: (..., W); cos/sin: (T, W) with x.numel()/W a multiple
+    of T (each table row serves `rows/T` consecutive rows of x, e.g. the heads of a token)."""
+    width = x.shape[-1]
+    rows = x.numel() // max(width, 1)
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise ValueError("rope: out must match x")
+    if cos.shape != sin.shape or cos.dim() != 2 or cos.shape[1] != width or cos.dtype != x.dtype \
+            or sin.dtype != x.dtype:
+        raise ValueError("rope: cos/sin must be (T, W) tables of x's dtype")
+    t_rows = cos.shape[0]
+    if t_rows == 0 or rows % t_rows != 0:
+        raise ValueError(f"rope: {rows} rows cannot be served by a {t_rows}-row table")
+    s = _prepare(x, cos, sin, out)
+    return N.check(N.load().tl_b200_rope(_ptr(x), _ptr(cos), _ptr(sin), _ptr(out), rows, width,
+                                        rows // t_rows, dtype_code(x.dtype), s), "tl_b200_rope")
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor, out: torch.Tensor) -> int:
+    """out = up * silu(gate)."""
+    if gate.shape != up.shape or gate.shape != out.shape or not (gate.dtype == up.dtype == out.dtype):
+        raise ValueError("swiglu: gate, up and out must have equal shape and dtype")
+    s = _prepare(gate, up, out)
+    return N.check(N.load().tl_b200_swiglu(_ptr(gate), _ptr(up), _ptr(out), gate.numel(),
+                                          dtype_code(gate.dtype), s), "tl_b200_swiglu")
+
+
+def reduce_rows(x: torch.Tensor, y: torch.Tensor, op: str) -> int:
+    """y[r, 0] = sum|max over x[r, :]."""
+    if x.dim() != 2 or y.numel() != x.shape[0] or y.dtype != x.dtype:
+        raise ValueError("reduce_rows: x must be (rows, cols) and y hold rows elements of x's dtype")
+    code = {"sum": 0, "max": 1}[op]
+    s = _prepare(x, y)
+    return N.check(N.load().tl_b200_reduce_rows(_ptr(x), _ptr(y), x.shape[0], x.shape[1], code,
+                                               dtype_code(x.dtype), s), "tl_b200_reduce_rows")
+
+
+_UNARY = {"sigmoid": 0, "exp": 1, "rsqrt": 2, "copy": 3}
+_BINARY = {"add": 0, "sub": 1, "mul": 2, "div": 3}
+
+
+def unary(x: torch.Tensor, y: torch.Tensor, op: str) -> int:
+    if x.numel() != y.numel():
+        raise ValueError("unary: size mismatch")
+    s = _prepare(x, y)
+    return N.check(N.load().tl_b200_unary(_ptr(x), _ptr(y), x.numel(), _UNARY[op], dtype_code(x.dtype),
+                                         dtype_code(y.dtype), s), "tl_b200_unary")
+
+
+def binary(a: torch.Tensor, b, out: torch.Tensor, op: str) -> int:
+    """out = a (op) b; b is a tensor shaped like a, a (rows, 1) column, or a Python scalar."""
+    if a.dim() != 2 or out.shape != a.shape or out.dtype != a.dtype:
+        raise ValueError("binary: a and out must be 2-D with equal shape and dtype")
+    rows, cols = a.shape
+    scalar = 0.0
+    if isinstance(b, torch.Tensor):
+        if b.dtype != a.dtype:
+            raise ValueError("binary: dtype mismatch")
+        if b.shape == a.shape:
+            mode = 0
+        elif b.numel() == rows:
+            mode = 1
+        else:
+            raise ValueError("binary: b must match a or be a (rows, 1) column")
+        s = _prepare(a, b, out)
+        bp = _ptr(b)
+    else:
+        mode, scalar, bp = 2, float(b), None
+        s = _prepare(a, out)
+    return N.check(N.load().tl_b200_binary(_ptr(a), bp, _ptr(out), rows, cols, _BINARY[op], mode, scalar,
+                                          dtype_code(a.dtype), s), "tl_b200_binary")
+
+
+def gather_rows(param: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> int:
+    """out[i, :] = param[index[i], :]; index holds uint32 (or non-negative int32) row ids."""
+    if param.dim() != 2 or out.dim() != 2 or out.shape[1] != param.shape[1] or out.dtype != param.dtype:
+        raise ValueError("gather_rows: param (R, H) and out (n, H) must share H and dtype")
+    if index.dtype not in (torch.uint32, torch.int32) or index.numel() != out.shape[0]:
+        raise ValueError("gather_rows: index must hold out.shape[0] uint32/int32 entries")
+    s = _prepare(param, index, out)
+    row_bytes = param.shape[1] * param.element_size()
+    return N.check(N.load().tl_b200_gather_rows(_ptr(param), _ptr(index), _ptr(out), out.shape[0], row_bytes,
+                                               param.shape[0], s), "tl_b200_gather_rows")
+
+
+def topk(src: torch.Tensor, out_vals: torch.Tensor, out_idx: torch.Tensor, k: int, descending: bool = True) -> int:
+    """Sorted top-k of each row of src ((length,) or (rows, length)); the first k entries of each
+    row of out_vals / out_idx (int32) are written."""
+    if src.dim() not in (1, 2):
+        raise ValueError("topk: src must be 1-D or 2-D")
+    rows = 1 if src.dim() == 1 else src.shape[0]
+    length = src.shape[-1]
+    if src.dtype not in (torch.float32, torch.int32, torch.uint32):
+        raise ValueError("topk: src must be float32, int32 or uint32")
+    if out_vals.dtype != src.dtype or out_idx.dtype != torch.int32:
+        raise ValueError("topk: out_vals must have src's dtype and out_idx must be int32")
+    out_stride = out_vals.shape[-1]
+    if out_idx.shape[-1] != out_stride or out_vals.numel() != rows * out_stride \
+            or out_idx.numel() != rows * out_stride:
+        raise ValueError("topk: out_vals / out_idx must be (rows, stride) with equal stride")
+    s = _prepare(src, out_vals, out_idx)
+    return N.check(N.load().tl_b200_topk(_ptr(src), _ptr(out_vals), _ptr(out_idx), rows, length, int(k),
+                                        1 if descending else 0, out_stride, dtype_code(src.dtype), s),
+                   "tl_b200_topk")
