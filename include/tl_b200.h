@@ -51,6 +51,11 @@ int tl_b200_version(void);
 const char* tl_b200_last_error(void);
 /* Number of kernels this library has launched in the calling process. */
 int64_t tl_b200_launch_count(void);
+/* Kernels that wait on barriers bound every wait; one that gives up writes a non-zero code to
+ * a host-visible status word and exits cleanly.  Returns that code (0 = none) and clears it.
+ * Meaningful after the stream has been synchronised.  (The generated TPU host reports launch
+ * failures through its return value, main_template.cpp:64-67.)                               */
+int tl_b200_device_status(void);
 
 /* ---- RMSNorm program ------------------------------------------------------
  * y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) (* weight[:] if weight != NULL),
@@ -115,6 +120,17 @@ int tl_b200_gather_rows(const void* param, const uint32_t* index, void* out, int
  * (customize.py:358-362, codegen_ppl.cc:1878-1907).                                */
 int tl_b200_topk(const void* src, void* out_vals, int32_t* out_idx, int64_t rows, int64_t length,
                  int k, int descending, int64_t out_stride, int dtype, void* stream);
+
+/* ---- dense GEMM -------------------------------------------------------------
+ * C[m,n] = A[m,k] * B with fp32 accumulation, rounded once to out_dtype.  A is row-major
+ * [m,k].  trans_b == 0: B is row-major [k,n] (the matmul program,
+ * tpu_demo/matmul/tpu_test_matmul_fp16.py:9-30); trans_b != 0: B is row-major [n,k]
+ * (`transpose_B=True` of ppl_gemm, customize.py:101-133, codegen_ppl.cc:1244-1279).
+ * in_dtype TL_F16 / TL_BF16 run on tcgen05 tensor cores when A, B are 16-byte aligned,
+ * k % 8 == 0 and (trans_b or n % 8 == 0); other shapes and TL_F32 use an FMA kernel.
+ * out_dtype is in_dtype or TL_F32.                                                   */
+int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
+                 int in_dtype, int out_dtype, void* stream);
 
 #ifdef __cplusplus
 }

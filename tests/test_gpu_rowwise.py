@@ -84,7 +84,8 @@ def test_rope_golden_bit_exact(cuda_device):
     g = load_golden("rope_fp32")
     out = torch.zeros_like(g["x"], device=cuda_device)
     ops.rope(g["x"].to(cuda_device), g["cos"].to(cuda_device), g["sin"].to(cuda_device), out)
-    assert max_rel(out.cpu(), g["ref"]) < 1e-5
+    # products and sum are separate roundings in the kernel as in the reference function
+    assert torch.equal(out.cpu().view(torch.int32), g["ref"].view(torch.int32))
 
 
 @pytest.mark.parametrize("dtype", [BF, HF, F32])
@@ -96,11 +97,8 @@ def test_rope_shapes(cuda_device, dtype, tokens, heads, width):
     ref = O.rope(x, cos, sin)
     out = torch.zeros_like(x, device=cuda_device)
     ops.rope(x.to(cuda_device), cos.to(cuda_device), sin.to(cuda_device), out)
-    if dtype == F32:
-        assert max_rel(out.cpu(), ref) < 1e-5 or torch.allclose(out.cpu(), ref, atol=1e-6, rtol=1e-5)
-    else:
-        # the kernel rounds where the reference's tile ops round: identical bits
-        assert torch.equal(out.cpu().view(torch.int16), ref.view(torch.int16))
+    # the kernel rounds where the reference's tile ops round: identical bits for every dtype
+    assert torch.equal(out.cpu().view(torch.uint8), ref.view(torch.uint8))
 
 
 def test_rope_llama_config(cuda_device):

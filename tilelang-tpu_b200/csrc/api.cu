@@ -1,5 +1,6 @@
 // Library management entry points and the host-side error plumbing.
 #include "common.cuh"
+#include "sm100.cuh"
 
 #include <mutex>
 
@@ -34,6 +35,75 @@ int sm_count() {
   return g_sm_count;
 }
 
+// ---- tensor maps -------------------------------------------------------------------------------
+// cuTensorMapEncodeTiled is fetched through the runtime's driver entry point query, so the
+// library carries no link-time dependency on libcuda (it must load on machines without a GPU).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+static std::once_flag g_encode_once;
+
+int make_tensor_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const void* base,
+                    const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                    CUtensorMapSwizzle swizzle) {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode = (EncodeTiledFn)fn;
+  });
+  if (!g_encode) return fail(TL_B200_ECUDA, "cuTensorMapEncodeTiled is not available from this driver");
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0)
+    return fail(TL_B200_EINVAL, "tensor map base address must be 16-byte aligned");
+  cuuint64_t gdims[5];
+  cuuint64_t gstrides[4];
+  cuuint32_t gbox[5], estr[5];
+  for (int i = 0; i < rank; ++i) {
+    gdims[i] = dims[i];
+    gbox[i] = box[i];
+    estr[i] = 1;
+    if (i + 1 < rank) {
+      gstrides[i] = strides_bytes[i];
+      if (gstrides[i] % 16 != 0)
+        return fail(TL_B200_EINVAL, "tensor map stride %llu is not a multiple of 16 bytes",
+                    (unsigned long long)gstrides[i]);
+    }
+  }
+  CUresult r = g_encode(map, type, (cuuint32_t)rank, const_cast<void*>(base), gdims, gstrides, gbox, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TL_B200_ECUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return TL_B200_OK;
+}
+
+// ---- device status word ----------------------------------------------------------------------
+// Host-mapped so the host can read it without a device allocation or a copy.
+static int* g_status_host = nullptr;
+static int* g_status_dev = nullptr;
+static std::once_flag g_status_once;
+
+int* device_status_word() {
+  std::call_once(g_status_once, [] {
+    void* h = nullptr;
+    if (cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
+      g_status_host = (int*)h;
+      g_status_host[0] = 0;
+      void* d = nullptr;
+      if (cudaHostGetDevicePointer(&d, h, 0) == cudaSuccess) g_status_dev = (int*)d;
+    }
+  });
+  return g_status_dev;
+}
+
+int take_device_status() {
+  if (!g_status_host) return 0;
+  int v = *(volatile int*)g_status_host;
+  if (v) *(volatile int*)g_status_host = 0;
+  return v;
+}
+
 }  // namespace tl
 
 extern "C" {
@@ -59,5 +129,11 @@ int tl_b200_version(void) { return TL_B200_VERSION; }
 const char* tl_b200_last_error(void) { return tl::error_buffer(); }
 
 int64_t tl_b200_launch_count(void) { return tl::g_launches.load(std::memory_order_relaxed); }
+
+int tl_b200_device_status(void) {
+  int v = tl::take_device_status();
+  if (v) tl::fail(TL_B200_EDEVICE, "a kernel gave up a bounded wait (device status %d)", v);
+  return v;
+}
 
 }  // extern "C"

@@ -94,6 +94,38 @@ __device__ __forceinline__ void st_stream16(void* p, uint4 v) {
                "r"(v.z), "r"(v.w)
                : "memory");
 }
+// 32-byte (256-bit) global accesses, available from sm_100: half the instructions per byte and
+// twice the bytes in flight per thread.  Addresses must be 32-byte aligned.
+template <typename T> struct Vec32 {
+  static constexpr int N = 32 / sizeof(T);
+  union {
+    uint32_t w[8];
+    T e[N];
+  };
+};
+template <typename T> __device__ __forceinline__ Vec32<T> ld_stream32(const void* p) {
+  Vec32<T> v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::evict_first.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]),
+                 "=r"(v.w[6]), "=r"(v.w[7])
+               : "l"(p));
+  return v;
+}
+template <typename T> __device__ __forceinline__ Vec32<T> ld_cached32(const void* p) {
+  Vec32<T> v;
+  asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]),
+                 "=r"(v.w[6]), "=r"(v.w[7])
+               : "l"(p));
+  return v;
+}
+template <typename T> __device__ __forceinline__ void st_stream32(void* p, const Vec32<T>& v) {
+  asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.w[0]),
+               "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]), "r"(v.w[4]), "r"(v.w[5]), "r"(v.w[6]), "r"(v.w[7])
+               : "memory");
+}
+inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
+
 // 16-byte load for data that is re-read by other CTAs (tables, weights): default caching.
 __device__ __forceinline__ uint4 ld_cached16(const void* p) {
   return __ldg(reinterpret_cast<const uint4*>(p));

@@ -7,15 +7,48 @@ namespace tl {
 
 constexpr int kThreads = 256;
 
+// A VB-byte vector of T (VB = 16 or 32) with streaming / cached access.
+template <typename T, int VB> struct VecT;
+template <typename T> struct VecT<T, 16> {
+  static constexpr int N = 16 / sizeof(T);
+  Vec16<T> v;
+  __device__ __forceinline__ T& operator[](int i) { return v.e[i]; }
+  __device__ __forceinline__ void load_stream(const void* p) { v.raw = ld_stream16(p); }
+  __device__ __forceinline__ void load_cached(const void* p) { v.raw = ld_cached16(p); }
+  __device__ __forceinline__ void store_stream(void* p) { st_stream16(p, v.raw); }
+};
+template <typename T> struct VecT<T, 32> {
+  static constexpr int N = 32 / sizeof(T);
+  Vec32<T> v;
+  __device__ __forceinline__ T& operator[](int i) { return v.e[i]; }
+  __device__ __forceinline__ void load_stream(const void* p) { v = ld_stream32<T>(p); }
+  __device__ __forceinline__ void load_cached(const void* p) { v = ld_cached32<T>(p); }
+  __device__ __forceinline__ void store_stream(void* p) { st_stream32<T>(p, v); }
+};
+
+// Grid for a grid-stride kernel: exactly the CTAs that are resident at once (a multiple of the
+// SM count), never more than the work needs.
+template <typename K>
+static unsigned resident_grid(K kernel, int64_t work_items, int per_cta) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm < 1)
+    per_sm = 4;
+  int64_t need = (work_items + per_cta - 1) / per_cta;
+  int64_t cap = (int64_t)sm_count() * per_sm;
+  if (need < 1) need = 1;
+  return (unsigned)(need < cap ? need : cap);
+}
+
 // =================================================================================
 // RMSNorm.  THREADS_PER_ROW threads own one row and keep it in registers between the
 // sum-of-squares pass and the scaling pass, so every element is read once and written once.
 // =================================================================================
-template <typename T, int TPR, int VPT>
+template <typename T, int VB, int TPR, int VPT>
 __global__ void __launch_bounds__(kThreads)
 rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, int64_t rows,
                int nvec, float inv_cols, float eps) {
-  constexpr int VN = Vec16<T>::N;
+  using V = VecT<T, VB>;
+  constexpr int VN = V::N;
   constexpr int ROWS_PER_CTA = kThreads / TPR;
   __shared__ float partial[kThreads / 32];
 
@@ -24,14 +57,14 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
   const int64_t row = (int64_t)blockIdx.x * ROWS_PER_CTA + row_in_cta;
   const bool live = row < rows;
 
-  Vec16<T> v[VPT];
+  V v[VPT];
   float ss = 0.f;
   if (live) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x) + row * nvec;
+    const char* xr = reinterpret_cast<const char*>(x) + row * nvec * VB;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       int c = lane_in_row + i * TPR;
-      if (c < nvec) v[i].raw = ld_stream16(xr + c);
+      if (c < nvec) v[i].load_stream(xr + (int64_t)c * VB);
     }
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -39,7 +72,7 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
       if (c < nvec) {
 #pragma unroll
         for (int j = 0; j < VN; ++j) {
-          float f = to_f32(v[i].e[j]);
+          float f = to_f32(v[i][j]);
           ss = fmaf(f, f, ss);
         }
       }
@@ -57,22 +90,22 @@ rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__
   }
   if (!live) return;
   const float r = rsqrtf(ss * inv_cols + eps);
-  uint4* yr = reinterpret_cast<uint4*>(y) + row * nvec;
+  char* yr = reinterpret_cast<char*>(y) + row * nvec * VB;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     int c = lane_in_row + i * TPR;
     if (c < nvec) {
-      Vec16<T> o;
+      V o;
       if (w != nullptr) {
-        Vec16<T> wv;
-        wv.raw = ld_cached16(reinterpret_cast<const uint4*>(w) + c);
+        V wv;
+        wv.load_cached(reinterpret_cast<const char*>(w) + (int64_t)c * VB);
 #pragma unroll
-        for (int j = 0; j < VN; ++j) o.e[j] = from_f32<T>(to_f32(v[i].e[j]) * r * to_f32(wv.e[j]));
+        for (int j = 0; j < VN; ++j) o[j] = from_f32<T>(to_f32(v[i][j]) * r * to_f32(wv[j]));
       } else {
 #pragma unroll
-        for (int j = 0; j < VN; ++j) o.e[j] = from_f32<T>(to_f32(v[i].e[j]) * r);
+        for (int j = 0; j < VN; ++j) o[j] = from_f32<T>(to_f32(v[i][j]) * r);
       }
-      st_stream16(yr + c, o.raw);
+      o.store_stream(yr + (int64_t)c * VB);
     }
   }
 }
@@ -104,35 +137,43 @@ rmsnorm_generic_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __re
   }
 }
 
-template <typename T, int TPR, int VPT>
+template <typename T, int VB, int TPR, int VPT>
 static int launch_rmsnorm(const void* x, const void* w, void* y, int64_t rows, int nvec, float inv_cols,
                           float eps, cudaStream_t s) {
   constexpr int RPC = kThreads / TPR;
   int64_t grid = (rows + RPC - 1) / RPC;
-  rmsnorm_kernel<T, TPR, VPT><<<(unsigned)grid, kThreads, 0, s>>>(
+  rmsnorm_kernel<T, VB, TPR, VPT><<<(unsigned)grid, kThreads, 0, s>>>(
       (const T*)x, (const T*)w, (T*)y, rows, nvec, inv_cols, eps);
   TL_LAUNCH_CHECK("rmsnorm_kernel");
   return TL_B200_OK;
 }
 
+// Rows up to 256 vectors are owned by one warp (no CTA-wide barrier at all); longer rows by a
+// whole CTA.
+template <typename T, int VB>
+static int rmsnorm_vec(const void* x, const void* w, void* y, int64_t rows, int nv, float inv_cols, float eps,
+                       cudaStream_t s) {
+  if (nv <= 32) return launch_rmsnorm<T, VB, 32, 1>(x, w, y, rows, nv, inv_cols, eps, s);
+  if (nv <= 64) return launch_rmsnorm<T, VB, 32, 2>(x, w, y, rows, nv, inv_cols, eps, s);
+  if (nv <= 128) return launch_rmsnorm<T, VB, 32, 4>(x, w, y, rows, nv, inv_cols, eps, s);
+  if (nv <= 256) return launch_rmsnorm<T, VB, 32, 8>(x, w, y, rows, nv, inv_cols, eps, s);
+  if (nv <= 512) return launch_rmsnorm<T, VB, 256, 2>(x, w, y, rows, nv, inv_cols, eps, s);
+  if (nv <= 1024) return launch_rmsnorm<T, VB, 256, 4>(x, w, y, rows, nv, inv_cols, eps, s);
+  return launch_rmsnorm<T, VB, 256, 8>(x, w, y, rows, nv, inv_cols, eps, s);
+}
+
 template <typename T>
 static int rmsnorm_dispatch(const void* x, const void* w, void* y, int64_t rows, int64_t cols, float eps,
                             cudaStream_t s) {
-  constexpr int VN = Vec16<T>::N;
   const float inv_cols = 1.0f / (float)cols;
-  const bool vec_ok = cols % VN == 0 && aligned16(x) && aligned16(y) && (w == nullptr || aligned16(w));
-  const int64_t nvec = cols / VN;
-  if (vec_ok && nvec <= 2048 && rows < (1ll << 31)) {
-    const int nv = (int)nvec;
-    if (nv <= 32) return launch_rmsnorm<T, 32, 1>(x, w, y, rows, nv, inv_cols, eps, s);
-    if (nv <= 64) return launch_rmsnorm<T, 32, 2>(x, w, y, rows, nv, inv_cols, eps, s);
-    if (nv <= 128) return launch_rmsnorm<T, 32, 4>(x, w, y, rows, nv, inv_cols, eps, s);
-    if (nv <= 256) return launch_rmsnorm<T, 256, 1>(x, w, y, rows, nv, inv_cols, eps, s);
-    if (nv <= 512) return launch_rmsnorm<T, 256, 2>(x, w, y, rows, nv, inv_cols, eps, s);
-    if (nv <= 1024) return launch_rmsnorm<T, 256, 4>(x, w, y, rows, nv, inv_cols, eps, s);
-    return launch_rmsnorm<T, 256, 8>(x, w, y, rows, nv, inv_cols, eps, s);
-  }
+  const int64_t row_bytes = cols * (int64_t)sizeof(T);
   TL_REQUIRE(rows < (1ll << 31), "rmsnorm: rows %lld too large", (long long)rows);
+  if (row_bytes % 32 == 0 && row_bytes / 32 <= 2048 && aligned32(x) && aligned32(y) &&
+      (w == nullptr || aligned32(w)))
+    return rmsnorm_vec<T, 32>(x, w, y, rows, (int)(row_bytes / 32), inv_cols, eps, s);
+  if (row_bytes % 16 == 0 && row_bytes / 16 <= 2048 && aligned16(x) && aligned16(y) &&
+      (w == nullptr || aligned16(w)))
+    return rmsnorm_vec<T, 16>(x, w, y, rows, (int)(row_bytes / 16), inv_cols, eps, s);
   rmsnorm_generic_kernel<T><<<(unsigned)rows, kThreads, 0, s>>>((const T*)x, (const T*)w, (T*)y, cols,
                                                                 inv_cols, eps);
   TL_LAUNCH_CHECK("rmsnorm_generic_kernel");
@@ -146,49 +187,53 @@ static int rmsnorm_dispatch(const void* x, const void* w, void* y, int64_t rows,
 // =================================================================================
 template <typename T> __device__ __forceinline__ float rnd(float v) { return to_f32(from_f32<T>(v)); }
 
-template <typename T, int UNROLL>
+// One output pair.  __fmul_rn / __fadd_rn keep the products and the sum as separate roundings
+// (no FMA contraction), which is what separate tile ops produce; for 16-bit T each of them is
+// additionally rounded to T.
+template <typename T>
+__device__ __forceinline__ void rope_pair(float xe, float xo, float ce, float co, float se, float so, T& oe,
+                                          T& oo) {
+  // out[2i]   = (x*cos)[2i]   + (-x*sin)[2i+1]
+  // out[2i+1] = (x*cos)[2i+1] + ( x*sin)[2i]
+  oe = from_f32<T>(__fadd_rn(rnd<T>(__fmul_rn(xe, ce)), rnd<T>(__fmul_rn(-xo, so))));
+  oo = from_f32<T>(__fadd_rn(rnd<T>(__fmul_rn(xo, co)), rnd<T>(__fmul_rn(xe, se))));
+}
+
+template <typename T, int VB, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
 rope_kernel(const T* __restrict__ x, const T* __restrict__ cos_tab, const T* __restrict__ sin_tab,
-            T* __restrict__ out, int64_t total_vec, int vec_per_row, int64_t rows_per_table_row) {
-  constexpr int VN = Vec16<T>::N;
-  const int64_t stride = (int64_t)gridDim.x * kThreads;
-  const uint4* xv = reinterpret_cast<const uint4*>(x);
-  const uint4* cv = reinterpret_cast<const uint4*>(cos_tab);
-  const uint4* sv = reinterpret_cast<const uint4*>(sin_tab);
-  uint4* ov = reinterpret_cast<uint4*>(out);
-  for (int64_t base = (int64_t)blockIdx.x * kThreads + threadIdx.x; base < total_vec;
-       base += stride * UNROLL) {
-    Vec16<T> xa[UNROLL], ca[UNROLL], sa[UNROLL];
+            T* __restrict__ out, uint32_t total_vec, uint32_t vec_per_row, uint32_t vec_per_table_row) {
+  using V = VecT<T, VB>;
+  constexpr int VN = V::N;
+  const uint32_t stride = gridDim.x * kThreads;
+  const char* xb = reinterpret_cast<const char*>(x);
+  const char* cb = reinterpret_cast<const char*>(cos_tab);
+  const char* sb = reinterpret_cast<const char*>(sin_tab);
+  char* ob = reinterpret_cast<char*>(out);
+  // total_vec < 2^31, so base + u*stride cannot wrap before the bound check
+  for (uint32_t base = blockIdx.x * kThreads + threadIdx.x; base < total_vec; base += stride * UNROLL) {
+    V xa[UNROLL], ca[UNROLL], sa[UNROLL];
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      int64_t i = base + u * stride;
+      uint32_t i = base + u * stride;
       if (i < total_vec) {
-        int64_t row = i / vec_per_row;
-        int col = (int)(i - row * vec_per_row);
-        int64_t t = (row / rows_per_table_row) * vec_per_row + col;
-        xa[u].raw = ld_stream16(xv + i);
-        ca[u].raw = ld_cached16(cv + t);
-        sa[u].raw = ld_cached16(sv + t);
+        // vec_per_table_row = vectors of x served by one table row (heads * vec_per_row)
+        uint32_t t = (i / vec_per_table_row) * vec_per_row + i % vec_per_row;
+        xa[u].load_stream(xb + (int64_t)i * VB);
+        ca[u].load_cached(cb + (int64_t)t * VB);
+        sa[u].load_cached(sb + (int64_t)t * VB);
       }
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      int64_t i = base + u * stride;
+      uint32_t i = base + u * stride;
       if (i < total_vec) {
-        Vec16<T> o;
+        V o;
 #pragma unroll
-        for (int p = 0; p < VN; p += 2) {
-          float xe = to_f32(xa[u].e[p]), xo = to_f32(xa[u].e[p + 1]);
-          float ce = to_f32(ca[u].e[p]), co = to_f32(ca[u].e[p + 1]);
-          float se = to_f32(sa[u].e[p]), so = to_f32(sa[u].e[p + 1]);
-          // out[2i]   = (x*cos)[2i]   + (-x*sin)[2i+1]
-          // out[2i+1] = (x*cos)[2i+1] + ( x*sin)[2i]
-          float ev = rnd<T>(rnd<T>(xe * ce) + rnd<T>((-xo) * so));
-          float od = rnd<T>(rnd<T>(xo * co) + rnd<T>(xe * se));
-          o.e[p] = from_f32<T>(ev);
-          o.e[p + 1] = from_f32<T>(od);
-        }
-        st_stream16(ov + i, o.raw);
+        for (int p = 0; p < VN; p += 2)
+          rope_pair<T>(to_f32(xa[u][p]), to_f32(xa[u][p + 1]), to_f32(ca[u][p]), to_f32(ca[u][p + 1]),
+                       to_f32(sa[u][p]), to_f32(sa[u][p + 1]), o[p], o[p + 1]);
+        o.store_stream(ob + (int64_t)i * VB);
       }
     }
   }
@@ -208,8 +253,7 @@ rope_generic_kernel(const T* __restrict__ x, const T* __restrict__ cos_tab, cons
     float xe = to_f32(x[xi]), xo = to_f32(x[xi + 1]);
     float ce = to_f32(cos_tab[ti]), co = to_f32(cos_tab[ti + 1]);
     float se = to_f32(sin_tab[ti]), so = to_f32(sin_tab[ti + 1]);
-    out[xi] = from_f32<T>(rnd<T>(xe * ce) + rnd<T>((-xo) * so));
-    out[xi + 1] = from_f32<T>(rnd<T>(xo * co) + rnd<T>(xe * se));
+    rope_pair<T>(xe, xo, ce, co, se, so, out[xi], out[xi + 1]);
   }
 }
 
@@ -220,26 +264,34 @@ static unsigned elementwise_grid(int64_t work_items, int per_cta) {
   return (unsigned)(need < cap ? need : cap);
 }
 
+template <typename T, int VB, int UNROLL>
+static int launch_rope(const void* x, const void* c, const void* sn, void* out, int64_t rows, int64_t width,
+                       int64_t rptr, cudaStream_t s) {
+  const int64_t vpr = width * (int64_t)sizeof(T) / VB;
+  const int64_t total_vec = rows * vpr;
+  auto kernel = rope_kernel<T, VB, UNROLL>;
+  unsigned grid = resident_grid(kernel, total_vec, kThreads * UNROLL);
+  kernel<<<grid, kThreads, 0, s>>>((const T*)x, (const T*)c, (const T*)sn, (T*)out, (uint32_t)total_vec,
+                                   (uint32_t)vpr, (uint32_t)(vpr * rptr));
+  TL_LAUNCH_CHECK("rope_kernel");
+  return TL_B200_OK;
+}
+
 template <typename T>
 static int rope_dispatch(const void* x, const void* c, const void* sn, void* out, int64_t rows, int64_t width,
                          int64_t rptr, cudaStream_t s) {
-  constexpr int VN = Vec16<T>::N;
-  const bool vec_ok = width % VN == 0 && aligned16(x) && aligned16(c) && aligned16(sn) && aligned16(out) &&
-                      width / VN < (1ll << 31);
-  if (vec_ok) {
-    constexpr int UNROLL = 4;
-    int64_t total_vec = rows * (width / VN);
-    unsigned grid = elementwise_grid(total_vec, kThreads * UNROLL);
-    rope_kernel<T, UNROLL><<<grid, kThreads, 0, s>>>((const T*)x, (const T*)c, (const T*)sn, (T*)out,
-                                                     total_vec, (int)(width / VN), rptr);
-    TL_LAUNCH_CHECK("rope_kernel");
-  } else {
-    int64_t total_pairs = rows * (width / 2);
-    unsigned grid = elementwise_grid(total_pairs, kThreads);
-    rope_generic_kernel<T><<<grid, kThreads, 0, s>>>((const T*)x, (const T*)c, (const T*)sn, (T*)out,
-                                                     total_pairs, width / 2, rptr);
-    TL_LAUNCH_CHECK("rope_generic_kernel");
-  }
+  const int64_t row_bytes = width * (int64_t)sizeof(T);
+  // the vector kernels index with 32 bits
+  const bool small = rows * row_bytes / 16 < (1ll << 31) && row_bytes / 16 * rptr < (1ll << 31);
+  if (small && row_bytes % 32 == 0 && aligned32(x) && aligned32(c) && aligned32(sn) && aligned32(out))
+    return launch_rope<T, 32, 2>(x, c, sn, out, rows, width, rptr, s);
+  if (small && row_bytes % 16 == 0 && aligned16(x) && aligned16(c) && aligned16(sn) && aligned16(out))
+    return launch_rope<T, 16, 4>(x, c, sn, out, rows, width, rptr, s);
+  int64_t total_pairs = rows * (width / 2);
+  unsigned grid = elementwise_grid(total_pairs, kThreads);
+  rope_generic_kernel<T><<<grid, kThreads, 0, s>>>((const T*)x, (const T*)c, (const T*)sn, (T*)out,
+                                                   total_pairs, width / 2, rptr);
+  TL_LAUNCH_CHECK("rope_generic_kernel");
   return TL_B200_OK;
 }
 
@@ -256,34 +308,35 @@ template <typename T> __device__ __forceinline__ float silu_mul(float g, float u
   }
 }
 
-template <typename T, int UNROLL>
+template <typename T, int VB, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
 swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out, int64_t nvec,
               int64_t n_elems) {
-  constexpr int VN = Vec16<T>::N;
+  using V = VecT<T, VB>;
+  constexpr int VN = V::N;
   const int64_t stride = (int64_t)gridDim.x * kThreads;
   const int64_t tid = (int64_t)blockIdx.x * kThreads + threadIdx.x;
-  const uint4* gv = reinterpret_cast<const uint4*>(gate);
-  const uint4* uv = reinterpret_cast<const uint4*>(up);
-  uint4* ov = reinterpret_cast<uint4*>(out);
+  const char* gb = reinterpret_cast<const char*>(gate);
+  const char* ub = reinterpret_cast<const char*>(up);
+  char* ob = reinterpret_cast<char*>(out);
   for (int64_t base = tid; base < nvec; base += stride * UNROLL) {
-    Vec16<T> g[UNROLL], u[UNROLL];
+    V g[UNROLL], u[UNROLL];
 #pragma unroll
     for (int k = 0; k < UNROLL; ++k) {
       int64_t i = base + k * stride;
       if (i < nvec) {
-        g[k].raw = ld_stream16(gv + i);
-        u[k].raw = ld_stream16(uv + i);
+        g[k].load_stream(gb + i * VB);
+        u[k].load_stream(ub + i * VB);
       }
     }
 #pragma unroll
     for (int k = 0; k < UNROLL; ++k) {
       int64_t i = base + k * stride;
       if (i < nvec) {
-        Vec16<T> o;
+        V o;
 #pragma unroll
-        for (int j = 0; j < VN; ++j) o.e[j] = from_f32<T>(silu_mul<T>(to_f32(g[k].e[j]), to_f32(u[k].e[j])));
-        st_stream16(ov + i, o.raw);
+        for (int j = 0; j < VN; ++j) o[j] = from_f32<T>(silu_mul<T>(to_f32(g[k][j]), to_f32(u[k][j])));
+        o.store_stream(ob + i * VB);
       }
     }
   }
@@ -300,20 +353,23 @@ swiglu_scalar_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __
     out[i] = from_f32<T>(silu_mul<T>(to_f32(gate[i]), to_f32(up[i])));
 }
 
+template <typename T, int VB, int UNROLL>
+static int launch_swiglu(const void* g, const void* u, void* o, int64_t n, cudaStream_t s) {
+  int64_t nvec = n * (int64_t)sizeof(T) / VB;
+  auto kernel = swiglu_kernel<T, VB, UNROLL>;
+  unsigned grid = resident_grid(kernel, nvec, kThreads * UNROLL);
+  kernel<<<grid, kThreads, 0, s>>>((const T*)g, (const T*)u, (T*)o, nvec, n);
+  TL_LAUNCH_CHECK("swiglu_kernel");
+  return TL_B200_OK;
+}
+
 template <typename T>
 static int swiglu_dispatch(const void* g, const void* u, void* o, int64_t n, cudaStream_t s) {
-  constexpr int VN = Vec16<T>::N;
-  if (aligned16(g) && aligned16(u) && aligned16(o)) {
-    constexpr int UNROLL = 4;
-    int64_t nvec = n / VN;
-    unsigned grid = elementwise_grid(nvec, kThreads * UNROLL);
-    swiglu_kernel<T, UNROLL><<<grid, kThreads, 0, s>>>((const T*)g, (const T*)u, (T*)o, nvec, n);
-    TL_LAUNCH_CHECK("swiglu_kernel");
-  } else {
-    unsigned grid = elementwise_grid(n, kThreads);
-    swiglu_scalar_kernel<T><<<grid, kThreads, 0, s>>>((const T*)g, (const T*)u, (T*)o, n);
-    TL_LAUNCH_CHECK("swiglu_scalar_kernel");
-  }
+  if (aligned32(g) && aligned32(u) && aligned32(o)) return launch_swiglu<T, 32, 2>(g, u, o, n, s);
+  if (aligned16(g) && aligned16(u) && aligned16(o)) return launch_swiglu<T, 16, 4>(g, u, o, n, s);
+  unsigned grid = elementwise_grid(n, kThreads);
+  swiglu_scalar_kernel<T><<<grid, kThreads, 0, s>>>((const T*)g, (const T*)u, (T*)o, n);
+  TL_LAUNCH_CHECK("swiglu_scalar_kernel");
   return TL_B200_OK;
 }
 

@@ -23,6 +23,7 @@ PROTOTYPES = {
     "tl_b200_version": (c_int, []),
     "tl_b200_last_error": (c_char_p, []),
     "tl_b200_launch_count": (c_int64, []),
+    "tl_b200_device_status": (c_int, []),
     "tl_b200_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_void_p]),
     "tl_b200_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "tl_b200_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
@@ -31,6 +32,7 @@ PROTOTYPES = {
     "tl_b200_binary": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_float, c_int, c_void_p]),
     "tl_b200_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "tl_b200_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int64, c_int, c_void_p]),
+    "tl_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
 }
 
 

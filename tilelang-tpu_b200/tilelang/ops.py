@@ -177,3 +177,27 @@ def topk(src: torch.Tensor, out_vals: torch.Tensor, out_idx: torch.Tensor, k: in
     return N.check(N.load().tl_b200_topk(_ptr(src), _ptr(out_vals), _ptr(out_idx), rows, length, int(k),
                                         1 if descending else 0, out_stride, dtype_code(src.dtype), s),
                    "tl_b200_topk")
+
+
+def device_status() -> int:
+    """Status word left by a kernel that gave up a bounded wait (0 = none); clears it."""
+    return int(N.load().tl_b200_device_status())
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, transpose_b: bool = False) -> int:
+    """c = a @ b (b is (K, N)) or a @ b.T (b is (N, K), transpose_b=True); fp32 accumulation."""
+    if a.dim() != 2 or b.dim() != 2 or c.dim() != 2:
+        raise ValueError("gemm: a, b, c must be 2-D")
+    m, k = a.shape
+    n, kb = (b.shape[0], b.shape[1]) if transpose_b else (b.shape[1], b.shape[0])
+    if kb != k:
+        raise ValueError("gemm K shape check failed")          # message of ppl_gemm's assert
+    if tuple(c.shape) != (m, n):
+        raise ValueError(f"gemm: c must be ({m}, {n})")
+    if a.dtype != b.dtype or c.dtype not in (a.dtype, torch.float32):
+        raise ValueError("gemm: a and b must share a dtype; c has that dtype or float32")
+    if a.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise ValueError(f"gemm: unsupported dtype {a.dtype}")
+    s = _prepare(a, b, c)
+    return N.check(N.load().tl_b200_gemm(_ptr(a), _ptr(b), _ptr(c), m, n, k, 1 if transpose_b else 0,
+                                        dtype_code(a.dtype), dtype_code(c.dtype), s), "tl_b200_gemm")
