@@ -1,0 +1,273 @@
+"""Host-side front end: tracing of `T.ppl_*` programs, program matching, compile/adapter
+argument handling.  CPU only (binding a program needs no GPU; running it does)."""
+import ast
+from pathlib import Path
+
+import pytest
+import torch
+
+import tilelang
+import tilelang.language as T
+from tilelang.engine import UnsupportedProgram, bind
+
+REFERENCE = Path("/root/reference")
+
+
+# ------------------------------------------------------------------ programs written against the DSL
+def rms_norm_program(M, N, blk_m, dtype="bfloat16", eps=1e-12):
+    @T.prim_func
+    def main_kernel_inner(A: T.Tensor((M, N), dtype), B: T.Tensor((M, N), dtype)):
+        inv_n = T.float32(1.0 / N)
+        with T.Kernel(T.ceildiv(M, blk_m), is_cpu=True) as (bx,):
+            a16 = T.alloc_shared((blk_m, N), dtype)
+            a32 = T.alloc_shared((blk_m, N), "float32")
+            sq = T.alloc_shared((blk_m, N), "float32")
+            acc = T.alloc_shared((blk_m, 1), "float32")
+            T.ppl_copy(A[bx * blk_m, 0], a16)
+            T.ppl_copy(a16, a32)
+            T.ppl_mul(sq, a32, a32)
+            T.ppl_reduce_sum(sq, acc, dim=1)
+            T.ppl_mul_C(acc, acc, inv_n)
+            T.ppl_add_C(acc, acc, T.float32(eps))
+            T.ppl_rsqrt(acc, acc)
+            T.ppl_mul(a32, a32, acc)
+            T.ppl_copy(a32, a16)
+            T.ppl_copy(a16, B[bx * blk_m, 0])
+    return main_kernel_inner
+
+
+def matmul_program(M, N, K, bm, bn, bk, dtype="float16", trans_b=False):
+    b_shape = (N, K) if trans_b else (K, N)
+
+    @T.prim_func
+    def main_kernel_inner(A: T.Tensor((M, K), dtype), B: T.Tensor(b_shape, dtype), C: T.Tensor((M, N), dtype)):
+        with T.Kernel(T.ceildiv(N, bn), T.ceildiv(M, bm), is_cpu=True) as (bx, by):
+            a_t = T.alloc_shared((bm, bk), dtype)
+            b_t = T.alloc_shared((bn, bk) if trans_b else (bk, bn), dtype)
+            c_t = T.alloc_shared((bm, bn), "float32")
+            c_o = T.alloc_shared((bm, bn), dtype)
+            T.ppl_fill(c_t, T.float32(0))
+            for k in T.Pipelined(T.ceildiv(K, bk), num_stages=1):
+                T.ppl_copy(A[by * bm, k * bk], a_t)
+                if trans_b:
+                    T.ppl_copy(B[bx * bn, k * bk], b_t)
+                else:
+                    T.ppl_copy(B[k * bk, bx * bn], b_t)
+                T.ppl_gemm(a_t, b_t, c_t, transpose_B=trans_b)
+            T.ppl_copy(c_t, c_o)
+            T.ppl_copy(c_o, C[by * bm, bx * bn])
+    return main_kernel_inner
+
+
+def topk_program(length, K, descended=True):
+    @T.prim_func
+    def main_kernel_inner(Input: T.Tensor((length,), "float32"), Output: T.Tensor((length,), "float32"),
+                          Indices: T.Tensor((length,), "int32")):
+        with T.Kernel(1, 1, is_cpu=True) as (bx, by):
+            T.ppl_topk(Output, Indices, Input, K, 1 if descended else 0, length)
+    return main_kernel_inner
+
+
+# ------------------------------------------------------------------ tracing
+def test_trace_records_the_ppl_op_stream():
+    f = rms_norm_program(128, 128, 32)
+    assert [o.name for o in f.ops] == ["ppl.copy", "ppl.copy", "ppl.mul", "ppl.reduce_sum", "ppl.mul_C",
+                                       "ppl.add_C", "ppl.rsqrt", "ppl.mul", "ppl.copy", "ppl.copy"]
+    assert f.grid == (4,) and len(f.params) == 2 and f.params[0].shape == (128, 128)
+    load = f.ops[0]
+    src, dst = load.args
+    assert src.buffer is f.params[0] and src.extents == (32, 128)       # extents merged from the tile
+    assert repr(src.starts[0]) == "(bx * 32)" and src.starts[1] == 0
+    assert "ppl.rsqrt" in f.script()
+
+
+def test_trace_loops_slices_and_macros():
+    shape = [2, 64, 4, 16]
+
+    @T.macro
+    def load(K, tile, k, by, bz):
+        T.copy(K[bz, k * 8:(k + 1) * 8, by, :], tile)
+
+    @T.prim_func
+    def prog(K: T.Tensor(shape, "bfloat16"), O: T.Tensor(shape, "bfloat16")):
+        with T.Kernel(8, 4, 2, is_cpu=True) as (bx, by, bz):
+            tile = T.alloc_shared([8, 16], "bfloat16")
+            n = T.min(T.ceildiv(64, 8), T.ceildiv((bx + 1) * 8, 8))
+            for k in T.Pipelined(n, num_stages=2):
+                load(K, tile, k, by, bz)
+            T.copy(tile, O[bz, bx * 8:(bx + 1) * 8, by, :])
+
+    names = [o.name for o in prog.ops]
+    assert names == ["loop.begin", "ppl.copy", "loop.end", "ppl.copy"]
+    region = prog.ops[1].args[0]
+    assert region.extents == (1, 8, 1, 16)                 # point indices select one element
+    loop = prog.ops[0]
+    assert loop.attrs["num_stages"] == 2 and repr(loop.args[1]).startswith("min(")
+    bx, by, bz = prog.block_vars
+    assert loop.args[1].evaluate({bx: 2}) == 3 and loop.args[1].evaluate({bx: 7}) == 8
+
+
+def test_intrinsic_argument_checks():
+    with pytest.raises(AssertionError, match="gemm K shape check failed"):
+        @T.prim_func
+        def bad(A: T.Tensor((8, 8), "float16")):
+            with T.Kernel(1, is_cpu=True) as (bx,):
+                a = T.alloc_shared((8, 4), "float16")
+                b = T.alloc_shared((8, 8), "float16")
+                c = T.alloc_shared((8, 8), "float32")
+                T.ppl_gemm(a, b, c)
+    with pytest.raises(AssertionError, match="dim=1"):
+        @T.prim_func
+        def bad2(A: T.Tensor((8, 8), "float16")):
+            with T.Kernel(1, is_cpu=True) as (bx,):
+                a = T.alloc_shared((8, 8), "float16")
+                o = T.alloc_shared((8, 1), "float16")
+                T.ppl_reduce_sum(a, o, dim=0)
+    with pytest.raises(RuntimeError, match="inside a @T.prim_func"):
+        T.alloc_shared((4, 4), "float32")
+
+
+# ------------------------------------------------------------------ matching
+def test_bind_rmsnorm_extracts_eps_and_checks_the_mean_scale():
+    b = bind(rms_norm_program(128, 128, 32, eps=1e-6))
+    assert b.program == "rmsnorm" and b.entry_point == "tl_b200_rmsnorm"
+    assert b.facts["eps"] == pytest.approx(1e-6) and b.facts["rows"] == 128
+
+    @T.prim_func
+    def wrong_scale(A: T.Tensor((64, 64), "bfloat16"), B: T.Tensor((64, 64), "bfloat16")):
+        with T.Kernel(2, is_cpu=True) as (bx,):
+            a16 = T.alloc_shared((32, 64), "bfloat16")
+            a32 = T.alloc_shared((32, 64), "float32")
+            sq = T.alloc_shared((32, 64), "float32")
+            acc = T.alloc_shared((32, 1), "float32")
+            T.ppl_copy(A[bx * 32, 0], a16)
+            T.ppl_copy(a16, a32)
+            T.ppl_mul(sq, a32, a32)
+            T.ppl_reduce_sum(sq, acc, dim=1)
+            T.ppl_mul_C(acc, acc, T.float32(0.5))
+            T.ppl_add_C(acc, acc, T.float32(1e-6))
+            T.ppl_rsqrt(acc, acc)
+            T.ppl_mul(a32, a32, acc)
+            T.ppl_copy(a32, a16)
+            T.ppl_copy(a16, B[bx * 32, 0])
+    with pytest.raises(UnsupportedProgram, match="not 1/N"):
+        bind(wrong_scale)
+
+
+def test_bind_matmul_both_layouts_and_tiling_rule():
+    b = bind(matmul_program(64, 64, 64, 32, 32, 32))
+    assert b.program == "matmul" and b.facts["transpose_B"] is False and b.facts["K"] == 64
+    b = bind(matmul_program(128, 256, 64, 32, 64, 32, dtype="bfloat16", trans_b=True))
+    assert b.facts["transpose_B"] is True and b.facts["N"] == 256
+    with pytest.raises(UnsupportedProgram, match="no tail masking"):
+        bind(matmul_program(100, 64, 64, 32, 32, 32))
+
+
+def test_unmatched_program_is_rejected_with_its_listing():
+    @T.prim_func
+    def odd(A: T.Tensor((8, 8), "float32"), B: T.Tensor((8, 8), "float32")):
+        with T.Kernel(1, is_cpu=True) as (bx,):
+            t = T.alloc_shared((8, 8), "float32")
+            T.ppl_copy(A[0, 0], t)
+            T.ppl_rsqrt(t, t)
+            T.ppl_rsqrt(t, t)
+            T.ppl_copy(t, B[0, 0])
+    with pytest.raises(UnsupportedProgram, match="no CPU fallback"):
+        tilelang.compile(odd, out_idx=-1, target="b200")
+
+
+# ------------------------------------------------------------------ compile / adapter
+def test_compile_signature_and_out_idx_legalisation():
+    k = tilelang.compile(rms_norm_program(128, 128, 32), out_idx=-1, target="b200")
+    assert k.adapter.result_idx == [1] and [p.shape for p in k.params] == [[128, 128], [128, 128]]
+    assert k.params[0].dtype == torch.bfloat16
+    assert "tl_b200_rmsnorm" in k.get_kernel_source()
+    k2 = tilelang.compile(topk_program(1024, 8), out_idx=[1, 2], target="b200", mode="cmodel")
+    assert k2.adapter.result_idx == [1, 2]
+    with pytest.raises(ValueError):
+        tilelang.compile(topk_program(64, 8), out_idx=[5], target="b200")
+    with pytest.raises(AssertionError, match="not supported"):
+        tilelang.compile(topk_program(64, 8), out_idx=[1, 2], target="tpu")
+    with pytest.raises(AssertionError, match="Invalid mode"):
+        tilelang.compile(topk_program(64, 8), out_idx=[1, 2], target="b200", mode="fpga")
+
+
+def test_tpu_target_alias_is_opt_in(monkeypatch):
+    monkeypatch.setenv("TL_B200_ACCEPT_TPU_TARGET", "1")
+    k = tilelang.compile(topk_program(128, 4), out_idx=[1, 2], target="tpu")
+    assert k.target == "b200"
+
+
+def test_adapter_validates_arguments_before_launch():
+    k = tilelang.compile(rms_norm_program(128, 128, 32), out_idx=-1, target="b200")
+    a = torch.zeros(128, 128, dtype=torch.bfloat16)
+    with pytest.raises(ValueError, match="Expected 2 inputs"):
+        k(a)
+    with pytest.raises(ValueError, match="dtype"):
+        k(a, a.float())
+    with pytest.raises(ValueError, match="shape"):
+        k(a, torch.zeros(64, 128, dtype=torch.bfloat16))
+
+
+def test_compile_is_cached_per_program_object():
+    f = topk_program(256, 4)
+    assert tilelang.compile(f, out_idx=[1, 2], target="b200") is tilelang.compile(f, out_idx=[1, 2], target="b200")
+
+
+# ------------------------------------------------------------------ the reference's own demo programs
+def _reference_builder(rel_path: str, func_name: str):
+    """Lift one program-builder function out of a reference demo script (the script itself builds
+    a TPU kernel at import time, so it cannot be imported) and bind it to this package's T."""
+    src = (REFERENCE / rel_path).read_text()
+    tree = ast.parse(src)
+    nodes = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == func_name]
+    assert nodes, f"{func_name} not found in {rel_path}"
+    env = {"tilelang": tilelang, "T": T, "torch": torch}
+    T.copy = T.ppl_copy            # the demos do this at module level
+    exec(compile(ast.Module(body=nodes, type_ignores=[]), str(REFERENCE / rel_path), "exec"), env)
+    return env[func_name]
+
+
+needs_reference = pytest.mark.skipif(not REFERENCE.exists(), reason="reference tree not present")
+
+DEMOS = [
+    ("tpu_demo/matmul/tpu_test_matmul_fp16.py", "matmul", (64, 64, 64, 32, 32, 32), "matmul"),
+    ("tpu_demo/matmul/tpu_test_matmul_bf16.py", "matmul", (64, 64, 64, 32, 32, 32), "matmul"),
+    ("tpu_demo/rms_norm/rms_norm_bf16.py", "rms_norm", (128, 128, 32), "rmsnorm"),
+    ("tpu_demo/rms_norm/rmsnorm_splitk_bf16.py", "rms_norm_splitk", (512, 512, 32, 32), "rmsnorm_splitk"),
+    ("tpu_demo/tpu_test_rope_bf16.py", "rope", (64, 16, 128, 64), "rope"),
+    ("tpu_demo/tpu_test_swiglu_bf16.py", "swi_glu", (32, 32, 64, 64), "swiglu"),
+    ("tpu_demo/tpu_test_reduce_sum.py", "reduce_sum", (64, 64, 32, 64), "reduce_sum"),
+    ("tpu_demo/tpu_test_reduce_max.py", "reduce_max", (64, 64, 32, 64), "reduce_max"),
+    ("tpu_demo/tpu_test_topk_fp32.py", "topk_kernel", (1024, 8), "topk"),
+    ("tpu_demo/tpu_test_gather_fp32.py", "gather_kernel", (128, 64, 8), "gather"),
+    ("tpu_demo/tpu_test_sigmoid_fp32.py", "sigmoid_kernel", (32, 32, 1024, 1024), "sigmoid"),
+    ("tpu_demo/ppl/elementwise_add_kernel/elementwise_add.py", "elementwise_add",
+     (128, 128, 32, 32, "float32", "float32", 128), "elementwise_add"),
+]
+
+
+@needs_reference
+@pytest.mark.parametrize("path,builder,args,program", DEMOS, ids=[d[3] + "_" + Path(d[0]).stem for d in DEMOS])
+def test_unmodified_reference_demo_programs_bind(path, builder, args, program):
+    func = _reference_builder(path, builder)(*args)
+    assert bind(func).program == program
+
+
+@needs_reference
+@pytest.mark.parametrize("causal", [False, True])
+def test_reference_flash_attention_program_binds(causal):
+    build = _reference_builder("tpu_demo/flashattn/tpu_test_flashattn_bf16.py", "flashattn")
+    func = build(batch=1, heads=2, seq_len=256, dim=64, is_causal=causal)(64, 64, 1, 128)
+    b = bind(func)
+    assert b.program == "flash_attention_fwd"
+    assert b.facts["causal"] == ("block" if causal else "none")
+    assert b.facts["scale"] == pytest.approx(64 ** -0.5) and b.facts["block_M"] == 64
+
+
+@needs_reference
+def test_reference_mla_decode_program_binds():
+    build = _reference_builder("tpu_demo/ppl/deepseek_mla/mla_decode.py", "flashattn")
+    b = bind(build(4, 8, 1, 512, 32, 4, 4, 4))
+    assert b.program == "mla_decode" and b.facts["pe_dim"] == 4 and b.facts["seqlen_kv"] == 512
+    assert b.facts["scale"] == pytest.approx(36 ** -0.5)

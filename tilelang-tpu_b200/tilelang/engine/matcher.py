@@ -1,0 +1,400 @@
+"""Program matcher: binds a traced `ppl.*` program to a hand-written CUDA program.
+
+The reference lowers every program through TVM passes and prints C for the SOPHGO runtime
+(tilelang/engine/lower.py:195-250, src/target/codegen_ppl.cc).  Here the kernels are pre-built,
+so "lowering" is recognition: the op stream of a prim_func is compared with the canonical form
+of each supported program (the programs of tpu_demo/), the facts that matter (shapes, scalars,
+operand order, layouts) are extracted and checked, and the program is bound to one C-ABI entry
+point.  A program that matches nothing is rejected loudly; nothing ever falls back to the CPU.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Callable, Optional
+
+import torch
+
+from ..language.ir import Buffer, Call, Op, PrimFunc, Region, const_value
+
+
+class UnsupportedProgram(NotImplementedError):
+    pass
+
+
+@dataclass
+class BoundKernel:
+    """A recognised program: `run(*device_tensors) -> int` launches the CUDA kernels."""
+    program: str                   # e.g. "rmsnorm"
+    entry_point: str               # C-ABI symbol(s) it calls
+    run: Callable[..., int]
+    facts: dict
+
+    def describe(self) -> str:
+        return f"{self.program} -> {self.entry_point} {self.facts}"
+
+
+# ------------------------------------------------------------------------------- helpers
+def _names(ops):
+    return [o.name for o in ops]
+
+
+def _is_param(x, func: PrimFunc, index: Optional[int] = None) -> bool:
+    buf = x.buffer if isinstance(x, Region) else x
+    if not isinstance(buf, Buffer) or buf.scope != "global":
+        return False
+    return index is None or buf.param_index == index
+
+
+def _buf(x) -> Buffer:
+    return x.buffer if isinstance(x, Region) else x
+
+
+def _close(a: float, b: float, rel=1e-6) -> bool:
+    return abs(a - b) <= rel * max(abs(a), abs(b), 1e-30)
+
+
+def _require(cond, msg):
+    if not cond:
+        raise UnsupportedProgram(msg)
+
+
+def _check_tiling(func: PrimFunc, what: str, pairs):
+    """The reference checks tile bounds statically and has no tail masking
+    (src/target/codegen_ppl.cc:967-1002): tiles must divide the tensor."""
+    for full, tile in pairs:
+        _require(full % tile == 0, f"{what}: tile {tile} does not divide dimension {full} "
+                                   f"(the tile path has no tail masking)")
+
+
+def _grid(func: PrimFunc):
+    g = [const_value(e) for e in func.grid]
+    _require(all(v is not None for v in g), "launch grid must be static")
+    return [int(v) for v in g]
+
+
+# ------------------------------------------------------------------------------- programs
+def _match_matmul(func: PrimFunc):
+    n = _names(func.ops)
+    if n[:6] != ["ppl.fill", "loop.begin", "ppl.copy", "ppl.copy", "ppl.gemm", "loop.end"]:
+        return None
+    tail = n[6:]
+    if tail not in (["ppl.copy"], ["ppl.copy", "ppl.copy"]) or len(func.params) != 3:
+        return None
+    ops = func.ops
+    fill, _, cp_a, cp_b, gemm, _ = ops[:6]
+    a_tile, b_tile, c_tile = gemm.args
+    if fill.args[0] is not c_tile or fill.args[1] != 0.0:
+        return None
+    if _buf(cp_a.args[1]) is not a_tile or _buf(cp_b.args[1]) is not b_tile:
+        return None
+    a_src, b_src, store = cp_a.args[0], cp_b.args[0], ops[-1].args[1]
+    if not (_is_param(a_src, func) and _is_param(b_src, func) and _is_param(store, func)):
+        return None
+    _require(not gemm.attrs["transpose_A"], "matmul: transpose_A is not supported (the reference's code "
+                                            "generator ignores it)")
+    trans_b = gemm.attrs["transpose_B"]
+    A, B, C = _buf(a_src), _buf(b_src), _buf(store)
+    _require(len(A.shape) == 2 and len(B.shape) == 2 and len(C.shape) == 2, "matmul: tensors must be 2-D")
+    M, K = A.shape
+    N = B.shape[0] if trans_b else B.shape[1]
+    _require((B.shape[1] if trans_b else B.shape[0]) == K and tuple(C.shape) == (M, N),
+             "matmul: inconsistent A/B/C shapes")
+    bm, bk = a_tile.shape
+    bn = b_tile.shape[0] if trans_b else b_tile.shape[1]
+    _check_tiling(func, "matmul", [(M, bm), (N, bn), (K, bk)])
+    _require(const_value(ops[1].args[1]) == K // bk, "matmul: the K loop must cover K")
+    _require(sorted(_grid(func)) == sorted([N // bn, M // bm]), "matmul: the grid must cover C")
+    ia, ib, ic = A.param_index, B.param_index, C.param_index
+    from .. import ops as native
+
+    def run(*t):
+        return native.gemm(t[ia], t[ib], t[ic], transpose_b=trans_b)
+
+    return BoundKernel("matmul", "tl_b200_gemm", run,
+                       dict(M=M, N=N, K=K, transpose_B=trans_b, in_dtype=A.dtype, out_dtype=C.dtype))
+
+
+_RMS_BODY = ["ppl.copy", "ppl.copy", "ppl.mul", "ppl.reduce_sum", "ppl.mul_C", "ppl.add_C", "ppl.rsqrt", "ppl.mul",
+             "ppl.copy", "ppl.copy"]
+_RMS_SPLITK = ["ppl.fill", "loop.begin", "ppl.copy", "ppl.copy", "ppl.mul", "ppl.reduce_sum", "ppl.add", "loop.end",
+               "ppl.mul_C", "ppl.add_C", "ppl.rsqrt", "loop.begin", "ppl.copy", "ppl.copy", "ppl.mul", "ppl.copy",
+               "ppl.copy", "loop.end"]
+
+
+def _match_rmsnorm(func: PrimFunc):
+    n = _names(func.ops)
+    if n not in (_RMS_BODY, _RMS_SPLITK) or len(func.params) != 2:
+        return None
+    ops = func.ops
+    split = n == _RMS_SPLITK
+    load = ops[2] if split else ops[0]
+    store = ops[-2] if split else ops[-1]
+    mul_c = next(o for o in ops if o.name == "ppl.mul_C")
+    add_c = next(o for o in ops if o.name == "ppl.add_C")
+    if not (_is_param(load.args[0], func) and _is_param(store.args[1], func)):
+        return None
+    X, Y = _buf(load.args[0]), _buf(store.args[1])
+    _require(len(X.shape) == 2 and X.shape == Y.shape and X.dtype == Y.dtype, "rmsnorm: A and B must be equal 2-D")
+    M, N = X.shape
+    _require(_close(mul_c.args[2], 1.0 / N), f"rmsnorm: the mean scale {mul_c.args[2]} is not 1/N")
+    tile = _buf(load.args[1])
+    _check_tiling(func, "rmsnorm", [(M, tile.shape[0]), (N, tile.shape[1])])
+    _require(split or tile.shape[1] == N, "rmsnorm: the row tile must span N")
+    eps = float(add_c.args[2])
+    ix, iy = X.param_index, Y.param_index
+    from .. import ops as native
+
+    def run(*t):
+        return native.rmsnorm(t[ix], t[iy], None, eps)
+
+    return BoundKernel("rmsnorm_splitk" if split else "rmsnorm", "tl_b200_rmsnorm", run,
+                       dict(rows=M, cols=N, eps=eps, dtype=X.dtype))
+
+
+_ROPE = ["ppl.copy", "ppl.copy", "ppl.copy", "ppl.mul", "ppl.mul", "ppl.mul_C", "ppl.mul", "ppl.rope_add", "ppl.copy"]
+
+
+def _match_rope(func: PrimFunc):
+    if _names(func.ops) != _ROPE or len(func.params) != 4:
+        return None
+    ops = func.ops
+    ld_x, ld_c, ld_s, mul_xc, mul_xs, neg, mul_ns, radd, store = ops
+    x_t, c_t, s_t = _buf(ld_x.args[1]), _buf(ld_c.args[1]), _buf(ld_s.args[1])
+    ok = (mul_xc.args[1] is x_t and mul_xc.args[2] is c_t and mul_xs.args[1] is x_t and mul_xs.args[2] is s_t
+          and neg.args[1] is x_t and neg.args[2] == -1.0 and mul_ns.args[1] is neg.args[0]
+          and mul_ns.args[2] is s_t)
+    x_cos, x_sin, x_neg_sin = mul_xc.args[0], mul_xs.args[0], mul_ns.args[0]
+    out_t, e1, e2, o1, o2 = radd.args
+    ok = ok and e1 is x_cos and e2 is x_neg_sin and o1 is x_cos and o2 is x_sin and _buf(store.args[0]) is out_t
+    if not ok:
+        return None
+    X, Cs, Sn, Out = _buf(ld_x.args[0]), _buf(ld_c.args[0]), _buf(ld_s.args[0]), _buf(store.args[1])
+    _require(X.shape == Cs.shape == Sn.shape == Out.shape and len(X.shape) == 2, "rope: x/cos/sin/out must be "
+             "equal 2-D tensors")
+    _require(X.dtype == Cs.dtype == Sn.dtype == Out.dtype, "rope: one dtype for x/cos/sin/out")
+    _check_tiling(func, "rope", [(X.shape[0], x_t.shape[0]), (X.shape[1], x_t.shape[1])])
+    _require(x_t.shape[1] % 2 == 0, "rope: tile width must be even")
+    idx = [b.param_index for b in (X, Cs, Sn, Out)]
+    from .. import ops as native
+
+    def run(*t):
+        return native.rope(t[idx[0]], t[idx[1]], t[idx[2]], t[idx[3]])
+
+    return BoundKernel("rope", "tl_b200_rope", run, dict(rows=X.shape[0], width=X.shape[1], dtype=X.dtype))
+
+
+_SWIGLU = ["ppl.fill", "ppl.copy", "ppl.copy", "ppl.copy", "ppl.copy", "ppl.mul_C", "ppl.exp", "ppl.add", "ppl.div",
+           "ppl.mul", "ppl.copy", "ppl.copy"]
+
+
+def _match_swiglu(func: PrimFunc):
+    if _names(func.ops) != _SWIGLU or len(func.params) != 3:
+        return None
+    fill, ld_g, ld_u, cv_g, cv_u, neg, ex, add1, div, mul, cv_o, store = func.ops
+    ones = fill.args[0]
+    g32, u32 = _buf(cv_g.args[1]), _buf(cv_u.args[1])
+    ok = (fill.args[1] == 1.0 and _buf(cv_g.args[0]) is _buf(ld_g.args[1]) and _buf(cv_u.args[0]) is _buf(ld_u.args[1])
+          and neg.args[1] is g32 and neg.args[2] == -1.0 and ex.args[0] is neg.args[0]
+          and add1.args[1] is neg.args[0] and add1.args[2] is ones
+          and div.args[1] is g32 and div.args[2] is add1.args[0]
+          and mul.args[1] is u32 and mul.args[2] is div.args[0]
+          and _buf(cv_o.args[0]) is mul.args[0] and _buf(store.args[0]) is _buf(cv_o.args[1]))
+    if not ok:
+        return None
+    G, U, Out = _buf(ld_g.args[0]), _buf(ld_u.args[0]), _buf(store.args[1])
+    _require(G.shape == U.shape == Out.shape and G.dtype == U.dtype == Out.dtype, "swiglu: equal shapes and dtypes")
+    t = _buf(ld_g.args[1])
+    _check_tiling(func, "swiglu", [(G.shape[0], t.shape[0]), (G.shape[1], t.shape[1])])
+    idx = [b.param_index for b in (G, U, Out)]
+    from .. import ops as native
+
+    def run(*ts):
+        return native.swiglu(ts[idx[0]], ts[idx[1]], ts[idx[2]])
+
+    return BoundKernel("swiglu", "tl_b200_swiglu", run, dict(shape=list(G.shape), dtype=G.dtype))
+
+
+def _match_reduce(func: PrimFunc):
+    n = [x for x in _names(func.ops) if x != "ppl.fill"]
+    if len(n) != 3 or n[0] != "ppl.copy" or n[2] != "ppl.copy" or n[1] not in ("ppl.reduce_sum", "ppl.reduce_max"):
+        return None
+    ops = [o for o in func.ops if o.name != "ppl.fill"]
+    X, Y = _buf(ops[0].args[0]), _buf(ops[2].args[1])
+    if not (_is_param(X, func) and _is_param(Y, func)):
+        return None
+    tile = _buf(ops[0].args[1])
+    _require(len(X.shape) == 2 and tile.shape[1] == X.shape[1], "row reduce: the tile must span the whole row")
+    _require(Y.shape[0] == X.shape[0] and X.dtype == Y.dtype, "row reduce: Y must be (M, 1) of X's dtype")
+    _check_tiling(func, "row reduce", [(X.shape[0], tile.shape[0])])
+    op = "sum" if n[1] == "ppl.reduce_sum" else "max"
+    ix, iy = X.param_index, Y.param_index
+    from .. import ops as native
+
+    def run(*t):
+        return native.reduce_rows(t[ix], t[iy], op)
+
+    return BoundKernel(f"reduce_{op}", "tl_b200_reduce_rows", run, dict(rows=X.shape[0], cols=X.shape[1], dtype=X.dtype))
+
+
+def _match_topk(func: PrimFunc):
+    if _names(func.ops) != ["ppl.topk"]:
+        return None
+    dst, idx, src, k, desc, length = func.ops[0].args
+    _require(all(_is_param(b, func) for b in (dst, idx, src)), "topk operates on kernel parameters")
+    _require(src.shape[-1] == length, "topk: length must equal the source length")
+    i_d, i_i, i_s = dst.param_index, idx.param_index, src.param_index
+    from .. import ops as native
+
+    def run(*t):
+        return native.topk(t[i_s], t[i_d], t[i_i], k, bool(desc))
+
+    return BoundKernel("topk", "tl_b200_topk", run, dict(length=length, K=k, descended=bool(desc), dtype=src.dtype))
+
+
+def _match_gather(func: PrimFunc):
+    if _names(func.ops) != ["ppl.gather"]:
+        return None
+    out, param, index, rows = func.ops[0].args
+    _require(all(_is_param(b, func) for b in (out, param, index)), "gather operates on kernel parameters")
+    _require(rows == param.shape[0], "gather: param_h must equal the number of rows of Param")
+    i_o, i_p, i_i = out.param_index, param.param_index, index.param_index
+    from .. import ops as native
+
+    def run(*t):
+        return native.gather_rows(t[i_p], t[i_i], t[i_o])
+
+    return BoundKernel("gather", "tl_b200_gather_rows", run,
+                       dict(rows=rows, hidden=param.shape[1], n=out.shape[0], dtype=param.dtype))
+
+
+def _match_elementwise(func: PrimFunc):
+    n = _names(func.ops)
+    from .. import ops as native
+    if n == ["ppl.copy", "ppl.sigmoid", "ppl.copy"]:
+        ld, sg, st = func.ops
+        if not (sg.args[1] is _buf(ld.args[1]) and _buf(st.args[0]) is sg.args[0]):
+            return None
+        X, Y = _buf(ld.args[0]), _buf(st.args[1])
+        _require(X.shape == Y.shape, "sigmoid: equal shapes")
+        ix, iy = X.param_index, Y.param_index
+        return BoundKernel("sigmoid", "tl_b200_unary", lambda *t: native.unary(t[ix], t[iy], "sigmoid"),
+                           dict(shape=list(X.shape), dtype=X.dtype))
+    binary = {"ppl.add": "add", "ppl.sub": "sub", "ppl.mul": "mul", "ppl.div": "div"}
+    if len(n) == 4 and n[0] == n[1] == n[3] == "ppl.copy" and n[2] in binary:
+        la, lb, op, st = func.ops
+        if not (op.args[1] is _buf(la.args[1]) and op.args[2] is _buf(lb.args[1]) and _buf(st.args[0]) is op.args[0]):
+            return None
+        A, B, C = _buf(la.args[0]), _buf(lb.args[0]), _buf(st.args[1])
+        _require(A.shape == B.shape == C.shape and A.dtype == B.dtype == C.dtype and len(A.shape) == 2,
+                 "elementwise: equal 2-D shapes and dtypes")
+        name = binary[n[2]]
+        ia, ib, ic = A.param_index, B.param_index, C.param_index
+        return BoundKernel(f"elementwise_{name}", "tl_b200_binary", lambda *t: native.binary(t[ia], t[ib], t[ic], name),
+                           dict(shape=list(A.shape), dtype=A.dtype))
+    return None
+
+
+_FA_PROLOGUE = ["ppl.copy", "ppl.fill", "ppl.fill", "ppl.fill"]
+_FA_LOOP = ["ppl.copy", "ppl.fill", "ppl.gemm",                                   # S = Q K^T
+            "ppl.copy", "ppl.fill", "ppl.reduce_max", "ppl.sub", "ppl.mul_C", "ppl.exp",
+            "ppl.sub", "ppl.mul_C", "ppl.exp", "ppl.reduce_sum", "ppl.mul", "ppl.add", "ppl.copy",
+            "ppl.mul",                                                           # rescale O
+            "ppl.copy", "ppl.gemm"]                                              # O += P V
+_FA_EPILOGUE = ["ppl.div", "ppl.copy", "ppl.copy"]
+
+
+def _match_flash_attention(func: PrimFunc):
+    n = _names(func.ops)
+    want = _FA_PROLOGUE + ["loop.begin"] + _FA_LOOP + ["loop.end"] + _FA_EPILOGUE
+    if n != want or len(func.params) != 4:
+        return None
+    ops = func.ops
+    ld_q = ops[0]
+    loop = ops[4]
+    body = ops[5:5 + len(_FA_LOOP)]
+    ld_k, _, qk = body[0], body[1], body[2]
+    mul_scale = body[7]
+    ld_v, pv = body[17], body[18]
+    store = ops[-1]
+    Q, K, V, O = _buf(ld_q.args[0]), _buf(ld_k.args[0]), _buf(ld_v.args[0]), _buf(store.args[1])
+    if not all(_is_param(b, func) for b in (Q, K, V, O)):
+        return None
+    _require(qk.attrs["transpose_B"] and not pv.attrs["transpose_B"], "flash attention: S = Q K^T, O += P V")
+    _require(len(Q.shape) == 4 and Q.shape == O.shape and K.shape == V.shape, "flash attention: bshd tensors")
+    batch, seq_q, heads, dim = Q.shape
+    seq_k = K.shape[1]
+    bm = _buf(ld_q.args[1]).shape[0]
+    bn = _buf(ld_k.args[1]).shape[0]
+    _check_tiling(func, "flash attention", [(seq_q, bm), (seq_k, bn)])
+    scale = float(mul_scale.args[2])
+    extent = loop.args[1]
+    full = -(-seq_k // bn)
+    if const_value(extent) is not None:
+        _require(const_value(extent) == full, "flash attention: the KV loop must cover the sequence")
+        mode, diag = "none", 0
+    else:
+        # min(ceil(S/bn), ceil((bx+1)*bm / bn)): the reference's shortened causal loop; it does
+        # NOT mask inside the last tile, so a query sees every key of that tile.
+        _require(isinstance(extent, Call) and extent.fn == "min", "flash attention: unrecognised KV loop extent")
+        mode, diag = "block", 0
+    idx = [b.param_index for b in (Q, K, V, O)]
+    from .. import ops as native
+
+    def run(*t):
+        return native.flash_attn_fwd(t[idx[0]], t[idx[1]], t[idx[2]], t[idx[3]], scale=scale, causal=mode,
+                                     block_m=bm, block_n=bn)
+
+    return BoundKernel("flash_attention_fwd", "tl_b200_flash_attn_fwd", run,
+                       dict(batch=batch, heads=heads, seq_q=seq_q, seq_kv=seq_k, dim=dim, scale=scale, causal=mode,
+                            block_M=bm, block_N=bn, dtype=Q.dtype))
+
+
+def _match_mla_decode(func: PrimFunc):
+    n = _names(func.ops)
+    if len(func.params) != 5 or n.count("ppl.gemm") != 3 or n.count("loop.begin") != 1:
+        return None
+    if n[:5] != ["ppl.copy", "ppl.copy", "ppl.fill", "ppl.fill", "ppl.fill"] or n[-3:] != ["ppl.div", "ppl.copy", "ppl.copy"]:
+        return None
+    ops = func.ops
+    gemms = [o for o in ops if o.name == "ppl.gemm"]
+    if not (gemms[0].attrs["transpose_B"] and gemms[1].attrs["transpose_B"] and not gemms[2].attrs["transpose_B"]):
+        return None
+    loop_i = n.index("loop.begin")
+    ld_kv, ld_kpe = ops[loop_i + 1], ops[loop_i + 2]
+    Q, Qpe = _buf(ops[0].args[0]), _buf(ops[1].args[0])
+    KV, Kpe, Out = _buf(ld_kv.args[0]), _buf(ld_kpe.args[0]), _buf(ops[-1].args[1])
+    if not all(_is_param(b, func) for b in (Q, Qpe, KV, Kpe, Out)):
+        return None
+    _require(gemms[2].args[1] is gemms[0].args[1], "mla decode: V must be the latent KV tile")
+    b, h, one, dim = Q.shape
+    pe = Qpe.shape[-1]
+    s = KV.shape[1]
+    _require(one == 1 and KV.shape[2] == 1, "mla decode: one query token, one latent kv head")
+    scales = {float(o.args[2]) for o in ops if o.name == "ppl.mul_C"}
+    _require(len(scales) == 1, "mla decode: a single softmax scale is expected")
+    scale = scales.pop()
+    idx = [x.param_index for x in (Q, Qpe, KV, Kpe, Out)]
+    from .. import ops as native
+
+    def run(*t):
+        return native.mla_decode_dense(t[idx[0]], t[idx[1]], t[idx[2]], t[idx[3]], t[idx[4]], scale=scale)
+
+    return BoundKernel("mla_decode", "tl_b200_mla_decode_dense", run,
+                       dict(batch=b, heads=h, seqlen_kv=s, dim=dim, pe_dim=pe, scale=scale, dtype=Q.dtype))
+
+
+_MATCHERS = [_match_matmul, _match_rmsnorm, _match_rope, _match_swiglu, _match_reduce, _match_topk, _match_gather,
+             _match_elementwise, _match_flash_attention, _match_mla_decode]
+
+
+def bind(func: PrimFunc) -> BoundKernel:
+    """Recognise `func` and bind it to its CUDA program; raises UnsupportedProgram otherwise."""
+    for m in _MATCHERS:
+        bound = m(func)
+        if bound is not None:
+            return bound
+    raise UnsupportedProgram(
+        "this ppl_* program does not match any kernel of the b200 library (matmul, rmsnorm, "
+        "rmsnorm split-K, rope, swiglu, row reduce, top-k, gather, sigmoid, elementwise, flash "
+        "attention forward, MLA decode); there is no CPU fallback.  Recorded program:\n" + func.script())
