@@ -132,6 +132,28 @@ int tl_b200_topk(const void* src, void* out_vals, int32_t* out_idx, int64_t rows
 int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
                  int in_dtype, int out_dtype, void* stream);
 
+/* ---- FlashAttention forward -----------------------------------------------------
+ * o = softmax(scale * q k^T + mask) v on bshd tensors: q, o [batch, seq_q, heads, dim];
+ * k, v [batch, seq_kv, heads, dim]; fp32 softmax statistics; P is rounded to `dtype` before the
+ * second product, as the program does.  Replaces the program
+ * tpu_demo/flashattn/tpu_test_flashattn_bf16.py:14-135 (ppl_gemm / ppl_reduce_max / ppl_exp2 /
+ * ppl_reduce_sum chain).  mask_mode 0: none; 1: causal (key <= query), the mask of the
+ * reference's check function (:171-182); 2: the reference program's own causal form, a KV loop
+ * shortened to ceil((bx+1)*block_m/block_n) tiles with no mask inside the last tile (:116-118).
+ * TL_BF16 / TL_F16 with dim 64 or 128 run on tcgen05; other cases use an FMA kernel.          */
+int tl_b200_flash_attn_fwd(const void* q, const void* k, const void* v, void* o, int64_t batch,
+                           int64_t seq_q, int64_t seq_kv, int64_t heads, int64_t dim, float scale,
+                           int mask_mode, int block_m, int block_n, int dtype, void* stream);
+
+/* ---- MLA decode, dense cache ----------------------------------------------------
+ * out[b,h,0,:] = softmax(scale * (q.kv^T + q_pe.k_pe^T)) kv with q [batch,heads,1,dim],
+ * q_pe [batch,heads,1,pe_dim], kv [batch,seq_kv,1,dim], k_pe [batch,seq_kv,1,pe_dim],
+ * out [batch,heads,1,dim]; V is the latent kv itself.  Replaces the program
+ * tpu_demo/ppl/deepseek_mla/mla_decode.py:9-121.                                             */
+int tl_b200_mla_decode_dense(const void* q, const void* q_pe, const void* kv, const void* k_pe,
+                             void* out, int64_t batch, int64_t heads, int64_t seq_kv, int64_t dim,
+                             int64_t pe_dim, float scale, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -201,3 +201,48 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, transpose_b: bool = 
     s = _prepare(a, b, c)
     return N.check(N.load().tl_b200_gemm(_ptr(a), _ptr(b), _ptr(c), m, n, k, 1 if transpose_b else 0,
                                         dtype_code(a.dtype), dtype_code(c.dtype), s), "tl_b200_gemm")
+
+
+_MASK_MODES = {False: 0, None: 0, "none": 0, True: 1, "causal": 1, "block": 2}
+
+
+def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, scale: float | None = None,
+                   causal=False, block_m: int = 0, block_n: int = 0) -> int:
+    """Attention forward on bshd tensors.  causal: False / True (key <= query) / "block" (the
+    reference program's shortened KV loop without a mask inside the last tile; needs block sizes)."""
+    if q.dim() != 4 or k.dim() != 4 or k.shape != v.shape or o.shape != q.shape:
+        raise ValueError("flash_attn_fwd: q, o are (B, Sq, H, D); k, v are (B, Skv, H, D)")
+    b, sq, h, d = q.shape
+    if k.shape[0] != b or k.shape[2] != h or k.shape[3] != d:
+        raise ValueError("flash_attn_fwd: q and k/v disagree on batch, heads or head dim")
+    if not (q.dtype == k.dtype == v.dtype == o.dtype):
+        raise ValueError("flash_attn_fwd: one dtype for q, k, v, o")
+    try:
+        mode = _MASK_MODES[causal]
+    except (KeyError, TypeError):
+        raise ValueError(f"flash_attn_fwd: unknown mask {causal!r}") from None
+    if scale is None:
+        scale = d ** -0.5
+    s = _prepare(q, k, v, o)
+    return N.check(N.load().tl_b200_flash_attn_fwd(_ptr(q), _ptr(k), _ptr(v), _ptr(o), b, sq, k.shape[1], h, d,
+                                                  float(scale), mode, int(block_m), int(block_n),
+                                                  dtype_code(q.dtype), s), "tl_b200_flash_attn_fwd")
+
+
+def mla_decode_dense(q: torch.Tensor, q_pe: torch.Tensor, kv: torch.Tensor, k_pe: torch.Tensor, out: torch.Tensor,
+                     scale: float | None = None) -> int:
+    """Dense-cache MLA decode: q (B,H,1,D), q_pe (B,H,1,P), kv (B,S,1,D), k_pe (B,S,1,P), out (B,H,1,D)."""
+    if q.dim() != 4 or q.shape[2] != 1 or kv.dim() != 4 or kv.shape[2] != 1 or out.shape != q.shape:
+        raise ValueError("mla_decode_dense: expected q (B,H,1,D), kv (B,S,1,D), out like q")
+    b, h, _, d = q.shape
+    pe = q_pe.shape[-1]
+    if q_pe.shape != (b, h, 1, pe) or k_pe.shape != (b, kv.shape[1], 1, pe) or kv.shape[0] != b or kv.shape[3] != d:
+        raise ValueError("mla_decode_dense: inconsistent shapes")
+    if not (q.dtype == q_pe.dtype == kv.dtype == k_pe.dtype == out.dtype):
+        raise ValueError("mla_decode_dense: one dtype for all tensors")
+    if scale is None:
+        scale = (d + pe) ** -0.5
+    s = _prepare(q, q_pe, kv, k_pe, out)
+    return N.check(N.load().tl_b200_mla_decode_dense(_ptr(q), _ptr(q_pe), _ptr(kv), _ptr(k_pe), _ptr(out), b, h,
+                                                    kv.shape[1], d, pe, float(scale), dtype_code(q.dtype), s),
+                   "tl_b200_mla_decode_dense")
