@@ -132,6 +132,16 @@ int tl_b200_topk(const void* src, void* out_vals, int32_t* out_idx, int64_t rows
 int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
                  int in_dtype, int out_dtype, void* stream);
 
+/* ---- FP8 GEMM with 128-granular scales --------------------------------------------
+ * c[m,n] = sum_kb scales_a[m,kb] * scales_b[n/128,kb] * (a[m, kb*128:(kb+1)*128] . b[n, same]),
+ * a [m,k] and b [n,k] row-major e4m3, scales_a [m, k/128] and scales_b [ceil(n/128), k/128]
+ * fp32, every 128-wide partial product accumulated in fp32; c is TL_BF16 or TL_F32.
+ * Follows the block-scaled program examples/deepseek_deepgemm/example_deepgemm_fp8_2xAcc.py:14-83
+ * (quantisers :93-112).  k must be a multiple of 128.                                        */
+int tl_b200_gemm_fp8_blockscale(const void* a, const void* b, const float* scales_a,
+                                const float* scales_b, void* c, int64_t m, int64_t n, int64_t k,
+                                int out_dtype, void* stream);
+
 /* ---- FlashAttention forward -----------------------------------------------------
  * o = softmax(scale * q k^T + mask) v on bshd tensors: q, o [batch, seq_q, heads, dim];
  * k, v [batch, seq_kv, heads, dim]; fp32 softmax statistics; P is rounded to `dtype` before the
@@ -153,6 +163,26 @@ int tl_b200_flash_attn_fwd(const void* q, const void* k, const void* v, void* o,
 int tl_b200_mla_decode_dense(const void* q, const void* q_pe, const void* kv, const void* k_pe,
                              void* out, int64_t batch, int64_t heads, int64_t seq_kv, int64_t dim,
                              int64_t pe_dim, float scale, int dtype, void* stream);
+
+/* ---- MLA decode, paged cache ------------------------------------------------------
+ * One query token per sequence: out[b,h,:] = softmax(softmax_scale * q[b,h,:] . K_b^T) K_b[:, :dv]
+ * where K_b gathers the first cache_seqlens[b] tokens of sequence b through its page list
+ * block_table[b, 0:ceil(len/page_size)] from kv_cache [num_pages, page_size, d]; with an e4m3
+ * cache every token is multiplied by kv_scale[page, slot] (fp32).  q [batch, heads, d] and out
+ * [batch, heads, dv] are TL_BF16 or TL_F16; cache_dtype TL_E4M3 (kv_scale required), TL_F16 or
+ * TL_BF16 (kv_scale may be NULL).  Paging follows the reference's
+ * examples/deepseek_mla/example_mla_decode_paged.py:20-97 (block table, cache_seqlens, masked tail)
+ * with h_kv = 1; the FP8 cache with per-token scales is the benchmark's extension of it.
+ * The tensor-core path (e4m3, d 576, dv 512, heads <= 128, page_size % 64 == 0) needs a scratch
+ * buffer of tl_b200_mla_decode_paged_workspace_bytes(batch) bytes, 16-byte aligned, that it may
+ * overwrite (sequence ordering); other cases ignore it.                                       */
+int64_t tl_b200_mla_decode_paged_workspace_bytes(int64_t batch);
+int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, const float* kv_scale,
+                             const int32_t* block_table, const int32_t* cache_seqlens, void* out,
+                             int64_t batch, int64_t heads, int64_t d, int64_t dv, int64_t page_size,
+                             int64_t max_pages_per_seq, int64_t num_pages, float softmax_scale,
+                             int q_dtype, int cache_dtype, void* workspace, int64_t workspace_bytes,
+                             void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,116 @@
+"""Parity of paged MLA decode (tcgen05 FP8 kernel and FMA kernel) against the oracle."""
+import pytest
+import torch
+
+import oracle.ops as O
+from conftest import load_golden
+from tilelang import ops, workloads
+
+pytestmark = pytest.mark.gpu
+BF, HF, F8 = torch.bfloat16, torch.float16, torch.float8_e4m3fn
+
+
+def run(w, dev, heads=None):
+    q = w["q"].to(dev)
+    b, h = q.shape[0], q.shape[-2]
+    out = torch.full((b, h, w["dv"]), float("nan"), dtype=q.dtype, device=dev)
+    scale = w["kv_scale"].to(dev) if w["kv_scale"] is not None else None
+    assert ops.mla_decode_paged(q, w["kv_cache"].to(dev), scale, w["block_table"].to(dev),
+                                w["cache_seqlens"].to(dev), out, softmax_scale=w["softmax_scale"]) == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    return out.cpu()
+
+
+def oracle(w, rows=None):
+    q = w["q"].reshape(w["q"].shape[0], w["q"].shape[-2], w["q"].shape[-1])
+    sel = slice(None) if rows is None else rows
+    return O.mla_decode_paged(q[sel], w["kv_cache"], w["kv_scale"], w["block_table"][sel], w["cache_seqlens"][sel],
+                              w["dv"])
+
+
+# The tensor-core path cuts the query to e4m3 with one scale per head (FP8 attention): softmax
+# weights carry ~3% noise, i.e. ~2.5% error in norm and up to 4e-2 on the largest outputs.
+FP8_Q_TOL = 5e-2
+
+
+def assert_close(out, ref, rel_norm=0.05, tol=2e-2):
+    assert torch.allclose(out.float(), ref.float(), atol=tol, rtol=tol), (out.float() - ref.float()).abs().max()
+    # FP8 attention (query cut to e4m3 with one scale per head) is a few percent accurate in norm;
+    # random-data outputs are small, so the absolute tolerance alone would say little
+    err = (out.float() - ref.float()).norm() / ref.float().norm().clamp_min(1e-12)
+    assert err < rel_norm, f"relative error {err.item():.4f}"
+
+
+def test_golden_paged_fp16_cache(cuda_device):
+    g = load_golden("mla_paged_fp16", dict(q=HF, blocked_k=HF, ref=HF))
+    w = dict(q=g["q"], kv_cache=g["blocked_k"][:, :, 0].contiguous(), kv_scale=None, block_table=g["block_table"],
+             cache_seqlens=g["cache_seqlens"], dv=int(g["dv"]), softmax_scale=96 ** -0.5)
+    out = run(w, cuda_device)
+    assert torch.allclose(out.float(), g["ref"][:, 0].float(), atol=1e-2, rtol=1e-2)   # the example's tolerance
+
+
+@pytest.mark.parametrize("dtype", [BF, HF])
+def test_fma_kernel_small_fp8(cuda_device, dtype):
+    w = workloads.mla_fp8_paged(batch=3, heads=8, d=64, dv=32, page_size=16, min_len=1, max_len=100, seed=5, dtype=dtype)
+    assert_close(run(w, cuda_device), oracle(w), rel_norm=0.02)
+
+
+@pytest.mark.parametrize("heads,page,lens", [(128, 64, (1, 64, 65, 500, 1000, 2048)), (16, 64, (300, 77)),
+                                             (128, 128, (129, 1024, 640)), (100, 64, (2000,))])
+def test_tensor_core_kernel(cuda_device, heads, page, lens):
+    w = workloads.mla_fp8_paged(batch=len(lens), heads=heads, page_size=page, min_len=1, max_len=max(lens), seed=7)
+    w["cache_seqlens"] = torch.tensor(lens, dtype=torch.int32)
+    assert_close(run(w, cuda_device), oracle(w), tol=FP8_Q_TOL)
+
+
+def test_tensor_core_kernel_fp16_queries_and_empty_sequence(cuda_device):
+    w = workloads.mla_fp8_paged(batch=3, heads=128, min_len=100, max_len=700, seed=8, dtype=HF)
+    w["cache_seqlens"][1] = 0
+    out = run(w, cuda_device)
+    ref = oracle(w, rows=[0, 2])
+    assert_close(out[[0, 2]], ref, tol=FP8_Q_TOL)
+    assert (out[1] == 0).all()
+
+
+def test_peaked_attention_rows(cuda_device):
+    """A query aligned with one cached token: softmax is nearly one-hot, so the output must
+    reproduce that token's value row (checks the scale folding and the two-term P split)."""
+    w = workloads.mla_fp8_paged(batch=2, heads=128, min_len=300, max_len=400, seed=9)
+    cache, scale, table = w["kv_cache"], w["kv_scale"], w["block_table"]
+    for b, t in ((0, 17), (1, 250)):
+        page, slot = int(table[b, t // 64]), t % 64
+        k = cache[page, slot].float() * scale[page, slot]
+        w["q"][b, 0, :, :] = (k * 3.0).to(BF)
+    out = run(w, cuda_device)
+    assert_close(out, oracle(w), rel_norm=0.03)
+
+
+def test_run_to_run_determinism(cuda_device):
+    w = workloads.mla_fp8_paged(batch=4, heads=128, min_len=500, max_len=1500, seed=10)
+    a = run(w, cuda_device)
+    assert torch.equal(run(w, cuda_device).view(torch.int16), a.view(torch.int16))
+
+
+def test_benchmark_config(cuda_device):
+    """Batch 128, 128 heads, lengths uniform in [1024, 8192]: oracle on a sample of sequences and a
+    size-independent property on all (outputs lie inside the range of the de-quantised V rows)."""
+    w = workloads.mla_fp8_paged()
+    out = run(w, cuda_device)
+    assert torch.isfinite(out.float()).all()
+    rows = [0, 37, 127]
+    assert_close(out[rows], oracle(w, rows=rows))
+    vmax = (w["kv_cache"].float().abs().amax(dim=(1, 2)) * w["kv_scale"].amax(dim=1)).max()
+    assert out.float().abs().max() <= vmax
+
+
+def test_argument_errors(cuda_device):
+    w = workloads.mla_fp8_paged(batch=2, heads=8, d=64, dv=32, page_size=16, min_len=1, max_len=40, seed=1)
+    q = w["q"].to(cuda_device)
+    out = torch.zeros(2, 8, 32, dtype=BF, device=cuda_device)
+    with pytest.raises(ValueError, match="kv_scale"):
+        ops.mla_decode_paged(q, w["kv_cache"].to(cuda_device), None, w["block_table"].to(cuda_device),
+                             w["cache_seqlens"].to(cuda_device), out)
+    with pytest.raises(ValueError, match="int32"):
+        ops.mla_decode_paged(q, w["kv_cache"].to(cuda_device), w["kv_scale"].to(cuda_device),
+                             w["block_table"].to(cuda_device).long(), w["cache_seqlens"].to(cuda_device), out)

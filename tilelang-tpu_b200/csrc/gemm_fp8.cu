@@ -1,0 +1,265 @@
+// FP8 (e4m3) GEMM with 128-granular fp32 scales:
+//   C[m,n] = sum over 128-wide K blocks kb of  sa[m,kb] * sb[n/128,kb] * (A8[m,kb] . B8[n,kb])
+// A8 [M,K] row-major e4m3 with one scale per row per K block, B8 [N,K] row-major e4m3 with one
+// scale per 128x128 block, C bf16 or fp32.  Semantics of the block-scaled program
+// examples/deepseek_deepgemm/example_deepgemm_fp8_2xAcc.py:66-81: the tensor core produces an
+// fp32 partial product per K block, which is "promoted" into a separate fp32 accumulator with
+// the product of the two scales.
+//
+// Persistent warp-specialised kernel: TMA ring (6 stages of 128x128 A and B bytes, 128-byte
+// swizzle) -> tcgen05.mma kind::f8f6f4 into one of two partial accumulators in tensor memory ->
+// two epilogue warpgroups (64 columns each) pull the partial with tcgen05.ld and do the scaled
+// accumulation in registers while the tensor core already fills the other partial.
+#include "sm100.cuh"
+
+namespace tl {
+using namespace sm100;
+
+constexpr int kF8BM = 128, kF8BN = 128, kF8BK = 128;
+constexpr int kF8Stages = 6;
+constexpr int kF8Threads = 384;       // warp 0 TMA, warp 1 MMA, warp 2 TMEM alloc, warps 4-11 promotion/epilogue
+constexpr int kF8StageBytes = (kF8BM + kF8BN) * kF8BK;
+constexpr int kF8Smem = kF8Stages * kF8StageBytes + 1024 + 256;
+constexpr int kF8TmemCols = 2 * kF8BN;
+
+struct F8Params {
+  void* c;
+  const float* sa;      // [M, K/128]
+  const float* sb;      // [ceil(N/128), K/128]
+  int m, n, k, kblocks;
+  int tiles_m, tiles_n;
+  int* status;
+};
+
+template <typename TOut>
+__global__ void __launch_bounds__(kF8Threads, 1)
+gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                           const F8Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw_addr);
+  const uint32_t smem_a = base;
+  const uint32_t smem_b = base + kF8Stages * (kF8BM * kF8BK);
+  uint8_t* tail = base_ptr + kF8Stages * kF8StageBytes;
+  const uint32_t bar_full = smem_u32(tail);
+  const uint32_t bar_empty = bar_full + 8 * kF8Stages;
+  const uint32_t bar_tfull = bar_empty + 8 * kF8Stages;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kF8Stages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kF8Stages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 8);       // one arrival per promotion warp
+    }
+    mbar_fence_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(tmem_slot), kF8TmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // tiles walk 8 row-blocks per column-block so resident tiles share operands in L2
+  auto coords = [&](int tile, int& tm, int& tn) {
+    constexpr int G = 8;
+    const int per_group = G * p.tiles_n;
+    const int group = tile / per_group;
+    const int first_m = group * G;
+    const int rows = min(G, p.tiles_m - first_m);
+    const int in_group = tile - group * per_group;
+    tm = first_m + in_group % rows;
+    tn = in_group / rows;
+  };
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        int tm, tn;
+        coords(tile, tm, tn);
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag))) break;
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, kF8StageBytes);
+          tma_load_2d(smem_a + stage * (kF8BM * kF8BK), &tm_a, full, kb * kF8BK, tm * kF8BM);
+          tma_load_2d(smem_b + stage * (kF8BN * kF8BK), &tm_b, full, kb * kF8BK, tn * kF8BN);
+          if (++stage == kF8Stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc(kFmtE4M3, kFmtE4M3, false, false, kF8BM, kF8BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t it = 0;                       // K blocks issued so far: selects the partial accumulator
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const uint32_t buf = it & 1;
+          if (!(ok = mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag))) break;
+          if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag))) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_a + stage * (kF8BM * kF8BK);
+          const uint32_t b_addr = smem_b + stage * (kF8BN * kF8BK);
+#pragma unroll
+          for (int kk = 0; kk < kF8BK / 32; ++kk) {      // K = 32 per instruction for 8-bit operands
+            const uint64_t a_desc = smem_desc_sw128(a_addr + kk * 32, 16, 1024);
+            const uint64_t b_desc = smem_desc_sw128(b_addr + kk * 32, 16, 1024);
+            mma_f8_ss(tmem_base + buf * kF8BN, a_desc, b_desc, idesc, kk ? 1u : 0u);
+          }
+          mma_commit(bar_empty + 8 * stage);
+          mma_commit(bar_tfull + 8 * buf);
+          if (++stage == kF8Stages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp >= 4) {
+    const int wg = (warp - 4) / 4;            // column half
+    const int quarter = warp % 4;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    TOut* c = reinterpret_cast<TOut*>(p.c);
+    const bool vec_ok = ((int64_t)p.n * sizeof(TOut)) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.c) & 15u) == 0;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      int tm, tn;
+      coords(tile, tm, tn);
+      const int row = tm * kF8BM + r;
+      const float* sa_row = p.sa + (int64_t)(row < p.m ? row : 0) * p.kblocks;
+      const float* sb_row = p.sb + (int64_t)tn * p.kblocks;
+      float acc[64];
+#pragma unroll
+      for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+      float scale_next = __ldg(sa_row) * __ldg(sb_row);
+      for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+        const uint32_t buf = it & 1;
+        const float scale = scale_next;
+        if (kb + 1 < p.kblocks) scale_next = __ldg(sa_row + kb + 1) * __ldg(sb_row + kb + 1);
+        ok = mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+        const uint32_t t_addr = tmem_base + buf * kF8BN + wg * 64 + lane_off;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_addr + h * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[h * 32 + j] = fmaf(__uint_as_float(v[j]), scale, acc[h * 32 + j]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+      }
+      if (!ok) break;
+      const int col0 = tn * kF8BN + wg * 64;
+      if (row < p.m && col0 < p.n) {
+        TOut* dst = c + (int64_t)row * p.n + col0;
+        const int valid = min(64, p.n - col0);
+        if (vec_ok && valid == 64) {
+          if constexpr (sizeof(TOut) == 4) {
+#pragma unroll
+            for (int j = 0; j < 64; j += 4)
+              *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 64; j += 8) {
+              Vec16<TOut> o;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o.e[e] = from_f32<TOut>(acc[j + e]);
+              *reinterpret_cast<uint4*>(dst + j) = o.raw;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 64; ++j)
+            if (j < valid) dst[j] = from_f32<TOut>(acc[j]);
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    if (threadIdx.x == 0 && p.status) *p.status = *abort_flag;
+    __syncthreads();
+  }
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kF8TmemCols);
+  }
+}
+
+template <typename TOut>
+static int launch_f8(const CUtensorMap& ta, const CUtensorMap& tb, const F8Params& p, cudaStream_t s) {
+  auto kernel = gemm_fp8_blockscale_kernel<TOut>;
+  TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kF8Smem));
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  kernel<<<grid, kF8Threads, kF8Smem, s>>>(ta, tb, p);
+  TL_LAUNCH_CHECK("gemm_fp8_blockscale_kernel");
+  return TL_B200_OK;
+}
+
+}  // namespace tl
+
+using namespace tl;
+
+extern "C" int tl_b200_gemm_fp8_blockscale(const void* a, const void* b, const float* scales_a, const float* scales_b,
+                                           void* c, int64_t m, int64_t n, int64_t k, int out_dtype, void* stream) {
+  TL_REQUIRE(m >= 0 && n >= 0 && k >= 0, "gemm_fp8_blockscale: negative size");
+  TL_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), "gemm_fp8_blockscale: dimension exceeds 2^31");
+  if (m == 0 || n == 0) return TL_B200_OK;
+  TL_REQUIRE(a && b && c && scales_a && scales_b, "gemm_fp8_blockscale: null tensor pointer");
+  TL_REQUIRE(k > 0 && k % 128 == 0, "gemm_fp8_blockscale: K (%lld) must be a positive multiple of 128 (one scale "
+                                    "per 128-wide K block)", (long long)k);
+  TL_REQUIRE(out_dtype == TL_BF16 || out_dtype == TL_F32, "gemm_fp8_blockscale: output must be bfloat16 or float32");
+  TL_REQUIRE(aligned16(a) && aligned16(b), "gemm_fp8_blockscale: A and B must be 16-byte aligned");
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[2] = {(uint64_t)k, (uint64_t)m};
+    uint64_t strides[1] = {(uint64_t)k};
+    uint32_t box[2] = {(uint32_t)kF8BK, (uint32_t)kF8BM};
+    int rc = make_tensor_map(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)k, (uint64_t)n};
+    uint64_t strides[1] = {(uint64_t)k};
+    uint32_t box[2] = {(uint32_t)kF8BK, (uint32_t)kF8BN};
+    int rc = make_tensor_map(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+  }
+  F8Params p;
+  p.c = c; p.sa = scales_a; p.sb = scales_b;
+  p.m = (int)m; p.n = (int)n; p.k = (int)k; p.kblocks = (int)(k / 128);
+  p.tiles_m = (int)((m + kF8BM - 1) / kF8BM);
+  p.tiles_n = (int)((n + kF8BN - 1) / kF8BN);
+  p.status = device_status_word();
+  cudaStream_t s = (cudaStream_t)stream;
+  if (out_dtype == TL_F32) return launch_f8<float>(ta, tb, p, s);
+  return launch_f8<__nv_bfloat16>(ta, tb, p, s);
+}

@@ -1,0 +1,507 @@
+// MLA decode (one query token per sequence) over a PAGED latent KV cache.
+//
+//   scores[h,t] = softmax_scale * q[h,:] . K[t,:]        K[t,:] = cache[t,:] (* scale[t] for FP8)
+//   out[h,:]    = softmax(scores)[h,:] . K[:, :dv]        (V is the first dv columns of the latent)
+//
+// Paged semantics follow examples/deepseek_mla/example_mla_decode_paged.py:20-97,259-308 of the
+// reference (block table int32 [batch, max_pages], cache_seqlens int32 [batch], tail tokens of the
+// last page masked); the FP8 cache with one fp32 scale per token is the benchmark's extension.
+//
+// tcgen05 kernel (e4m3 cache, d = 576, dv = 512, <= 128 heads, page size a multiple of 64).  The
+// cache bytes are used by the tensor core exactly as they sit in HBM: TMA drops each 64-token
+// page slice into shared memory (128-byte swizzle, 128-column slabs) and the SAME image is the
+// K-major operand of S = Q K^T and the MN-major operand of O += P V, so nothing is ever
+// de-quantised elementwise.  The per-token scale multiplies the S columns after the first MMA
+// and the P columns before the second.  Q is quantised once per CTA to e4m3 with one scale per
+// head; P is split into two e4m3 terms (value + residual) so the second product keeps ~8
+// mantissa bits.  The fp32 O accumulator for 128 heads x 512 columns alone would fill tensor
+// memory, so two CTAs share a sequence, each owning 256 output columns (S is computed by both).
+// Sequences are ordered longest-first by a small pre-kernel (scratch: one int32 per sequence).
+//
+// Other shapes / cache dtypes run a one-thread-per-(sequence, head) FMA kernel.
+#include "sm100.cuh"
+
+#include <type_traits>
+
+namespace tl {
+using namespace sm100;
+
+constexpr int kMlaD = 576, kMlaDV = 512, kMlaHeads = 128, kMlaBN = 64;
+constexpr int kMlaSlabs = 5;                     // 128-byte column slabs per token row (last one half used)
+constexpr int kMlaStages = 3;
+constexpr int kMlaTile = kMlaSlabs * kMlaBN * 128;          // 40 KB of cache bytes per stage
+constexpr int kMlaStageBytes = kMlaTile + kMlaBN * 4;       // + 64 token scales
+constexpr int kMlaQBytes = kMlaSlabs * kMlaHeads * 128;     // 80 KB of quantised Q
+constexpr int kMlaPBytes = kMlaHeads * 128;                 // 16 KB: [P_hi | P_lo] rows of 128 bytes
+constexpr int kMlaOffKV = kMlaQBytes;
+constexpr int kMlaOffP = kMlaOffKV + kMlaStages * (kMlaTile + 1024);   // scale area padded to 1 KB
+constexpr int kMlaOffBar = kMlaOffP + kMlaPBytes;
+constexpr int kMlaSmem = kMlaOffBar + 1024 + 1024;
+constexpr int kMlaThreads = 256;                 // warp 0 TMA, warp 1 MMA, warp 2 TMEM alloc, warps 4-7 softmax
+constexpr int kMlaTmemCols = 512;
+constexpr int kMlaColS = 0, kMlaColO = 128;
+
+struct MlaParams {
+  const void* q;               // [batch, heads, 576]
+  const float* kv_scale;       // [num_pages * page_size]
+  const int* block_table;      // [batch, max_pages]
+  const int* seqlens;          // [batch]
+  const int* order;            // [batch] sequence ids, longest first
+  void* out;                   // [batch, heads, 512]
+  int batch, heads, page_size, max_pages;
+  float scale_log2;
+  int* status;
+};
+
+__global__ void mla_order_kernel(const int* __restrict__ seqlens, int* __restrict__ order, int batch) {
+  for (int b = blockIdx.x * blockDim.x + threadIdx.x; b < batch; b += gridDim.x * blockDim.x) {
+    const int len = seqlens[b];
+    int rank = 0;
+    for (int o = 0; o < batch; ++o) {
+      const int lo = seqlens[o];
+      rank += (lo > len) || (lo == len && o < b);
+    }
+    order[rank] = b;
+  }
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t v) {
+  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v & 0xffffu), __NV_E4M3);
+  return __half22float2(*reinterpret_cast<__half2*>(&h));
+}
+
+template <typename TQ>
+__global__ void __launch_bounds__(kMlaThreads, 1)
+mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw_addr);
+  const uint32_t sm_q = base;
+  const uint32_t sm_kv = base + kMlaOffKV;                   // stage s at s * (tile + 1 KB)
+  const uint32_t sm_p = base + kMlaOffP;
+  const uint32_t bar0 = base + kMlaOffBar;
+  const uint32_t bar_kvfull = bar0;                          // [stages]
+  const uint32_t bar_kvempty = bar0 + 8 * kMlaStages;
+  const uint32_t bar_sfull = bar_kvempty + 8 * kMlaStages;   // [2]
+  const uint32_t bar_pfull = bar_sfull + 16;
+  const uint32_t bar_pvdone = bar_pfull + 8;
+  const uint32_t bar_qready = bar_pvdone + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kMlaOffBar + 8 * (2 * kMlaStages + 5));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* red = reinterpret_cast<float*>(base_ptr + kMlaOffBar + 256);       // 4 floats for the scale max
+
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int item = blockIdx.x;
+  const int b = p.order[item >> 1];
+  const int half = item & 1;
+  const int seqlen = max(p.seqlens[b], 0);
+  const int n_tiles = (seqlen + kMlaBN - 1) / kMlaBN;
+  const int* table = p.block_table + (int64_t)b * p.max_pages;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kMlaStages; ++s) {
+      mbar_init(bar_kvfull + 8 * s, 1);
+      mbar_init(bar_kvempty + 8 * s, 1);
+    }
+    mbar_init(bar_sfull, 1);
+    mbar_init(bar_sfull + 8, 1);
+    mbar_init(bar_pfull, kMlaHeads);
+    mbar_init(bar_pvdone, 1);
+    mbar_init(bar_qready, kMlaHeads);
+    mbar_fence_init();
+    prefetch_tensormap(&tm_kv);
+  }
+  if (warp == 2) {
+    tmem_alloc(smem_u32(tmem_slot), kMlaTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto stage_addr = [&](int s) { return sm_kv + s * (kMlaTile + 1024); };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j % kMlaStages;
+        const uint32_t ph = (j / kMlaStages) & 1;
+        if (!(ok = mbar_wait(bar_kvempty + 8 * st, ph ^ 1, abort_flag))) break;
+        const int tok = j * kMlaBN;
+        const int page = __ldg(table + tok / p.page_size);
+        const int row = page * p.page_size + tok % p.page_size;      // row of the flattened cache
+        const uint32_t full = bar_kvfull + 8 * st;
+        mbar_expect_tx(full, kMlaStageBytes);
+#pragma unroll
+        for (int s = 0; s < kMlaSlabs; ++s)           // columns 576..639 of the last slab are out of range: zero fill
+          tma_load_2d(stage_addr(st) + s * (kMlaBN * 128), &tm_kv, full, s * 128, row);
+        bulk_load(stage_addr(st) + kMlaTile, p.kv_scale + row, kMlaBN * 4, full);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one() && n_tiles > 0) {
+      const uint32_t idesc_s = make_idesc(kFmtE4M3, kFmtE4M3, false, false, kMlaHeads, kMlaBN);
+      const uint32_t idesc_o = make_idesc(kFmtE4M3, kFmtE4M3, false, true, kMlaHeads, 256);
+      auto issue_s = [&](int j) {
+        const uint32_t kv = stage_addr(j % kMlaStages);
+        const uint32_t d = tmem_base + kMlaColS + (j & 1) * kMlaBN;
+#pragma unroll
+        for (int kk = 0; kk < kMlaD / 32; ++kk) {
+          const uint64_t a = smem_desc_sw128(sm_q + (kk / 4) * (kMlaHeads * 128) + (kk % 4) * 32, 16, 1024);
+          const uint64_t bd = smem_desc_sw128(kv + (kk / 4) * (kMlaBN * 128) + (kk % 4) * 32, 16, 1024);
+          mma_f8_ss(d, a, bd, idesc_s, kk ? 1u : 0u);
+        }
+        mma_commit(bar_sfull + 8 * (j & 1));
+      };
+      bool ok = mbar_wait(bar_qready, 0, abort_flag);
+      if (ok) ok = mbar_wait(bar_kvfull, 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_s(0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          const int st1 = (j + 1) % kMlaStages;
+          if (!(ok = mbar_wait(bar_kvfull + 8 * st1, ((j + 1) / kMlaStages) & 1, abort_flag))) break;
+          tc_fence_after_sync();
+          issue_s(j + 1);
+        }
+        if (!(ok = mbar_wait(bar_pfull, j & 1, abort_flag))) break;
+        tc_fence_after_sync();
+        const uint32_t kv = stage_addr(j % kMlaStages);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          // A: P row = [hi(64 tokens) | lo(64 tokens)], 32 bytes per step.  B: this half's 256 V
+          // columns = two 128-column slabs (8 KB apart), 32 tokens = 4 KB per step; the lo terms
+          // reuse the same tokens.
+          const uint64_t a = smem_desc_sw128(sm_p + kk * 32, 16, 1024);
+          const uint64_t bd = smem_desc_sw128(kv + (2 * half) * (kMlaBN * 128) + (kk & 1) * 4096, kMlaBN * 128, 1024);
+          mma_f8_ss(tmem_base + kMlaColO, a, bd, idesc_o, (j | kk) ? 1u : 0u);
+        }
+        mma_commit(bar_pvdone);
+        mma_commit(bar_kvempty + 8 * (j % kMlaStages));
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ Q quantisation, softmax, epilogue
+    const int quarter = warp % 4;
+    const int h = quarter * 32 + lane;            // head = TMEM lane
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    // (1) quantise this head's query row to e4m3 with one scale
+    float q_scale = 1.f;
+    {
+      const TQ* qrow = reinterpret_cast<const TQ*>(p.q) + ((int64_t)b * p.heads + h) * kMlaD;
+      float amax = 0.f;
+      if (h < p.heads)
+        for (int c = 0; c < kMlaD / 8; ++c) {
+          Vec16<TQ> v;
+          v.raw = __ldg(reinterpret_cast<const uint4*>(qrow) + c);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(to_f32(v.e[e])));
+        }
+      amax = fmaxf(amax, 1e-10f);
+      q_scale = amax / 448.0f;
+      const float inv = 448.0f / amax;
+      for (int c16 = 0; c16 < kMlaSlabs * 8; ++c16) {        // 16-byte chunks of the 640-byte padded row
+        uint32_t w[4] = {0, 0, 0, 0};
+        if (h < p.heads && c16 * 16 < kMlaD) {
+          Vec16<TQ> v0, v1;
+          v0.raw = __ldg(reinterpret_cast<const uint4*>(qrow) + 2 * c16);
+          v1.raw = __ldg(reinterpret_cast<const uint4*>(qrow) + 2 * c16 + 1);
+          w[0] = pack_e4m3x4(to_f32(v0.e[0]) * inv, to_f32(v0.e[1]) * inv, to_f32(v0.e[2]) * inv, to_f32(v0.e[3]) * inv);
+          w[1] = pack_e4m3x4(to_f32(v0.e[4]) * inv, to_f32(v0.e[5]) * inv, to_f32(v0.e[6]) * inv, to_f32(v0.e[7]) * inv);
+          w[2] = pack_e4m3x4(to_f32(v1.e[0]) * inv, to_f32(v1.e[1]) * inv, to_f32(v1.e[2]) * inv, to_f32(v1.e[3]) * inv);
+          w[3] = pack_e4m3x4(to_f32(v1.e[4]) * inv, to_f32(v1.e[5]) * inv, to_f32(v1.e[6]) * inv, to_f32(v1.e[7]) * inv);
+        }
+        const int slab = c16 / 8, c = c16 % 8;
+        st_shared_v4(sm_q + slab * (kMlaHeads * 128) + h * 128 + ((c ^ (h & 7)) << 4), w[0], w[1], w[2], w[3]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(bar_qready);
+    }
+    // (2) largest token scale of the sequence: P is multiplied by 128 * scale[t] / max_scale before
+    //     it is cut to e4m3, which keeps it inside (0, 256]
+    float max_ts = 0.f;
+    for (int t = threadIdx.x - 128; t < seqlen; t += kMlaHeads) {
+      const int page = __ldg(table + t / p.page_size);
+      max_ts = fmaxf(max_ts, __ldg(p.kv_scale + (int64_t)page * p.page_size + t % p.page_size));
+    }
+    max_ts = warp_max(max_ts);
+    if (lane == 0) red[quarter] = max_ts;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    max_ts = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    constexpr float kPScale = 128.0f;
+    const float ts_norm = max_ts > 0.f ? kPScale / max_ts : kPScale;
+    const float s_scale = q_scale * p.scale_log2;
+
+    // (3) online softmax, one row per thread
+    float m_used = -INFINITY, row_sum = 0.f;
+    const uint32_t p_row = sm_p + h * 128;
+    const uint32_t t_o = tmem_base + kMlaColO + lane_off;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = mbar_wait(bar_sfull + 8 * (j & 1), (j >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      uint32_t sv[64];
+      tmem_ld_32x64(tmem_base + kMlaColS + (j & 1) * kMlaBN + lane_off, sv);
+      tmem_ld_wait();
+      const float* ts = reinterpret_cast<const float*>(base_ptr + (stage_addr(j % kMlaStages) - base) + kMlaTile);
+      const int valid = seqlen - j * kMlaBN;          // tokens of this tile that exist
+      float m_tile = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 64; ++c) {
+        float s = __uint_as_float(sv[c]) * (s_scale * ts[c]);
+        s = (c < valid) ? s : -INFINITY;
+        sv[c] = __float_as_uint(s);
+        m_tile = fmaxf(m_tile, s);
+      }
+      const float m_new = fmaxf(m_used, m_tile);
+      if (j > 0) {
+        ok = mbar_wait(bar_pvdone, (j - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after_sync();
+      }
+      // e4m3 has little dynamic range (smallest normal 2^-6), so P is kept in (0, 2] - the running
+      // maximum may lag by at most one binade - and scaled by kPScale = 128 before it is cut to e4m3
+      const bool grow = (j == 0) || (m_new - m_used > 1.0f);
+      if (j > 0 && __any_sync(0xffffffffu, grow && m_used != -INFINITY)) {
+        const float alpha = (grow && m_used != -INFINITY) ? ex2_approx(m_used - m_new) : 1.0f;
+        row_sum *= alpha;
+#pragma unroll 1
+        for (int c = 0; c < 256 / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld_32x32(t_o + c * 32, ov);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * alpha);
+          tmem_st_32x32(t_o + c * 32, ov);
+        }
+        tmem_st_wait();
+      }
+      if (grow) m_used = m_new;
+      const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+      float tile_sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 64; c += 16) {
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 16; e += 4) {
+          float w[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float pr = ex2_approx(__uint_as_float(sv[c + e + i]) - m_safe);
+            tile_sum += pr;
+            w[i] = pr * (ts[c + e + i] * ts_norm);
+          }
+          const uint32_t hq = pack_e4m3x4(w[0], w[1], w[2], w[3]);
+          const float2 h01 = e4m3x2_to_float2(hq), h23 = e4m3x2_to_float2(hq >> 16);
+          hi[e / 4] = hq;
+          lo[e / 4] = pack_e4m3x4(w[0] - h01.x, w[1] - h01.y, w[2] - h23.x, w[3] - h23.y);
+        }
+        const int chunk = c / 16;                                // 16 tokens = one 16-byte chunk
+        st_shared_v4(p_row + ((chunk ^ (h & 7)) << 4), hi[0], hi[1], hi[2], hi[3]);
+        st_shared_v4(p_row + (((chunk + 4) ^ (h & 7)) << 4), lo[0], lo[1], lo[2], lo[3]);
+      }
+      row_sum += tile_sum;
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(bar_pfull);
+    }
+    // (4) epilogue
+    TQ* out = reinterpret_cast<TQ*>(p.out) + ((int64_t)b * p.heads + h) * kMlaDV + half * 256;
+    if (n_tiles == 0) {
+      if (h < p.heads)
+        for (int c = 0; c < 256 / 8; ++c) reinterpret_cast<uint4*>(out)[c] = make_uint4(0, 0, 0, 0);
+    } else if (ok) {
+      ok = mbar_wait(bar_pvdone, (n_tiles - 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (ok) {
+        tc_fence_after_sync();
+        const float inv = row_sum > 0.f ? max_ts / (kPScale * row_sum) : 0.f;     // undo the P normalisation
+#pragma unroll 1
+        for (int c = 0; c < 256 / 32; ++c) {
+          uint32_t ov[32];
+          tmem_ld_32x32(t_o + c * 32, ov);
+          tmem_ld_wait();
+          if (h < p.heads) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              Vec16<TQ> v;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v.e[i] = from_f32<TQ>(__uint_as_float(ov[e + i]) * inv);
+              *reinterpret_cast<uint4*>(out + c * 32 + e) = v.raw;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    if (threadIdx.x == 0 && p.status) *p.status = *abort_flag;
+    __syncthreads();
+  }
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kMlaTmemCols);
+  }
+}
+
+// =================================================================================
+// FMA kernel: one thread per (sequence, head); any d / dv <= 512, any page size, cache in
+// e4m3 (+ per-token scale), fp16 or bf16.
+// =================================================================================
+template <typename T> __device__ __forceinline__ float cache_f32(const T* p) { return to_f32(*p); }
+template <> __device__ __forceinline__ float cache_f32<__nv_fp8_e4m3>(const __nv_fp8_e4m3* p) { return float(*p); }
+
+struct MlaRowParams {
+  const void *q, *cache;
+  const float* kv_scale;
+  const int *block_table, *seqlens;
+  void* out;
+  int batch, heads, d, dv, page_size, max_pages;
+  float scale;
+};
+
+template <typename TQ, typename TC, int MAXDV>
+__global__ void __launch_bounds__(128)
+mla_rows_kernel(const MlaRowParams p) {
+  const int idx = blockIdx.x * 128 + threadIdx.x;
+  if (idx >= p.batch * p.heads) return;
+  const int b = idx / p.heads, h = idx % p.heads;
+  const TQ* q = (const TQ*)p.q + (int64_t)idx * p.d;
+  const int* table = p.block_table + (int64_t)b * p.max_pages;
+  const int seqlen = p.seqlens[b];
+  float acc[MAXDV];
+#pragma unroll
+  for (int i = 0; i < MAXDV; ++i) acc[i] = 0.f;
+  float m = -INFINITY, l = 0.f;
+  for (int t = 0; t < seqlen; ++t) {
+    const int64_t row = (int64_t)table[t / p.page_size] * p.page_size + t % p.page_size;
+    const TC* kr = (const TC*)p.cache + row * p.d;
+    const float ts = p.kv_scale ? p.kv_scale[row] : 1.f;
+    float s = 0.f;
+    for (int i = 0; i < p.d; ++i) s = fmaf(to_f32(q[i]), cache_f32<TC>(kr + i), s);
+    s *= ts * p.scale;
+    const float m_new = fmaxf(m, s);
+    const float alpha = (m == -INFINITY) ? 0.f : expf(m - m_new);
+    const float pj = expf(s - m_new);
+    l = l * alpha + pj;
+    const float w = pj * ts;
+#pragma unroll
+    for (int i = 0; i < MAXDV; ++i)
+      if (i < p.dv) acc[i] = fmaf(w, cache_f32<TC>(kr + i), acc[i] * alpha);
+    m = m_new;
+  }
+  TQ* out = (TQ*)p.out + (int64_t)idx * p.dv;
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXDV; ++i)
+    if (i < p.dv) out[i] = from_f32<TQ>(acc[i] * inv);
+}
+
+template <typename TQ, typename TC>
+static int launch_mla_rows(const MlaRowParams& p, cudaStream_t s) {
+  const unsigned grid = (unsigned)((p.batch * p.heads + 127) / 128);
+  if (p.dv <= 64) mla_rows_kernel<TQ, TC, 64><<<grid, 128, 0, s>>>(p);
+  else mla_rows_kernel<TQ, TC, 512><<<grid, 128, 0, s>>>(p);
+  TL_LAUNCH_CHECK("mla_rows_kernel");
+  return TL_B200_OK;
+}
+
+template <typename TQ>
+static int launch_mla_rows_cache(const MlaRowParams& p, int cache_dtype, cudaStream_t s) {
+  switch (cache_dtype) {
+    case TL_E4M3: return launch_mla_rows<TQ, __nv_fp8_e4m3>(p, s);
+    case TL_F16: return launch_mla_rows<TQ, __half>(p, s);
+    case TL_BF16: return launch_mla_rows<TQ, __nv_bfloat16>(p, s);
+    default: return fail(TL_B200_EINVAL, "mla_decode_paged: unsupported cache dtype %d", cache_dtype);
+  }
+}
+
+}  // namespace tl
+
+using namespace tl;
+
+extern "C" int64_t tl_b200_mla_decode_paged_workspace_bytes(int64_t batch) {
+  return batch > 0 ? ((batch * 4 + 255) / 256) * 256 : 0;
+}
+
+extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, const float* kv_scale,
+                                        const int32_t* block_table, const int32_t* cache_seqlens, void* out,
+                                        int64_t batch, int64_t heads, int64_t d, int64_t dv, int64_t page_size,
+                                        int64_t max_pages_per_seq, int64_t num_pages, float softmax_scale, int q_dtype,
+                                        int cache_dtype, void* workspace, int64_t workspace_bytes, void* stream) {
+  TL_REQUIRE(batch >= 0 && heads >= 0 && d > 0 && dv > 0 && page_size > 0 && max_pages_per_seq >= 0 && num_pages >= 0,
+             "mla_decode_paged: bad size");
+  TL_REQUIRE(dv <= d, "mla_decode_paged: dv (%lld) exceeds d (%lld)", (long long)dv, (long long)d);
+  if (batch == 0 || heads == 0) return TL_B200_OK;
+  TL_REQUIRE(q && kv_cache && block_table && cache_seqlens && out, "mla_decode_paged: null tensor pointer");
+  TL_REQUIRE(q_dtype == TL_BF16 || q_dtype == TL_F16, "mla_decode_paged: q/out must be bfloat16 or float16");
+  TL_REQUIRE(cache_dtype != TL_E4M3 || kv_scale, "mla_decode_paged: an e4m3 cache needs per-token scales");
+  TL_REQUIRE(batch < (1 << 24) && num_pages * page_size < (1ll << 31), "mla_decode_paged: size too large");
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool tc = cache_dtype == TL_E4M3 && d == kMlaD && dv == kMlaDV && heads <= kMlaHeads && page_size % kMlaBN == 0 &&
+                  aligned16(q) && aligned16(out) && aligned16(kv_cache) && aligned16(kv_scale);
+  if (tc) {
+    TL_REQUIRE(workspace && workspace_bytes >= tl_b200_mla_decode_paged_workspace_bytes(batch),
+               "mla_decode_paged: workspace of %lld bytes required (tl_b200_mla_decode_paged_workspace_bytes)",
+               (long long)tl_b200_mla_decode_paged_workspace_bytes(batch));
+    CUtensorMap tm;
+    uint64_t dims[2] = {(uint64_t)kMlaD, (uint64_t)(num_pages * page_size)};
+    uint64_t strides[1] = {(uint64_t)kMlaD};
+    uint32_t box[2] = {128u, (uint32_t)kMlaBN};
+    int rc = make_tensor_map(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, kv_cache, dims, strides, box,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    int* order = reinterpret_cast<int*>(workspace);
+    mla_order_kernel<<<(unsigned)((batch + 255) / 256), 256, 0, s>>>(cache_seqlens, order, (int)batch);
+    TL_LAUNCH_CHECK("mla_order_kernel");
+    MlaParams p;
+    p.q = q; p.kv_scale = kv_scale; p.block_table = block_table; p.seqlens = cache_seqlens; p.order = order; p.out = out;
+    p.batch = (int)batch; p.heads = (int)heads; p.page_size = (int)page_size; p.max_pages = (int)max_pages_per_seq;
+    p.scale_log2 = softmax_scale * 1.4426950408889634f;
+    p.status = device_status_word();
+    if (q_dtype == TL_BF16) {
+      auto kernel = mla_decode_fp8_kernel<__nv_bfloat16>;
+      TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
+      kernel<<<(unsigned)(2 * batch), kMlaThreads, kMlaSmem, s>>>(tm, p);
+    } else {
+      auto kernel = mla_decode_fp8_kernel<__half>;
+      TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
+      kernel<<<(unsigned)(2 * batch), kMlaThreads, kMlaSmem, s>>>(tm, p);
+    }
+    TL_LAUNCH_CHECK("mla_decode_fp8_kernel");
+    return TL_B200_OK;
+  }
+  TL_REQUIRE(dv <= 512, "mla_decode_paged: dv above 512 is not supported");
+  MlaRowParams rp;
+  rp.q = q; rp.cache = kv_cache; rp.kv_scale = kv_scale; rp.block_table = block_table; rp.seqlens = cache_seqlens;
+  rp.out = out; rp.batch = (int)batch; rp.heads = (int)heads; rp.d = (int)d; rp.dv = (int)dv;
+  rp.page_size = (int)page_size; rp.max_pages = (int)max_pages_per_seq; rp.scale = softmax_scale;
+  if (q_dtype == TL_BF16) return launch_mla_rows_cache<__nv_bfloat16>(rp, cache_dtype, s);
+  return launch_mla_rows_cache<__half>(rp, cache_dtype, s);
+}

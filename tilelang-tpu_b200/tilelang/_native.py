@@ -32,10 +32,16 @@ PROTOTYPES = {
     "tl_b200_binary": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_float, c_int, c_void_p]),
     "tl_b200_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "tl_b200_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_int64, c_int, c_void_p]),
+    "tl_b200_gemm_fp8_blockscale": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                            c_int64, c_int, c_void_p]),
     "tl_b200_flash_attn_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                        c_int64, c_float, c_int, c_int, c_int, c_int, c_void_p]),
     "tl_b200_mla_decode_dense": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                          c_int64, c_int64, c_int64, c_float, c_int, c_void_p]),
+    "tl_b200_mla_decode_paged_workspace_bytes": (c_int64, [c_int64]),
+    "tl_b200_mla_decode_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                         c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_void_p,
+                                         c_int64, c_void_p]),
     "tl_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
 }
 

@@ -246,3 +246,71 @@ def mla_decode_dense(q: torch.Tensor, q_pe: torch.Tensor, kv: torch.Tensor, k_pe
     return N.check(N.load().tl_b200_mla_decode_dense(_ptr(q), _ptr(q_pe), _ptr(kv), _ptr(k_pe), _ptr(out), b, h,
                                                     kv.shape[1], d, pe, float(scale), dtype_code(q.dtype), s),
                    "tl_b200_mla_decode_dense")
+
+
+def gemm_fp8_blockscale(a8: torch.Tensor, b8: torch.Tensor, scales_a: torch.Tensor, scales_b: torch.Tensor,
+                        c: torch.Tensor) -> int:
+    """c = (a8 * scales_a) @ (b8 * scales_b)^T with 128-granular fp32 scales: a8 (M,K) e4m3 with
+    scales_a (M, K/128); b8 (N,K) e4m3 with scales_b (ceil(N/128), K/128); c (M,N) bf16 or fp32."""
+    f8 = torch.float8_e4m3fn
+    if a8.dtype != f8 or b8.dtype != f8 or a8.dim() != 2 or b8.dim() != 2 or a8.shape[1] != b8.shape[1]:
+        raise ValueError("gemm_fp8_blockscale: a8 (M,K) and b8 (N,K) must be e4m3 with equal K")
+    m, k = a8.shape
+    n = b8.shape[0]
+    if k % 128 != 0:
+        raise ValueError("gemm_fp8_blockscale: K must be a multiple of 128")
+    if tuple(scales_a.shape) != (m, k // 128) or tuple(scales_b.shape) != (-(-n // 128), k // 128) \
+            or scales_a.dtype != torch.float32 or scales_b.dtype != torch.float32:
+        raise ValueError("gemm_fp8_blockscale: scales_a must be (M, K/128) and scales_b (ceil(N/128), K/128), fp32")
+    if tuple(c.shape) != (m, n) or c.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("gemm_fp8_blockscale: c must be (M, N) bfloat16 or float32")
+    s = _prepare(a8, b8, scales_a, scales_b, c)
+    return N.check(N.load().tl_b200_gemm_fp8_blockscale(_ptr(a8), _ptr(b8), _ptr(scales_a), _ptr(scales_b), _ptr(c),
+                                                       m, n, k, dtype_code(c.dtype), s),
+                   "tl_b200_gemm_fp8_blockscale")
+
+
+_workspaces: dict = {}
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Scratch owned by this module, one growing buffer per device (the library never allocates)."""
+    buf = _workspaces.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 4096), dtype=torch.uint8, device=device)
+        _workspaces[device] = buf
+    return buf
+
+
+def mla_decode_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torch.Tensor | None, block_table: torch.Tensor,
+                     cache_seqlens: torch.Tensor, out: torch.Tensor, dv: int | None = None,
+                     softmax_scale: float | None = None) -> int:
+    """Paged MLA decode.  q (B, H, D) or (B, 1, H, D); kv_cache (num_pages, page, D) or
+    (num_pages, page, 1, D) in e4m3 / fp16 / bf16; kv_scale (num_pages, page) fp32 for e4m3;
+    block_table (B, max_pages) int32; cache_seqlens (B,) int32; out (B, H, DV) or (B, 1, H, DV)."""
+    b, h, d = q.shape[0], q.shape[-2], q.shape[-1]
+    if q.numel() != b * h * d or kv_cache.shape[-1] != d:
+        raise ValueError("mla_decode_paged: q must hold one token per sequence and share D with the cache")
+    num_pages, page = kv_cache.shape[0], kv_cache.shape[1]
+    if kv_cache.numel() != num_pages * page * d:
+        raise ValueError("mla_decode_paged: the cache must have a single kv head")
+    dv = int(dv if dv is not None else out.shape[-1])
+    if out.numel() != b * h * dv or out.dtype != q.dtype:
+        raise ValueError("mla_decode_paged: out must be (B, H, DV) of q's dtype")
+    if block_table.dtype != torch.int32 or cache_seqlens.dtype != torch.int32 or block_table.shape[0] != b \
+            or cache_seqlens.numel() != b:
+        raise ValueError("mla_decode_paged: block_table (B, max_pages) and cache_seqlens (B,) must be int32")
+    if kv_scale is not None and (kv_scale.dtype != torch.float32 or kv_scale.numel() != num_pages * page):
+        raise ValueError("mla_decode_paged: kv_scale must be (num_pages, page) float32")
+    if kv_cache.dtype == torch.float8_e4m3fn and kv_scale is None:
+        raise ValueError("mla_decode_paged: an e4m3 cache needs kv_scale")
+    if softmax_scale is None:
+        softmax_scale = d ** -0.5
+    s = _prepare(q, kv_cache, kv_scale, block_table, cache_seqlens, out)
+    lib = N.load()
+    ws = _workspace(q.device, int(lib.tl_b200_mla_decode_paged_workspace_bytes(b)))
+    return N.check(lib.tl_b200_mla_decode_paged(_ptr(q), _ptr(kv_cache), _ptr(kv_scale), _ptr(block_table),
+                                               _ptr(cache_seqlens), _ptr(out), b, h, d, dv, page,
+                                               block_table.shape[1], num_pages, float(softmax_scale),
+                                               dtype_code(q.dtype), dtype_code(kv_cache.dtype), _ptr(ws), ws.numel(), s),
+                   "tl_b200_mla_decode_paged")

@@ -53,3 +53,41 @@ def llama8b_algorithmic_bytes(tokens: int = 8192, hidden: int = 4096, q_heads: i
         "rope": 2 * tokens * (q_heads + kv_heads) * head_dim * elem + 2 * tokens * head_dim * elem,
         "swiglu": 3 * tokens * ffn * elem,
     }
+
+
+def quantise_tokens_e4m3(x: torch.Tensor):
+    """One fp32 scale per token over all its columns: scale = amax / 448 (clamped), bytes = e4m3(x / scale)."""
+    amax = x.abs().amax(dim=-1, keepdim=True).clamp(min=1e-4)
+    scale = amax / 448.0
+    return (x / scale).to(torch.float8_e4m3fn), scale.squeeze(-1).float()
+
+
+def mla_fp8_paged(batch: int = 128, heads: int = 128, d: int = 576, dv: int = 512, page_size: int = 64,
+                  min_len: int = 1024, max_len: int = 8192, seed: int = 3, spare_pages: int = 8,
+                  dtype=torch.bfloat16) -> dict:
+    """FP8 MLA paged decode at DeepSeek-V3 shape: one query token per sequence, latent KV cache in
+    e4m3 with one fp32 scale per token, pages of `page_size` tokens assigned by a random
+    permutation, sequence lengths uniform in [min_len, max_len]."""
+    g = _gen(seed)
+    lens = torch.randint(min_len, max_len + 1, (batch,), generator=g, dtype=torch.int32)
+    pages_per_seq = (lens + page_size - 1) // page_size
+    total_pages = int(pages_per_seq.sum()) + spare_pages
+    max_pages = (max_len + page_size - 1) // page_size
+    perm = torch.randperm(total_pages, generator=g).to(torch.int32)
+    table = torch.zeros(batch, max_pages, dtype=torch.int32)
+    cursor = 0
+    for b in range(batch):
+        n = int(pages_per_seq[b])
+        table[b, :n] = perm[cursor:cursor + n]
+        cursor += n
+    cache = torch.empty(total_pages, page_size, d, dtype=torch.float8_e4m3fn)
+    scale = torch.empty(total_pages, page_size, dtype=torch.float32)
+    step = 512
+    for p0 in range(0, total_pages, step):                      # bounded fp32 staging
+        p1 = min(total_pages, p0 + step)
+        c8, sc = quantise_tokens_e4m3(torch.randn(p1 - p0, page_size, d, generator=g))
+        cache[p0:p1] = c8
+        scale[p0:p1] = sc
+    q = torch.randn(batch, 1, heads, d, generator=g).to(dtype)
+    return {"q": q, "kv_cache": cache, "kv_scale": scale, "block_table": table, "cache_seqlens": lens, "dv": dv,
+            "softmax_scale": d ** -0.5, "total_tokens": int(lens.sum())}
