@@ -184,6 +184,24 @@ int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, const float* k
                              int q_dtype, int cache_dtype, void* workspace, int64_t workspace_bytes,
                              void* stream);
 
+/* Same computation as tl_b200_mla_decode_paged on its tensor-core configuration (e4m3 cache with
+ * per-token scales, d 576, dv 512, heads <= 128, page_size % 64 == 0), for callers that must not
+ * allocate device memory when they decode (a pool already handed out to the KV cache, code that
+ * runs under another component's allocator lock, hosts that forbid cudaMalloc after warm-up).
+ * This entry point has no counterpart in the reference.  It takes no workspace: the sequence
+ * ordering scratch is a fixed 16 KB array inside the library image, held by every GPU that
+ * loads the library until the process exits, which limits batch to 4096 sequences (larger
+ * batches are rejected with TL_B200_EINVAL).  It calls no allocating routine.  The first call on
+ * a device looks up the array's device address; make that call before any stream capture.  All
+ * calls on a device share the array, so calls that may overlap on the GPU (different streams)
+ * race on it; within one stream they are ordered.  A bounded wait that gives up is not
+ * reported through tl_b200_device_status() by this variant.                                   */
+int tl_b200_mla_decode_paged_noalloc(const void* q, const void* kv_cache, const float* kv_scale,
+                                     const int32_t* block_table, const int32_t* cache_seqlens,
+                                     void* out, int64_t batch, int64_t heads, int64_t page_size,
+                                     int64_t max_pages_per_seq, int64_t num_pages, float softmax_scale,
+                                     int q_dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

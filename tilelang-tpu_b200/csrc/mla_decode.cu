@@ -505,3 +505,80 @@ extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, con
   if (q_dtype == TL_BF16) return launch_mla_rows_cache<__nv_bfloat16>(rp, cache_dtype, s);
   return launch_mla_rows_cache<__half>(rp, cache_dtype, s);
 }
+
+// =================================================================================
+// Allocation-free variant of the tensor-core path.
+//
+// Some callers cannot allocate device memory at the point where they decode: a serving loop
+// whose memory pool is fully handed out to the KV cache, a plugin that runs inside someone
+// else's allocator lock, or a host that forbids cudaMalloc once warm-up is over.  For them the
+// one piece of scratch this kernel needs (the longest-first ordering of the sequences) lives in
+// a fixed array inside the library image instead of a caller-provided workspace.  Every GPU
+// that loads the library holds these 16 KB until the process exits.
+// =================================================================================
+namespace tl {
+constexpr int kMlaNoAllocMaxBatch = 4096;
+static __device__ __align__(256) int g_mla_order_scratch[kMlaNoAllocMaxBatch];
+
+// In host code the array's name is only a handle for the runtime, not a device address, so the
+// address is looked up once per device (with that device current) and cached.
+constexpr int kMaxDevices = 64;
+static int* g_mla_order_ptr[kMaxDevices] = {};
+}  // namespace tl
+
+extern "C" int tl_b200_mla_decode_paged_noalloc(const void* q, const void* kv_cache, const float* kv_scale,
+                                                const int32_t* block_table, const int32_t* cache_seqlens,
+                                                void* out, int64_t batch, int64_t heads, int64_t page_size,
+                                                int64_t max_pages_per_seq, int64_t num_pages, float softmax_scale,
+                                                int q_dtype, void* stream) {
+  TL_REQUIRE(batch >= 0 && heads >= 0 && page_size > 0 && max_pages_per_seq >= 0 && num_pages >= 0,
+             "mla_decode_paged_noalloc: bad size");
+  TL_REQUIRE(batch <= kMlaNoAllocMaxBatch,
+             "mla_decode_paged_noalloc: batch %lld exceeds the built-in scratch (%d sequences); use "
+             "tl_b200_mla_decode_paged with a caller-provided workspace", (long long)batch, kMlaNoAllocMaxBatch);
+  if (batch == 0 || heads == 0) return TL_B200_OK;
+  TL_REQUIRE(q && kv_cache && kv_scale && block_table && cache_seqlens && out,
+             "mla_decode_paged_noalloc: null tensor pointer");
+  TL_REQUIRE(q_dtype == TL_BF16 || q_dtype == TL_F16, "mla_decode_paged_noalloc: q/out must be bfloat16 or float16");
+  TL_REQUIRE(heads <= kMlaHeads && page_size % kMlaBN == 0,
+             "mla_decode_paged_noalloc: needs heads <= 128 and a page size that is a multiple of 64");
+  TL_REQUIRE(num_pages * page_size < (1ll << 31), "mla_decode_paged_noalloc: cache too large");
+  TL_REQUIRE(aligned16(q) && aligned16(out) && aligned16(kv_cache) && aligned16(kv_scale),
+             "mla_decode_paged_noalloc: tensors must be 16-byte aligned");
+  int dev = 0;
+  TL_CUDA(cudaGetDevice(&dev));
+  TL_REQUIRE(dev >= 0 && dev < kMaxDevices, "mla_decode_paged_noalloc: device index %d out of range", dev);
+  if (g_mla_order_ptr[dev] == nullptr) {
+    int* ptr = nullptr;
+    TL_CUDA(cudaGetSymbolAddress((void**)&ptr, g_mla_order_scratch));
+    g_mla_order_ptr[dev] = ptr;
+  }
+  int* order = g_mla_order_ptr[dev];
+  cudaStream_t s = (cudaStream_t)stream;
+  CUtensorMap tm;
+  uint64_t dims[2] = {(uint64_t)kMlaD, (uint64_t)(num_pages * page_size)};
+  uint64_t strides[1] = {(uint64_t)kMlaD};
+  uint32_t box[2] = {128u, (uint32_t)kMlaBN};
+  int rc = make_tensor_map(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, kv_cache, dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  // every entry of order[0, batch) is rewritten by this launch, so nothing has to be cleared
+  mla_order_kernel<<<(unsigned)((batch + 255) / 256), 256, 0, s>>>(cache_seqlens, order, (int)batch);
+  TL_LAUNCH_CHECK("mla_order_kernel");
+  MlaParams p;
+  p.q = q; p.kv_scale = kv_scale; p.block_table = block_table; p.seqlens = cache_seqlens; p.order = order; p.out = out;
+  p.batch = (int)batch; p.heads = (int)heads; p.page_size = (int)page_size; p.max_pages = (int)max_pages_per_seq;
+  p.scale_log2 = softmax_scale * 1.4426950408889634f;
+  p.status = nullptr;      // the host-visible status word is allocated on demand; this path allocates nothing
+  if (q_dtype == TL_BF16) {
+    auto kernel = mla_decode_fp8_kernel<__nv_bfloat16>;
+    TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
+    kernel<<<(unsigned)(2 * batch), kMlaThreads, kMlaSmem, s>>>(tm, p);
+  } else {
+    auto kernel = mla_decode_fp8_kernel<__half>;
+    TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
+    kernel<<<(unsigned)(2 * batch), kMlaThreads, kMlaSmem, s>>>(tm, p);
+  }
+  TL_LAUNCH_CHECK("mla_decode_fp8_kernel");
+  return TL_B200_OK;
+}
