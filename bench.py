@@ -40,15 +40,19 @@ FALLBACK_HBM_GBS = 6650.0
 
 
 # ------------------------------------------------------------------------------------------
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
 def measured_peaks():
+    """HBM GB/s (and the bf16 burst figure for kernels timed alone) measured on this pool."""
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
             d = json.loads(p.read_text())
-            return float(d["hbm_gbs"]), "measured"
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "note": "of measured"}
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS, "note": "of fallback"}
 
 
 class ClockSampler:
@@ -174,6 +178,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--tokens", type=int, default=8192, help="tokens per GPU (default: the named config)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-kernels", action="store_true",
+                    help="skip the per-kernel section (GEMM bf16/FP8, FlashAttention, MLA decode)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -192,7 +198,8 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(minutes=5))
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
 
@@ -293,8 +300,17 @@ def main():
     e2e_ms = float(t2.item()) / e2e_steps
     e2e_value = world * bytes_per_step / (e2e_ms * 1e-3) / 1e9
 
+    # hand the big buffers back before the per-kernel section allocates its own
+    del hin, hout, d, y, qo, ko, so
+    torch.cuda.empty_cache()
+    peaks = measured_peaks()
+    kernels = None
+    if not args.no_kernels:
+        from tilelang import kernel_bench
+        kernels = kernel_bench.run_all(dev, rank, world, peaks)
+
     if rank == 0:
-        peak, peak_kind = measured_peaks()
+        peak, peak_kind = peaks["hbm_gbs"], peaks["note"].replace("of ", "")
         achieved = alg["swiglu"] / (swiglu_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
@@ -311,6 +327,8 @@ def main():
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if kernels is not None:
+            line["kernels"] = kernels
         if world == 1 and not args.no_cpu_baseline:
             cpu_gbs, cpu_s = time_cpu(w, bytes_per_step)
             line["cpu_baseline"] = {

@@ -1,0 +1,170 @@
+"""Per-kernel throughput of the tensor-core programs at the benchmark shapes, sharded over the
+ranks of one node the way `parallel.py` describes (GEMM by N columns, attention by heads, MLA
+decode by sequences) with one all-gather of the outputs timed separately.
+
+Inputs are synthetic and generated on the device (these runs measure speed; parity lives in
+tests/).  Work formulas are the reference's own: GEMM 2*M*N*K
+(examples/deepseek_deepgemm/example_deepgemm_fp8_2xAcc.py:180), attention 4*B*H*S^2*D, halved
+when causal (examples/flash_attention/example_mha_fwd_bshd.py:197-200), MLA decode
+2*sum(L)*H*(d+dv) (examples/deepseek_mla/example_mla_decode_paged.py:380).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import ops, parallel
+
+
+def _time(fn, world, reps=5, warmup=3):
+    """ms per call: CUDA events on the current stream, barrier on both sides, max over ranks."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(reps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / reps], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _entry(name, config, work, unit_scale, unit, ms, ms_gather, peak, peak_note, sharding, launches):
+    value = work / (ms * 1e-3) / unit_scale
+    return {"kernel": name, "config": config, "value": value, "unit": unit, "ms": ms,
+            "ms_with_output_gather": ms_gather, "frac_of_peak": value / peak if peak else None,
+            "peak": peak, "peak_source": peak_note, "sharding": sharding, "launches_per_call": launches}
+
+
+def gemm_bf16(dev, rank, world, peaks, m=8192, n=28672, k=8192):
+    lo, hi = parallel.partition(n, world, rank, 256)
+    g = torch.Generator(device=dev).manual_seed(2)
+    a = (torch.randn(m, k, generator=g, device=dev) * 0.05).bfloat16()
+    b = (torch.randn(k, hi - lo, generator=g, device=dev) * 0.05).bfloat16()
+    c = torch.empty(m, hi - lo, dtype=torch.bfloat16, device=dev)
+    ms = _time(lambda: ops.gemm(a, b, c), world)
+    ms_g = _time(lambda: (ops.gemm(a, b, c), parallel.all_gather_cat(c, 1)), world, reps=2, warmup=1) if world > 1 else ms
+    return _entry("gemm_tcgen05_kernel", f"bf16 M{m} K{k} N{n}, B row-major [K,N]", 2.0 * m * n * k, 1e12, "TFLOP/s",
+                  ms, ms_g, peaks["bf16_tflops"], peaks["note"], f"N columns / {world}", 1)
+
+
+def gemm_fp8(dev, rank, world, peaks, m=8192, n=28672, k=8192):
+    lo, hi = parallel.partition(n, world, rank, 128)
+    nl = hi - lo
+    g = torch.Generator(device=dev).manual_seed(2)
+    a8 = torch.randn(m, k, generator=g, device=dev).to(torch.float8_e4m3fn)
+    b8 = torch.randn(nl, k, generator=g, device=dev).to(torch.float8_e4m3fn)
+    sa = torch.rand(m, k // 128, generator=g, device=dev) * 1e-3 + 1e-4
+    sb = torch.rand(-(-nl // 128), k // 128, generator=g, device=dev) * 1e-3 + 1e-4
+    c = torch.empty(m, nl, dtype=torch.bfloat16, device=dev)
+    ms = _time(lambda: ops.gemm_fp8_blockscale(a8, b8, sa, sb, c), world)
+    ms_g = _time(lambda: (ops.gemm_fp8_blockscale(a8, b8, sa, sb, c), parallel.all_gather_cat(c, 1)), world,
+                 reps=2, warmup=1) if world > 1 else ms
+    return _entry("gemm_fp8_blockscale_kernel", f"e4m3 M{m} K{k} N{n}, fp32 scales per 1x128 (A) and 128x128 (B)",
+                  2.0 * m * n * k, 1e12, "TFLOP/s", ms, ms_g, 2 * peaks["bf16_tflops"],
+                  "2 x " + peaks["note"] + " (no FP8 peak was measured)", f"N columns / {world}", 1)
+
+
+def flash_attn(dev, rank, world, peaks, b=4, s=4096, h=32, d=128):
+    lo, hi = parallel.partition(h, world, rank)
+    hl = hi - lo
+    g = torch.Generator(device=dev).manual_seed(4)
+    q, k, v = (torch.randn(b, s, hl, d, generator=g, device=dev).bfloat16() for _ in range(3))
+    o = torch.empty_like(q)
+    ms = _time(lambda: ops.flash_attn_fwd(q, k, v, o, causal=True), world)
+    ms_g = _time(lambda: (ops.flash_attn_fwd(q, k, v, o, causal=True), parallel.all_gather_cat(o, 2)), world,
+                 reps=2, warmup=1) if world > 1 else ms
+    return _entry("flash_attn_tcgen05_kernel", f"bf16 causal B{b} H{h} S{s} D{d} (bshd)", 4.0 * b * h * s * s * d * 0.5,
+                  1e12, "TFLOP/s", ms, ms_g, peaks["bf16_tflops"], peaks["note"], f"heads / {world}", 1)
+
+
+def mla_decode(dev, rank, world, peaks, batch=128, heads=128, d=576, dv=512, page=64, lo_len=1024, hi_len=8192):
+    gc = torch.Generator(device="cpu").manual_seed(3)
+    lens_all = torch.randint(lo_len, hi_len + 1, (batch,), generator=gc, dtype=torch.int32)
+    mine = parallel.balance_by_length(lens_all.tolist(), world)[rank]
+    lens = lens_all[mine].contiguous()
+    nb = len(mine)
+    pages_per = (lens + page - 1) // page
+    total_pages = int(pages_per.sum()) + 8
+    max_pages = -(-hi_len // page)
+    perm = torch.randperm(total_pages, generator=gc).to(torch.int32)
+    table = torch.zeros(nb, max_pages, dtype=torch.int32)
+    cur = 0
+    for i in range(nb):
+        n = int(pages_per[i])
+        table[i, :n] = perm[cur:cur + n]
+        cur += n
+    g = torch.Generator(device=dev).manual_seed(3)
+    cache = torch.empty(total_pages, page, d, dtype=torch.float8_e4m3fn, device=dev)
+    scale = torch.empty(total_pages, page, dtype=torch.float32, device=dev)
+    for p0 in range(0, total_pages, 1024):
+        p1 = min(total_pages, p0 + 1024)
+        x = torch.randn(p1 - p0, page, d, generator=g, device=dev)
+        sc = x.abs().amax(dim=-1, keepdim=True).clamp(min=1e-4) / 448.0
+        cache[p0:p1] = (x / sc).to(torch.float8_e4m3fn)
+        scale[p0:p1] = sc.squeeze(-1)
+    q = torch.randn(nb, heads, d, generator=g, device=dev).bfloat16()
+    out = torch.empty(nb, heads, dv, dtype=torch.bfloat16, device=dev)
+    table, lens_d = table.to(dev), lens.to(dev)
+    fn = lambda: ops.mla_decode_paged(q, cache, scale, table, lens_d, out, softmax_scale=d ** -0.5)   # noqa: E731
+    ms = _time(fn, world)
+    lists = parallel.balance_by_length(lens_all.tolist(), world)
+    ms_g = _time(lambda: (fn(), parallel.all_gather_rows_by_index(out, lists)), world, reps=2, warmup=1) if world > 1 else ms
+    tokens = int(lens_all.sum())
+    flops = 2.0 * tokens * heads * (d + dv)
+    nbytes = tokens * (d + 4) + batch * heads * (d + dv) * 2
+    e = _entry("mla_decode_fp8_kernel", f"e4m3 paged cache, batch {batch}, {heads} heads, d {d}, dv {dv}, page {page}, "
+               f"lengths U[{lo_len},{hi_len}] ({tokens} tokens)", nbytes, 1e9, "GB/s", ms, ms_g, peaks["hbm_gbs"],
+               peaks["note"], f"sequences / {world} (balanced by length)", 2)
+    e["tflops"] = flops / (ms * 1e-3) / 1e12
+    e["frac_of_bf16_tensor_peak"] = e["tflops"] / peaks["bf16_tflops"]
+    return e
+
+
+def run_all(dev, rank, world, peaks):
+    out = []
+    for fn in (gemm_bf16, gemm_fp8, flash_attn, mla_decode):
+        try:
+            out.append(fn(dev, rank, world, peaks))
+        except Exception as exc:       # a failing extra must not lose the headline line
+            out.append({"kernel": fn.__name__, "error": f"{type(exc).__name__}: {exc}"})
+        torch.cuda.empty_cache()
+    return out
+
+
+SMALL = {      # reduced shapes for profiler captures: inputs above the 126 MB L2, a few hundred MB on the device
+    "gemm_bf16": dict(m=4096, n=8192, k=4096),
+    "gemm_fp8": dict(m=4096, n=8192, k=4096),
+    "flash_attn": dict(b=2, s=4096, h=16, d=128),
+    "mla_decode": dict(batch=32),
+}
+
+
+def main(argv=None):
+    """`python -m tilelang.kernel_bench --kernel flash_attn [--small]` on one GPU."""
+    import argparse
+    import json
+    from pathlib import Path
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", required=True, choices=sorted(SMALL))
+    ap.add_argument("--small", action="store_true", help="reduced shape (for profiler captures)")
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "note": "of fallback"}
+    f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if f.exists():
+        d = json.loads(f.read_text())
+        peaks = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "note": "of measured"}
+    fn = globals()[args.kernel]
+    print(json.dumps(fn(dev, 0, 1, peaks, **(SMALL[args.kernel] if args.small else {}))))
+
+
+if __name__ == "__main__":
+    main()
