@@ -4,8 +4,9 @@
 // (batch, head) as two 128-row "lanes".  Both lanes share every K/V tile that TMA brings into a
 // 3-stage shared-memory ring, which halves L2 traffic per flop, and they ping-pong on the tensor
 // core: while one lane's softmax warpgroup works on its scores, the MMA thread runs the other
-// lane's S = Q K^T or O += P V.  S and O live in tensor memory; P goes back through shared memory
-// (written by the softmax threads in the 128-byte-swizzled K-major layout the MMA reads).
+// lane's S = Q K^T or O += P V.  S, P and O all live in tensor memory: every lane has two S
+// buffers, so S runs two key tiles ahead of P V, and the softmax threads write P (16-bit) over the
+// S buffer it came from, which the second MMA reads as its A operand straight from tensor memory.
 // Softmax runs in the log2 domain with one thread per query row, fp32 statistics, and rescales O
 // only when a row maximum grows by more than 2^8 (the stale maximum is exact algebraically and
 // keeps P below 2^8, far inside bf16/fp32 range).
@@ -49,23 +50,23 @@ __device__ __forceinline__ int key_limit(int q, int mode, int bm, int bn, int se
 // =================================================================================
 constexpr int kFaBM = 128;       // rows per lane
 constexpr int kFaBN = 64;        // keys per tile
-constexpr int kFaStages = 3;
+constexpr int kFaStages = 4;     // K ring and V ring, each
 constexpr int kFaThreads = 384;  // warp 0 TMA, warp 1 MMA, warp 2 TMEM alloc, warps 4-7 / 8-11 softmax
 
 template <int HD> struct FaCfg {
   static constexpr int kSlabs = HD / 64;
   static constexpr int kQLane = kFaBM * HD * 2;           // one lane of Q
   static constexpr int kKV = kFaBN * HD * 2;              // one K or V tile
-  static constexpr int kP = kFaBM * kFaBN * 2;            // one lane of P
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = 2 * kQLane;
   static constexpr int kOffV = kOffK + kFaStages * kKV;
-  static constexpr int kOffP = kOffV + kFaStages * kKV;
-  static constexpr int kOffBar = kOffP + 2 * kP;
+  static constexpr int kOffBar = kOffV + kFaStages * kKV;
   static constexpr int kSmemBytes = kOffBar + 256 + 1024;
   static constexpr int kTmemCols = 512;
-  static constexpr int kColS = 0;                          // lane l: [l*64, l*64+64)
-  static constexpr int kColO = 128;                        // lane l: [128 + l*HD, ...)
+  // lane l: two S buffers of 64 fp32 columns at l*128 + buf*64 (P, 16-bit, is written over the
+  // first 32 columns of the S buffer it came from); O at 256 + l*HD
+  static constexpr int kColS = 0;
+  static constexpr int kColO = 256;
 };
 
 template <int HD, typename T>
@@ -77,7 +78,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
-  const uint32_t sm_q = base + Cfg::kOffQ, sm_k = base + Cfg::kOffK, sm_v = base + Cfg::kOffV, sm_p = base + Cfg::kOffP;
+  const uint32_t sm_q = base + Cfg::kOffQ, sm_k = base + Cfg::kOffK, sm_v = base + Cfg::kOffV;
   const uint32_t bar0 = base + Cfg::kOffBar;
   // barrier map (8 bytes each)
   const uint32_t bar_q = bar0;
@@ -85,10 +86,12 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
   const uint32_t bar_kempty = bar_kfull + 8 * kFaStages;
   const uint32_t bar_vfull = bar_kempty + 8 * kFaStages;
   const uint32_t bar_vempty = bar_vfull + 8 * kFaStages;
-  const uint32_t bar_sfull = bar_vempty + 8 * kFaStages;     // [2 lanes]
-  const uint32_t bar_pfull = bar_sfull + 16;                 // [2 lanes]
-  const uint32_t bar_pvdone = bar_pfull + 16;                // [2 lanes]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 8 * (1 + 4 * kFaStages + 6));
+  const uint32_t bar_sfull = bar_vempty + 8 * kFaStages;     // [2 lanes][2 buffers]
+  // P-ready and PV-retired barriers are per S buffer as well: a thread can only reach the next
+  // tile of the same buffer after the previous phase has completed, so phases never overlap
+  const uint32_t bar_pfull = bar_sfull + 32;                 // [2 lanes][2 buffers]
+  const uint32_t bar_pvdone = bar_pfull + 32;                // [2 lanes][2 buffers]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + Cfg::kOffBar + 8 * (1 + 4 * kFaStages + 12));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x / 32, lane_id = threadIdx.x % 32;
@@ -119,10 +122,10 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       mbar_init(bar_vfull + 8 * s, 1);
       mbar_init(bar_vempty + 8 * s, 1);
     }
-    for (int l = 0; l < 2; ++l) {
-      mbar_init(bar_sfull + 8 * l, 1);
-      mbar_init(bar_pfull + 8 * l, kFaBM);       // every softmax thread of the lane arrives
-      mbar_init(bar_pvdone + 8 * l, 1);
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar_sfull + 8 * i, 1);
+      mbar_init(bar_pfull + 8 * i, kFaBM);       // every softmax thread of the lane arrives
+      mbar_init(bar_pvdone + 8 * i, 1);
     }
     mbar_fence_init();
     prefetch_tensormap(&tm_q);
@@ -165,67 +168,65 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     }
   } else if (warp == 1) {
     // ---------------------------------------------------------------- MMA issuer
+    // Per lane S runs two key tiles ahead of P V, so a lane's softmax never waits for the tensor
+    // core:  S(0) S(1) | PV(0) S(2) | PV(1) S(3) | ...   (lane 0 and lane 1 interleaved)
     if (elect_one() && n_total > 0) {
       const uint32_t idesc_s = make_idesc(p.in_fmt, p.in_fmt, false, false, kFaBM, kFaBN);   // S = Q K^T
       const uint32_t idesc_o = make_idesc(p.in_fmt, p.in_fmt, false, true, kFaBM, HD);       // O += P V
       bool ok = mbar_wait(bar_q, 0, abort_flag);
 
-      auto issue_s = [&](int l, int j) {       // S_l = Q_l K_j^T, K dimension = head dim
+      auto s_col = [&](int l, int j) { return tmem_base + Cfg::kColS + l * 128 + (j & 1) * kFaBN; };
+      auto issue_s = [&](int l, int j) {       // S_l(j) = Q_l K_j^T, K dimension = head dim
         const int st = j % kFaStages;
-        const uint32_t d = tmem_base + Cfg::kColS + l * kFaBN;
 #pragma unroll
         for (int s = 0; s < Cfg::kSlabs; ++s)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
             const uint64_t a = smem_desc_sw128(sm_q + l * Cfg::kQLane + s * (kFaBM * 128) + kk * 32, 16, 1024);
             const uint64_t bd = smem_desc_sw128(sm_k + st * Cfg::kKV + s * (kFaBN * 128) + kk * 32, 16, 1024);
-            mma_f16_ss(d, a, bd, idesc_s, (s | kk) ? 1u : 0u);
+            mma_f16_ss(s_col(l, j), a, bd, idesc_s, (s | kk) ? 1u : 0u);
           }
-        mma_commit(bar_sfull + 8 * l);
+        mma_commit(bar_sfull + 8 * (2 * l + (j & 1)));
       };
-      auto issue_pv = [&](int l, int j) {      // O_l += P_l V_j, K dimension = keys of the tile
+      auto issue_pv = [&](int l, int j) {      // O_l += P_l(j) V_j; P comes from tensor memory
         const int st = j % kFaStages;
         const uint32_t d = tmem_base + Cfg::kColO + l * HD;
 #pragma unroll
         for (int kk = 0; kk < kFaBN / 16; ++kk) {
-          const uint64_t a = smem_desc_sw128(sm_p + l * Cfg::kP + kk * 32, 16, 1024);
-          // V tile: 64-column slabs (leading offset), 8-key groups 1 KB apart, 16 keys = 2 KB
+          // A: 16 keys of P = 8 columns of packed 16-bit pairs.  B: V tile, 64-column slabs
+          // (leading offset), 8-key groups 1 KB apart, 16 keys = 2 KB
           const uint64_t bd = smem_desc_sw128(sm_v + st * Cfg::kKV + kk * 2048, kFaBN * 128, 1024);
-          mma_f16_ss(d, a, bd, idesc_o, (j | kk) ? 1u : 0u);
+          mma_f16_ts(d, s_col(l, j) + kk * 8, bd, idesc_o, (j | kk) ? 1u : 0u);
         }
-        mma_commit(bar_pvdone + 8 * l);
+        mma_commit(bar_pvdone + 8 * (2 * l + (j & 1)));
       };
       auto last_lane = [&](int j) { return j < n_lane[1] ? 1 : 0; };   // issue order is lane 0, lane 1
-
-      if (ok) ok = mbar_wait(bar_kfull, 0, abort_flag);
-      if (ok) {
+      auto issue_s_both = [&](int j) {         // S(j) of every lane that needs it, then free the K stage
+        const int st = j % kFaStages;
+        if (!(ok = mbar_wait(bar_kfull + 8 * st, (j / kFaStages) & 1, abort_flag))) return;
         tc_fence_after_sync();
         for (int l = 0; l < 2; ++l)
-          if (n_lane[l] > 0) {
-            issue_s(l, 0);
-            if (l == last_lane(0)) mma_commit(bar_kempty);
-          }
-      }
+          if (j < n_lane[l]) issue_s(l, j);
+        mma_commit(bar_kempty + 8 * st);
+      };
+      (void)last_lane;
+
+      if (ok) issue_s_both(0);
+      if (ok && n_total > 1) issue_s_both(1);
       for (int j = 0; j < n_total && ok; ++j) {
         const int st = j % kFaStages;
         const uint32_t ph = (j / kFaStages) & 1;
+        if (!(ok = mbar_wait(bar_vfull + 8 * st, ph, abort_flag))) break;
         for (int l = 0; l < 2 && ok; ++l) {
           if (j < n_lane[l]) {
-            if (!(ok = mbar_wait(bar_vfull + 8 * st, ph, abort_flag))) break;
-            if (!(ok = mbar_wait(bar_pfull + 8 * l, j & 1, abort_flag))) break;
+            if (!(ok = mbar_wait(bar_pfull + 8 * (2 * l + (j & 1)), (j >> 1) & 1, abort_flag))) break;
             tc_fence_after_sync();
             issue_pv(l, j);
-            if (l == last_lane(j)) mma_commit(bar_vempty + 8 * st);
-          }
-          if (j + 1 < n_lane[l]) {
-            const int st1 = (j + 1) % kFaStages;
-            const uint32_t ph1 = ((j + 1) / kFaStages) & 1;
-            if (!(ok = mbar_wait(bar_kfull + 8 * st1, ph1, abort_flag))) break;
-            tc_fence_after_sync();
-            issue_s(l, j + 1);
-            if (l == last_lane(j + 1)) mma_commit(bar_kempty + 8 * st1);
           }
         }
+        if (!ok) break;
+        mma_commit(bar_vempty + 8 * st);
+        if (j + 2 < n_total) issue_s_both(j + 2);     // reuses the S buffers whose P was just consumed
       }
     }
   } else if (warp >= 4) {
@@ -236,14 +237,14 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const int q = q0 + l * kFaBM + r;
     const int n = n_lane[l];
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    const uint32_t t_s = tmem_base + Cfg::kColS + l * kFaBN + lane_off;
+    const uint32_t t_s0 = tmem_base + Cfg::kColS + l * 128 + lane_off;
     const uint32_t t_o = tmem_base + Cfg::kColO + l * HD + lane_off;
     const int limit = q < p.seq_q ? key_limit(q, p.mode, p.prog_bm, p.prog_bn, p.seq_kv) : 0;
-    const uint32_t p_row = sm_p + l * Cfg::kP + r * 128;
     float m_used = -INFINITY, row_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < n; ++j) {
-      ok = mbar_wait(bar_sfull + 8 * l, j & 1, abort_flag);
+      const uint32_t t_s = t_s0 + (j & 1) * kFaBN;
+      ok = mbar_wait(bar_sfull + 8 * (2 * l + (j & 1)), (j >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
@@ -251,28 +252,26 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       tmem_ld_32x64(t_s, sv);
       tmem_ld_wait();
       const int k0 = j * kFaBN;
-      float m_tile = -INFINITY;
-      if (k0 + kFaBN <= limit) {
+      if (k0 + kFaBN > limit) {
 #pragma unroll
-        for (int c = 0; c < 64; ++c) m_tile = fmaxf(m_tile, __uint_as_float(sv[c]));
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          float s = (k0 + c < limit) ? __uint_as_float(sv[c]) : -INFINITY;
-          sv[c] = __float_as_uint(s);
-          m_tile = fmaxf(m_tile, s);
-        }
+        for (int c = 0; c < 64; ++c)
+          if (k0 + c >= limit) sv[c] = 0xff800000u;          // -inf
       }
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 64; c += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) m4[e] = fmaxf(m4[e], __uint_as_float(sv[c + e]));
+      }
+      const float m_tile = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       const float m_new = fmaxf(m_used, m_tile * p.scale_log2);
-      // O and the P buffer are touched only after the previous P V of this lane has retired
-      if (j > 0) {
-        ok = mbar_wait(bar_pvdone + 8 * l, (j - 1) & 1, abort_flag);
+      const bool grow = (j == 0) || (m_new - m_used > 8.0f);
+      if (j > 0 && __any_sync(0xffffffffu, grow && m_used != -INFINITY)) {
+        // O is rescaled only after the previous P V of this lane has retired
+        ok = mbar_wait(bar_pvdone + 8 * (2 * l + ((j - 1) & 1)), ((j - 1) >> 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-      }
-      const bool grow = (j == 0) || (m_new - m_used > 8.0f);
-      if (j > 0 && __any_sync(0xffffffffu, grow && m_used != -INFINITY)) {
         const float alpha = (grow && m_used != -INFINITY) ? ex2_approx(m_used - m_new) : 1.0f;
         row_sum *= alpha;
 #pragma unroll 1
@@ -288,33 +287,30 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       }
       if (grow) m_used = m_new;
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      float tile_sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[32];
 #pragma unroll
-      for (int c = 0; c < 64; c += 8) {
-        uint32_t packed[4];
-#pragma unroll
-        for (int e = 0; e < 8; e += 2) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(sv[c + e]), p.scale_log2, -m_safe));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(sv[c + e + 1]), p.scale_log2, -m_safe));
-          tile_sum += p0 + p1;
-          if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-            packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
-          } else {
-            __half2 h = __floats2half2_rn(p0, p1);
-            packed[e / 2] = *reinterpret_cast<uint32_t*>(&h);
-          }
+      for (int c = 0; c < 64; c += 2) {
+        const float p0 = ex2_approx(fmaf(__uint_as_float(sv[c]), p.scale_log2, -m_safe));
+        const float p1 = ex2_approx(fmaf(__uint_as_float(sv[c + 1]), p.scale_log2, -m_safe));
+        sum4[(c >> 1) & 3] += p0 + p1;
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          packed[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
+        } else {
+          __half2 h = __floats2half2_rn(p0, p1);
+          packed[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
         }
-        st_shared_v4(p_row + (((c / 8) ^ (r & 7)) << 4), packed[0], packed[1], packed[2], packed[3]);
       }
-      row_sum += tile_sum;
-      fence_proxy_async_smem();          // P must be visible to the tensor core's shared-memory reads
+      row_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      tmem_st_32x32(t_s, packed);        // P over the first half of its own S buffer
+      tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(bar_pfull + 8 * l);
+      mbar_arrive(bar_pfull + 8 * (2 * l + (j & 1)));
     }
     // epilogue: O / row_sum -> global
     if (ok && n > 0) {
-      ok = mbar_wait(bar_pvdone + 8 * l, (n - 1) & 1, abort_flag);
+      ok = mbar_wait(bar_pvdone + 8 * (2 * l + ((n - 1) & 1)), ((n - 1) >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after_sync();

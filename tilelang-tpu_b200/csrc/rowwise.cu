@@ -199,6 +199,39 @@ __device__ __forceinline__ void rope_pair(float xe, float xo, float ce, float co
   oo = from_f32<T>(__fadd_rn(rnd<T>(__fmul_rn(xo, co)), rnd<T>(__fmul_rn(xe, se))));
 }
 
+// Packed form for 16-bit types: one 32-bit word holds an (even, odd) pair.  A bf16x2 / f16x2
+// multiply rounds each exact product once to T, which is exactly the rounding of the separate
+// tile multiplies, and costs no float conversion; only the final sum goes through fp32.
+template <typename T> struct Pair16;
+template <> struct Pair16<__nv_bfloat16> {
+  using V2 = __nv_bfloat162;
+  static __device__ __forceinline__ float lo(uint32_t w) { return __uint_as_float(w << 16); }
+  static __device__ __forceinline__ float hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    V2 r = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+};
+template <> struct Pair16<__half> {
+  using V2 = __half2;
+  static __device__ __forceinline__ float lo(uint32_t w) { return __low2float(*reinterpret_cast<V2*>(&w)); }
+  static __device__ __forceinline__ float hi(uint32_t w) { return __high2float(*reinterpret_cast<V2*>(&w)); }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    V2 r = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+};
+template <typename T>
+__device__ __forceinline__ uint32_t rope_word(uint32_t x, uint32_t c, uint32_t s) {
+  using P = Pair16<T>;
+  using V2 = typename P::V2;
+  V2 xc = __hmul2(*reinterpret_cast<V2*>(&x), *reinterpret_cast<V2*>(&c));   // (xe*ce, xo*co)
+  V2 xs = __hmul2(*reinterpret_cast<V2*>(&x), *reinterpret_cast<V2*>(&s));   // (xe*se, xo*so)
+  const uint32_t wc = *reinterpret_cast<uint32_t*>(&xc), ws = *reinterpret_cast<uint32_t*>(&xs);
+  // out[2i] = (x*cos)[2i] + (-x*sin)[2i+1];  out[2i+1] = (x*cos)[2i+1] + (x*sin)[2i]
+  return P::pack(__fadd_rn(P::lo(wc), -P::hi(ws)), __fadd_rn(P::hi(wc), P::lo(ws)));
+}
+
 template <typename T, int VB, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
 rope_kernel(const T* __restrict__ x, const T* __restrict__ cos_tab, const T* __restrict__ sin_tab,
@@ -229,10 +262,19 @@ rope_kernel(const T* __restrict__ x, const T* __restrict__ cos_tab, const T* __r
       uint32_t i = base + u * stride;
       if (i < total_vec) {
         V o;
+        if constexpr (sizeof(T) == 2) {
+          const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xa[u]);
+          const uint32_t* cw = reinterpret_cast<const uint32_t*>(&ca[u]);
+          const uint32_t* sw = reinterpret_cast<const uint32_t*>(&sa[u]);
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-        for (int p = 0; p < VN; p += 2)
-          rope_pair<T>(to_f32(xa[u][p]), to_f32(xa[u][p + 1]), to_f32(ca[u][p]), to_f32(ca[u][p + 1]),
-                       to_f32(sa[u][p]), to_f32(sa[u][p + 1]), o[p], o[p + 1]);
+          for (int p = 0; p < VB / 4; ++p) ow[p] = rope_word<T>(xw[p], cw[p], sw[p]);
+        } else {
+#pragma unroll
+          for (int p = 0; p < VN; p += 2)
+            rope_pair<T>(to_f32(xa[u][p]), to_f32(xa[u][p + 1]), to_f32(ca[u][p]), to_f32(ca[u][p + 1]),
+                         to_f32(sa[u][p]), to_f32(sa[u][p + 1]), o[p], o[p + 1]);
+        }
         o.store_stream(ob + (int64_t)i * VB);
       }
     }
