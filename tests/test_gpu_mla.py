@@ -29,12 +29,10 @@ def oracle(w, rows=None):
                               w["dv"])
 
 
-# The tensor-core path cuts the query to e4m3 with one scale per head (FP8 attention): softmax
-# weights carry ~3% noise, i.e. ~2.5% error in norm and up to 4e-2 on the largest outputs.
-FP8_Q_TOL = 5e-2
-
-
-def assert_close(out, ref, rel_norm=0.05, tol=2e-2):
+# The tensor-core path feeds the query and the softmax weights to the FP8 tensor core as two e4m3
+# terms each (value + residual), which keeps ~8 mantissa bits: the stated 2e-2 holds with margin
+# and the error in norm stays below one percent.
+def assert_close(out, ref, rel_norm=0.01, tol=2e-2):
     assert torch.allclose(out.float(), ref.float(), atol=tol, rtol=tol), (out.float() - ref.float()).abs().max()
     # FP8 attention (query cut to e4m3 with one scale per head) is a few percent accurate in norm;
     # random-data outputs are small, so the absolute tolerance alone would say little
@@ -53,7 +51,7 @@ def test_golden_paged_fp16_cache(cuda_device):
 @pytest.mark.parametrize("dtype", [BF, HF])
 def test_fma_kernel_small_fp8(cuda_device, dtype):
     w = workloads.mla_fp8_paged(batch=3, heads=8, d=64, dv=32, page_size=16, min_len=1, max_len=100, seed=5, dtype=dtype)
-    assert_close(run(w, cuda_device), oracle(w), rel_norm=0.02)
+    assert_close(run(w, cuda_device), oracle(w))
 
 
 @pytest.mark.parametrize("heads,page,lens", [(128, 64, (1, 64, 65, 500, 1000, 2048)), (16, 64, (300, 77)),
@@ -61,7 +59,7 @@ def test_fma_kernel_small_fp8(cuda_device, dtype):
 def test_tensor_core_kernel(cuda_device, heads, page, lens):
     w = workloads.mla_fp8_paged(batch=len(lens), heads=heads, page_size=page, min_len=1, max_len=max(lens), seed=7)
     w["cache_seqlens"] = torch.tensor(lens, dtype=torch.int32)
-    assert_close(run(w, cuda_device), oracle(w), tol=FP8_Q_TOL)
+    assert_close(run(w, cuda_device), oracle(w))
 
 
 def test_tensor_core_kernel_fp16_queries_and_empty_sequence(cuda_device):
@@ -69,7 +67,7 @@ def test_tensor_core_kernel_fp16_queries_and_empty_sequence(cuda_device):
     w["cache_seqlens"][1] = 0
     out = run(w, cuda_device)
     ref = oracle(w, rows=[0, 2])
-    assert_close(out[[0, 2]], ref, tol=FP8_Q_TOL)
+    assert_close(out[[0, 2]], ref)
     assert (out[1] == 0).all()
 
 
@@ -83,7 +81,7 @@ def test_peaked_attention_rows(cuda_device):
         k = cache[page, slot].float() * scale[page, slot]
         w["q"][b, 0, :, :] = (k * 3.0).to(BF)
     out = run(w, cuda_device)
-    assert_close(out, oracle(w), rel_norm=0.03)
+    assert_close(out, oracle(w))
 
 
 def test_run_to_run_determinism(cuda_device):

@@ -12,9 +12,9 @@
 // page slice into shared memory (128-byte swizzle, 128-column slabs) and the SAME image is the
 // K-major operand of S = Q K^T and the MN-major operand of O += P V, so nothing is ever
 // de-quantised elementwise.  The per-token scale multiplies the S columns after the first MMA
-// and the P columns before the second.  Q is quantised once per CTA to e4m3 with one scale per
-// head; P is split into two e4m3 terms (value + residual) so the second product keeps ~8
-// mantissa bits.  The fp32 O accumulator for 128 heads x 512 columns alone would fill tensor
+// and the P columns before the second.  Q (bf16/fp16) and P are each split into two e4m3 terms
+// (value + residual, one scale per head for Q), so both products keep ~8 mantissa bits; Q's
+// residual term and P live in tensor memory and enter the MMAs as the A operand from there.  The fp32 O accumulator for 128 heads x 512 columns alone would fill tensor
 // memory, so two CTAs share a sequence, each owning 256 output columns (S is computed by both).
 // Sequences are ordered longest-first by a small pre-kernel (scratch: one int32 per sequence).
 //
@@ -31,15 +31,17 @@ constexpr int kMlaSlabs = 5;                     // 128-byte column slabs per to
 constexpr int kMlaStages = 3;
 constexpr int kMlaTile = kMlaSlabs * kMlaBN * 128;          // 40 KB of cache bytes per stage
 constexpr int kMlaStageBytes = kMlaTile + kMlaBN * 4;       // + 64 token scales
-constexpr int kMlaQBytes = kMlaSlabs * kMlaHeads * 128;     // 80 KB of quantised Q
-constexpr int kMlaPBytes = kMlaHeads * 128;                 // 16 KB: [P_hi | P_lo] rows of 128 bytes
+constexpr int kMlaQBytes = kMlaSlabs * kMlaHeads * 128;     // 80 KB: e4m3 Q (value term; slab 4 also holds
+                                                            // the residual term of columns 512..575)
 constexpr int kMlaOffKV = kMlaQBytes;
-constexpr int kMlaOffP = kMlaOffKV + kMlaStages * (kMlaTile + 1024);   // scale area padded to 1 KB
-constexpr int kMlaOffBar = kMlaOffP + kMlaPBytes;
-constexpr int kMlaSmem = kMlaOffBar + 1024 + 1024;
-constexpr int kMlaThreads = 256;                 // warp 0 TMA, warp 1 MMA, warp 2 TMEM alloc, warps 4-7 softmax
+constexpr int kMlaOffBar = kMlaOffKV + kMlaStages * (kMlaTile + 1024);   // scale area padded to 1 KB
+constexpr int kMlaSmem = kMlaOffBar + 6144 + 1024;
+constexpr int kMlaThreads = 384;                 // warp 0 TMA, warp 1 MMA, warp 2 TMEM alloc, warps 4-11 softmax
+constexpr int kMlaSoftmaxThreads = 256;          // two warpgroups: tokens 0-31 and 32-63 of every tile
 constexpr int kMlaTmemCols = 512;
-constexpr int kMlaColS = 0, kMlaColO = 128;
+// tensor memory: S buffers [0,64) and [64,128) (P overwrites the first 32 columns of its S buffer),
+// residual term of Q for columns 0..511 in [128,256), O in [256,512)
+constexpr int kMlaColS = 0, kMlaColQlo = 128, kMlaColO = 256;
 
 struct MlaParams {
   const void* q;               // [batch, heads, 576]
@@ -90,17 +92,21 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
   const uint32_t sm_q = base;
   const uint32_t sm_kv = base + kMlaOffKV;                   // stage s at s * (tile + 1 KB)
-  const uint32_t sm_p = base + kMlaOffP;
   const uint32_t bar0 = base + kMlaOffBar;
   const uint32_t bar_kvfull = bar0;                          // [stages]
   const uint32_t bar_kvempty = bar0 + 8 * kMlaStages;
-  const uint32_t bar_sfull = bar_kvempty + 8 * kMlaStages;   // [2]
-  const uint32_t bar_pfull = bar_sfull + 16;
-  const uint32_t bar_pvdone = bar_pfull + 8;
-  const uint32_t bar_qready = bar_pvdone + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kMlaOffBar + 8 * (2 * kMlaStages + 5));
+  const uint32_t bar_sfull = bar_kvempty + 8 * kMlaStages;   // [2 S buffers]
+  const uint32_t bar_pfull = bar_sfull + 16;                 // [2]
+  const uint32_t bar_pvdone = bar_pfull + 16;                // [2]
+  const uint32_t bar_qready = bar_pvdone + 16;
+  // the two softmax warpgroups meet on mbarriers (bounded waits), never on bar.sync
+  const uint32_t bar_xch = bar_qready + 8;                   // [2 tile parities]
+  const uint32_t bar_pre = bar_xch + 16;
+  const uint32_t bar_post = bar_pre + 8;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kMlaOffBar + 8 * (2 * kMlaStages + 11));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* red = reinterpret_cast<float*>(base_ptr + kMlaOffBar + 256);       // 4 floats for the scale max
+  // exchange area of the two softmax warpgroups: [2 tile parities][2 warpgroups][128 rows] floats
+  float* exch = reinterpret_cast<float*>(base_ptr + kMlaOffBar + 1024);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int item = blockIdx.x;
@@ -116,11 +122,16 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       mbar_init(bar_kvfull + 8 * s, 1);
       mbar_init(bar_kvempty + 8 * s, 1);
     }
-    mbar_init(bar_sfull, 1);
-    mbar_init(bar_sfull + 8, 1);
-    mbar_init(bar_pfull, kMlaHeads);
-    mbar_init(bar_pvdone, 1);
-    mbar_init(bar_qready, kMlaHeads);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_sfull + 8 * i, 1);
+      mbar_init(bar_pfull + 8 * i, kMlaSoftmaxThreads);
+      mbar_init(bar_pvdone + 8 * i, 1);
+    }
+    mbar_init(bar_qready, kMlaSoftmaxThreads);
+    mbar_init(bar_xch, kMlaSoftmaxThreads);
+    mbar_init(bar_xch + 8, kMlaSoftmaxThreads);
+    mbar_init(bar_pre, kMlaSoftmaxThreads);
+    mbar_init(bar_post, kMlaSoftmaxThreads);
     mbar_fence_init();
     prefetch_tensormap(&tm_kv);
   }
@@ -156,55 +167,68 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    // S runs two tiles ahead of P V:  S(0) S(1) | PV(0) S(2) | PV(1) S(3) | ...
     if (elect_one() && n_tiles > 0) {
       const uint32_t idesc_s = make_idesc(kFmtE4M3, kFmtE4M3, false, false, kMlaHeads, kMlaBN);
       const uint32_t idesc_o = make_idesc(kFmtE4M3, kFmtE4M3, false, true, kMlaHeads, 256);
+      bool ok = true;
       auto issue_s = [&](int j) {
-        const uint32_t kv = stage_addr(j % kMlaStages);
+        const int st = j % kMlaStages;
+        if (!(ok = mbar_wait(bar_kvfull + 8 * st, (j / kMlaStages) & 1, abort_flag))) return;
+        tc_fence_after_sync();
+        const uint32_t kv = stage_addr(st);
         const uint32_t d = tmem_base + kMlaColS + (j & 1) * kMlaBN;
+        // value term of Q (shared memory) x K, all 576 columns
 #pragma unroll
         for (int kk = 0; kk < kMlaD / 32; ++kk) {
           const uint64_t a = smem_desc_sw128(sm_q + (kk / 4) * (kMlaHeads * 128) + (kk % 4) * 32, 16, 1024);
           const uint64_t bd = smem_desc_sw128(kv + (kk / 4) * (kMlaBN * 128) + (kk % 4) * 32, 16, 1024);
           mma_f8_ss(d, a, bd, idesc_s, kk ? 1u : 0u);
         }
+        // residual term of Q x K: columns 0..511 from tensor memory (8 columns per 32-byte step) ...
+#pragma unroll
+        for (int kk = 0; kk < 16; ++kk) {
+          const uint64_t bd = smem_desc_sw128(kv + (kk / 4) * (kMlaBN * 128) + (kk % 4) * 32, 16, 1024);
+          mma_f8_ts(d, tmem_base + kMlaColQlo + kk * 8, bd, idesc_s, 1u);
+        }
+        // ... columns 512..575 from the upper half of Q slab 4
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+          const uint64_t a = smem_desc_sw128(sm_q + 4 * (kMlaHeads * 128) + 64 + kk * 32, 16, 1024);
+          const uint64_t bd = smem_desc_sw128(kv + 4 * (kMlaBN * 128) + kk * 32, 16, 1024);
+          mma_f8_ss(d, a, bd, idesc_s, 1u);
+        }
         mma_commit(bar_sfull + 8 * (j & 1));
       };
-      bool ok = mbar_wait(bar_qready, 0, abort_flag);
-      if (ok) ok = mbar_wait(bar_kvfull, 0, abort_flag);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_s(0);
-      }
+      ok = mbar_wait(bar_qready, 0, abort_flag);
+      if (ok) issue_s(0);
+      if (ok && n_tiles > 1) issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) {
-          const int st1 = (j + 1) % kMlaStages;
-          if (!(ok = mbar_wait(bar_kvfull + 8 * st1, ((j + 1) / kMlaStages) & 1, abort_flag))) break;
-          tc_fence_after_sync();
-          issue_s(j + 1);
-        }
-        if (!(ok = mbar_wait(bar_pfull, j & 1, abort_flag))) break;
+        if (!(ok = mbar_wait(bar_pfull + 8 * (j & 1), (j >> 1) & 1, abort_flag))) break;
         tc_fence_after_sync();
         const uint32_t kv = stage_addr(j % kMlaStages);
+        const uint32_t pa = tmem_base + kMlaColS + (j & 1) * kMlaBN;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          // A: P row = [hi(64 tokens) | lo(64 tokens)], 32 bytes per step.  B: this half's 256 V
-          // columns = two 128-column slabs (8 KB apart), 32 tokens = 4 KB per step; the lo terms
-          // reuse the same tokens.
-          const uint64_t a = smem_desc_sw128(sm_p + kk * 32, 16, 1024);
+          // A: P row = [value(64 tokens) | residual(64 tokens)] in 32 columns, 8 columns per step.
+          // B: this half's 256 V columns = two 128-column slabs (8 KB apart), 32 tokens = 4 KB per
+          // step; the residual steps reuse the same tokens.
           const uint64_t bd = smem_desc_sw128(kv + (2 * half) * (kMlaBN * 128) + (kk & 1) * 4096, kMlaBN * 128, 1024);
-          mma_f8_ss(tmem_base + kMlaColO, a, bd, idesc_o, (j | kk) ? 1u : 0u);
+          mma_f8_ts(tmem_base + kMlaColO, pa + kk * 8, bd, idesc_o, (j | kk) ? 1u : 0u);
         }
-        mma_commit(bar_pvdone);
+        mma_commit(bar_pvdone + 8 * (j & 1));
         mma_commit(bar_kvempty + 8 * (j % kMlaStages));
+        if (j + 2 < n_tiles) issue_s(j + 2);
       }
     }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ Q quantisation, softmax, epilogue
+    const int wg = (warp - 4) / 4;                // 0: tokens 0-31 of a tile, 1: tokens 32-63
     const int quarter = warp % 4;
     const int h = quarter * 32 + lane;            // head = TMEM lane
+    const int st_id = threadIdx.x - 128;          // 0..255 among the softmax threads
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    // (1) quantise this head's query row to e4m3 with one scale
+    // (1) quantise this head's query row: q ~ (v + r) * q_scale with v, r in e4m3
     float q_scale = 1.f;
     {
       const TQ* qrow = reinterpret_cast<const TQ*>(p.q) + ((int64_t)b * p.heads + h) * kMlaD;
@@ -219,76 +243,119 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       amax = fmaxf(amax, 1e-10f);
       q_scale = amax / 448.0f;
       const float inv = 448.0f / amax;
-      for (int c16 = 0; c16 < kMlaSlabs * 8; ++c16) {        // 16-byte chunks of the 640-byte padded row
-        uint32_t w[4] = {0, 0, 0, 0};
-        if (h < p.heads && c16 * 16 < kMlaD) {
-          Vec16<TQ> v0, v1;
-          v0.raw = __ldg(reinterpret_cast<const uint4*>(qrow) + 2 * c16);
-          v1.raw = __ldg(reinterpret_cast<const uint4*>(qrow) + 2 * c16 + 1);
-          w[0] = pack_e4m3x4(to_f32(v0.e[0]) * inv, to_f32(v0.e[1]) * inv, to_f32(v0.e[2]) * inv, to_f32(v0.e[3]) * inv);
-          w[1] = pack_e4m3x4(to_f32(v0.e[4]) * inv, to_f32(v0.e[5]) * inv, to_f32(v0.e[6]) * inv, to_f32(v0.e[7]) * inv);
-          w[2] = pack_e4m3x4(to_f32(v1.e[0]) * inv, to_f32(v1.e[1]) * inv, to_f32(v1.e[2]) * inv, to_f32(v1.e[3]) * inv);
-          w[3] = pack_e4m3x4(to_f32(v1.e[4]) * inv, to_f32(v1.e[5]) * inv, to_f32(v1.e[6]) * inv, to_f32(v1.e[7]) * inv);
+      // 16 columns -> 4 words of value term and 4 words of residual term
+      auto quant16 = [&](int c16, uint32_t (&val)[4], uint32_t (&res)[4]) {
+        Vec16<TQ> v0, v1;
+        v0.raw = __ldg(reinterpret_cast<const uint4*>(qrow) + 2 * c16);
+        v1.raw = __ldg(reinterpret_cast<const uint4*>(qrow) + 2 * c16 + 1);
+        float f[16];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { f[e] = to_f32(v0.e[e]) * inv; f[8 + e] = to_f32(v1.e[e]) * inv; }
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          val[w] = pack_e4m3x4(f[4 * w], f[4 * w + 1], f[4 * w + 2], f[4 * w + 3]);
+          const float2 a = e4m3x2_to_float2(val[w]), c = e4m3x2_to_float2(val[w] >> 16);
+          res[w] = pack_e4m3x4(f[4 * w] - a.x, f[4 * w + 1] - a.y, f[4 * w + 2] - c.x, f[4 * w + 3] - c.y);
         }
-        const int slab = c16 / 8, c = c16 % 8;
-        st_shared_v4(sm_q + slab * (kMlaHeads * 128) + h * 128 + ((c ^ (h & 7)) << 4), w[0], w[1], w[2], w[3]);
+      };
+      if (wg == 0) {
+        // value term -> shared memory (K-major, 128-byte swizzle), 36 chunks of 16 columns; the
+        // residual of columns 512..575 goes to chunks 4..7 of slab 4
+        for (int c16 = 0; c16 < kMlaD / 16; ++c16) {
+          uint32_t val[4] = {0, 0, 0, 0}, res[4] = {0, 0, 0, 0};
+          if (h < p.heads) quant16(c16, val, res);
+          const int slab = c16 / 8, c = c16 % 8;
+          const uint32_t row_addr = sm_q + slab * (kMlaHeads * 128) + h * 128;
+          st_shared_v4(row_addr + ((c ^ (h & 7)) << 4), val[0], val[1], val[2], val[3]);
+          if (slab == 4) st_shared_v4(row_addr + (((c + 4) ^ (h & 7)) << 4), res[0], res[1], res[2], res[3]);
+        }
+        fence_proxy_async_smem();
+      } else {
+        // residual term of columns 0..511 -> tensor memory, 4 words per 16 columns
+#pragma unroll 1
+        for (int c128 = 0; c128 < 4; ++c128) {
+          uint32_t words[32];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            uint32_t val[4] = {0, 0, 0, 0}, res[4] = {0, 0, 0, 0};
+            if (h < p.heads) quant16(c128 * 8 + i, val, res);
+#pragma unroll
+            for (int w = 0; w < 4; ++w) words[4 * i + w] = res[w];
+          }
+          tmem_st_32x32(tmem_base + kMlaColQlo + c128 * 32 + lane_off, words);
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
       }
-      fence_proxy_async_smem();
       mbar_arrive(bar_qready);
     }
     // (2) largest token scale of the sequence: P is multiplied by 128 * scale[t] / max_scale before
     //     it is cut to e4m3, which keeps it inside (0, 256]
     float max_ts = 0.f;
-    for (int t = threadIdx.x - 128; t < seqlen; t += kMlaHeads) {
+    for (int t = st_id; t < seqlen; t += kMlaSoftmaxThreads) {
       const int page = __ldg(table + t / p.page_size);
       max_ts = fmaxf(max_ts, __ldg(p.kv_scale + (int64_t)page * p.page_size + t % p.page_size));
     }
     max_ts = warp_max(max_ts);
-    if (lane == 0) red[quarter] = max_ts;
-    asm volatile("bar.sync 1, 128;" ::: "memory");
-    max_ts = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    bool ok = true;
+    {
+      float* pre = exch + 1024;                     // its own 8 floats, apart from the per-tile area
+      if (lane == 0) pre[warp - 4] = max_ts;
+      mbar_arrive(bar_pre);
+      ok = mbar_wait(bar_pre, 0, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      max_ts = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) max_ts = fmaxf(max_ts, pre[i]);
+    }
     constexpr float kPScale = 128.0f;
     const float ts_norm = max_ts > 0.f ? kPScale / max_ts : kPScale;
     const float s_scale = q_scale * p.scale_log2;
 
-    // (3) online softmax, one row per thread
+    // (3) online softmax: a row is shared by one thread of each warpgroup (32 tokens each)
     float m_used = -INFINITY, row_sum = 0.f;
-    const uint32_t p_row = sm_p + h * 128;
-    const uint32_t t_o = tmem_base + kMlaColO + lane_off;
-    bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
+    const uint32_t t_o = tmem_base + kMlaColO + wg * 128 + lane_off;
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const uint32_t t_s = tmem_base + kMlaColS + (j & 1) * kMlaBN + lane_off;
       ok = mbar_wait(bar_sfull + 8 * (j & 1), (j >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after_sync();
-      uint32_t sv[64];
-      tmem_ld_32x64(tmem_base + kMlaColS + (j & 1) * kMlaBN + lane_off, sv);
+      uint32_t sv[32];
+      tmem_ld_32x32(t_s + wg * 32, sv);
       tmem_ld_wait();
-      const float* ts = reinterpret_cast<const float*>(base_ptr + (stage_addr(j % kMlaStages) - base) + kMlaTile);
-      const int valid = seqlen - j * kMlaBN;          // tokens of this tile that exist
-      float m_tile = -INFINITY;
+      const float* ts = reinterpret_cast<const float*>(base_ptr + (stage_addr(j % kMlaStages) - base) + kMlaTile) + wg * 32;
+      const int valid = seqlen - j * kMlaBN - wg * 32;      // tokens of this half tile that exist
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      float tsv[32];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float s = __uint_as_float(sv[c]) * (s_scale * ts[c]);
+      for (int c = 0; c < 32; ++c) {
+        tsv[c] = ts[c];
+        float s = __uint_as_float(sv[c]) * (s_scale * tsv[c]);
         s = (c < valid) ? s : -INFINITY;
         sv[c] = __float_as_uint(s);
-        m_tile = fmaxf(m_tile, s);
+        m4[c & 3] = fmaxf(m4[c & 3], s);
       }
+      float* ex = exch + (j & 1) * 256;
+      ex[wg * 128 + h] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      mbar_arrive(bar_xch + 8 * (j & 1));
+      ok = mbar_wait(bar_xch + 8 * (j & 1), (j >> 1) & 1, abort_flag);   // also: all of S is in registers now
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const float m_tile = fmaxf(ex[h], ex[128 + h]);
       const float m_new = fmaxf(m_used, m_tile);
-      if (j > 0) {
-        ok = mbar_wait(bar_pvdone, (j - 1) & 1, abort_flag);
+      // e4m3 has little dynamic range (smallest normal 2^-6), so P is kept in (0, 2] - the running
+      // maximum may lag by at most one binade - and scaled by kPScale before it is cut to e4m3
+      const bool grow = (j == 0) || (m_new - m_used > 1.0f);
+      if (j > 0 && __any_sync(0xffffffffu, grow && m_used != -INFINITY)) {
+        ok = mbar_wait(bar_pvdone + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
-      }
-      // e4m3 has little dynamic range (smallest normal 2^-6), so P is kept in (0, 2] - the running
-      // maximum may lag by at most one binade - and scaled by kPScale = 128 before it is cut to e4m3
-      const bool grow = (j == 0) || (m_new - m_used > 1.0f);
-      if (j > 0 && __any_sync(0xffffffffu, grow && m_used != -INFINITY)) {
         const float alpha = (grow && m_used != -INFINITY) ? ex2_approx(m_used - m_new) : 1.0f;
         row_sum *= alpha;
 #pragma unroll 1
-        for (int c = 0; c < 256 / 32; ++c) {
+        for (int c = 0; c < 128 / 32; ++c) {
           uint32_t ov[32];
           tmem_ld_32x32(t_o + c * 32, ov);
           tmem_ld_wait();
@@ -300,46 +367,49 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       }
       if (grow) m_used = m_new;
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      float tile_sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t hi[8], lo[8];
 #pragma unroll
-      for (int c = 0; c < 64; c += 16) {
-        uint32_t hi[4], lo[4];
+      for (int c = 0; c < 32; c += 4) {
+        float w[4];
 #pragma unroll
-        for (int e = 0; e < 16; e += 4) {
-          float w[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float pr = ex2_approx(__uint_as_float(sv[c + e + i]) - m_safe);
-            tile_sum += pr;
-            w[i] = pr * (ts[c + e + i] * ts_norm);
-          }
-          const uint32_t hq = pack_e4m3x4(w[0], w[1], w[2], w[3]);
-          const float2 h01 = e4m3x2_to_float2(hq), h23 = e4m3x2_to_float2(hq >> 16);
-          hi[e / 4] = hq;
-          lo[e / 4] = pack_e4m3x4(w[0] - h01.x, w[1] - h01.y, w[2] - h23.x, w[3] - h23.y);
+        for (int i = 0; i < 4; ++i) {
+          const float pr = ex2_approx(__uint_as_float(sv[c + i]) - m_safe);
+          sum4[i] += pr;
+          w[i] = (c + i < valid) ? pr * (tsv[c + i] * ts_norm) : 0.f;
         }
-        const int chunk = c / 16;                                // 16 tokens = one 16-byte chunk
-        st_shared_v4(p_row + ((chunk ^ (h & 7)) << 4), hi[0], hi[1], hi[2], hi[3]);
-        st_shared_v4(p_row + (((chunk + 4) ^ (h & 7)) << 4), lo[0], lo[1], lo[2], lo[3]);
+        const uint32_t hq = pack_e4m3x4(w[0], w[1], w[2], w[3]);
+        const float2 h01 = e4m3x2_to_float2(hq), h23 = e4m3x2_to_float2(hq >> 16);
+        hi[c / 4] = hq;
+        lo[c / 4] = pack_e4m3x4(w[0] - h01.x, w[1] - h01.y, w[2] - h23.x, w[3] - h23.y);
       }
-      row_sum += tile_sum;
-      fence_proxy_async_smem();
+      row_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      // P row: value term of the 64 tokens in columns 0..15, residual term in columns 16..31
+      tmem_st_32x8(t_s + wg * 8, hi);
+      tmem_st_32x8(t_s + 16 + wg * 8, lo);
+      tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(bar_pfull);
+      mbar_arrive(bar_pfull + 8 * (j & 1));
     }
-    // (4) epilogue
-    TQ* out = reinterpret_cast<TQ*>(p.out) + ((int64_t)b * p.heads + h) * kMlaDV + half * 256;
+    // (4) epilogue: each warpgroup writes 128 of this CTA's 256 output columns
+    TQ* out = reinterpret_cast<TQ*>(p.out) + ((int64_t)b * p.heads + h) * kMlaDV + half * 256 + wg * 128;
     if (n_tiles == 0) {
       if (h < p.heads)
-        for (int c = 0; c < 256 / 8; ++c) reinterpret_cast<uint4*>(out)[c] = make_uint4(0, 0, 0, 0);
-    } else if (ok) {
-      ok = mbar_wait(bar_pvdone, (n_tiles - 1) & 1, abort_flag);
+        for (int c = 0; c < 128 / 8; ++c) reinterpret_cast<uint4*>(out)[c] = make_uint4(0, 0, 0, 0);
+    } else {
+      ok = ok && mbar_wait(bar_pvdone + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
+      float* ex = exch + 512;
+      ex[wg * 128 + h] = row_sum;
+      mbar_arrive(bar_post);
+      ok = mbar_wait(bar_post, 0, abort_flag) && ok;
+      ok = __all_sync(0xffffffffu, ok);
+      const float total = ex[h] + ex[128 + h];
       if (ok) {
         tc_fence_after_sync();
-        const float inv = row_sum > 0.f ? max_ts / (kPScale * row_sum) : 0.f;     // undo the P normalisation
+        const float inv = total > 0.f ? max_ts / (kPScale * total) : 0.f;     // undo the P normalisation
 #pragma unroll 1
-        for (int c = 0; c < 256 / 32; ++c) {
+        for (int c = 0; c < 128 / 32; ++c) {
           uint32_t ov[32];
           tmem_ld_32x32(t_o + c * 32, ov);
           tmem_ld_wait();
