@@ -124,7 +124,7 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar_sfull + 8 * i, 1);
-      mbar_init(bar_pfull + 8 * i, kFaBM);       // every softmax thread of the lane arrives
+      mbar_init(bar_pfull + 8 * i, kFaBM / 32);  // one arrival per softmax warp of the lane
       mbar_init(bar_pvdone + 8 * i, 1);
     }
     mbar_fence_init();
@@ -306,7 +306,8 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       tmem_st_32x32(t_s, packed);        // P over the first half of its own S buffer
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(bar_pfull + 8 * (2 * l + (j & 1)));
+      __syncwarp();
+      if (lane_id == 0) mbar_arrive(bar_pfull + 8 * (2 * l + (j & 1)));
     }
     // epilogue: O / row_sum -> global
     if (ok && n > 0) {

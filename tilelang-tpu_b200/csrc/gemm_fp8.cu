@@ -7,9 +7,9 @@
 // the product of the two scales.
 //
 // Persistent warp-specialised kernel: TMA ring (6 stages of 128x128 A and B bytes, 128-byte
-// swizzle) -> tcgen05.mma kind::f8f6f4 into one of two partial accumulators in tensor memory ->
+// swizzle) -> tcgen05.mma kind::f8f6f4 into one of four partial accumulators in tensor memory ->
 // two epilogue warpgroups (64 columns each) pull the partial with tcgen05.ld and do the scaled
-// accumulation in registers while the tensor core already fills the other partial.
+// accumulation in registers while the tensor core already fills the next partials.
 #include "sm100.cuh"
 
 namespace tl {
@@ -20,7 +20,8 @@ constexpr int kF8Stages = 6;
 constexpr int kF8Threads = 384;       // warp 0 TMA, warp 1 MMA, warp 2 TMEM alloc, warps 4-11 promotion/epilogue
 constexpr int kF8StageBytes = (kF8BM + kF8BN) * kF8BK;
 constexpr int kF8Smem = kF8Stages * kF8StageBytes + 1024 + 256;
-constexpr int kF8TmemCols = 2 * kF8BN;
+constexpr int kF8Acc = 4;             // partial accumulators in tensor memory (4 x 128 columns)
+constexpr int kF8TmemCols = kF8Acc * kF8BN;
 
 struct F8Params {
   void* c;
@@ -45,8 +46,8 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
   const uint32_t bar_full = smem_u32(tail);
   const uint32_t bar_empty = bar_full + 8 * kF8Stages;
   const uint32_t bar_tfull = bar_empty + 8 * kF8Stages;
-  const uint32_t bar_tempty = bar_tfull + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kF8Stages + 4));
+  const uint32_t bar_tempty = bar_tfull + 8 * kF8Acc;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kF8Stages + 2 * kF8Acc));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -58,7 +59,7 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < kF8Acc; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
       mbar_init(bar_tempty + 8 * a, 8);       // one arrival per promotion warp
     }
@@ -114,8 +115,8 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-          const uint32_t buf = it & 1;
-          if (!(ok = mbar_wait(bar_tempty + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag))) break;
+          const uint32_t buf = it % kF8Acc;
+          if (!(ok = mbar_wait(bar_tempty + 8 * buf, ((it / kF8Acc) & 1) ^ 1, abort_flag))) break;
           if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag))) break;
           tc_fence_after_sync();
           const uint32_t a_addr = smem_a + stage * (kF8BM * kF8BK);
@@ -147,15 +148,16 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       const int row = tm * kF8BM + r;
       const float* sa_row = p.sa + (int64_t)(row < p.m ? row : 0) * p.kblocks;
       const float* sb_row = p.sb + (int64_t)tn * p.kblocks;
-      float acc[64];
+      float2 acc2[32];                         // 64 fp32 accumulators, updated two at a time
 #pragma unroll
-      for (int j = 0; j < 64; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 32; ++j) acc2[j] = make_float2(0.f, 0.f);
+      float* acc = reinterpret_cast<float*>(acc2);
       float scale_next = __ldg(sa_row) * __ldg(sb_row);
       for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-        const uint32_t buf = it & 1;
+        const uint32_t buf = it % kF8Acc;
         const float scale = scale_next;
         if (kb + 1 < p.kblocks) scale_next = __ldg(sa_row + kb + 1) * __ldg(sb_row + kb + 1);
-        ok = mbar_wait(bar_tfull + 8 * buf, (it >> 1) & 1, abort_flag);
+        ok = mbar_wait(bar_tfull + 8 * buf, (it / kF8Acc) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after_sync();
@@ -165,8 +167,11 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
           uint32_t v[32];
           tmem_ld_32x32(t_addr + h * 32, v);
           tmem_ld_wait();
+          const float2 sc2 = make_float2(scale, scale);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) acc[h * 32 + j] = fmaf(__uint_as_float(v[j]), scale, acc[h * 32 + j]);
+          for (int j = 0; j < 32; j += 2)
+            acc2[h * 16 + j / 2] = fma2(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), sc2,
+                                        acc2[h * 16 + j / 2]);
         }
         tc_fence_before_sync();
         __syncwarp();

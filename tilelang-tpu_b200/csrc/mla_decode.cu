@@ -38,6 +38,7 @@ constexpr int kMlaOffBar = kMlaOffKV + kMlaStages * (kMlaTile + 1024);   // scal
 constexpr int kMlaSmem = kMlaOffBar + 6144 + 1024;
 constexpr int kMlaThreads = 384;                 // warp 0 TMA, warp 1 MMA, warp 2 TMEM alloc, warps 4-11 softmax
 constexpr int kMlaSoftmaxThreads = 256;          // two warpgroups: tokens 0-31 and 32-63 of every tile
+constexpr int kMlaSoftmaxWarps = kMlaSoftmaxThreads / 32;   // barriers count one arrival per warp
 constexpr int kMlaTmemCols = 512;
 // tensor memory: S buffers [0,64) and [64,128) (P overwrites the first 32 columns of its S buffer),
 // residual term of Q for columns 0..511 in [128,256), O in [256,512)
@@ -124,14 +125,14 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_sfull + 8 * i, 1);
-      mbar_init(bar_pfull + 8 * i, kMlaSoftmaxThreads);
+      mbar_init(bar_pfull + 8 * i, kMlaSoftmaxWarps);
       mbar_init(bar_pvdone + 8 * i, 1);
     }
-    mbar_init(bar_qready, kMlaSoftmaxThreads);
-    mbar_init(bar_xch, kMlaSoftmaxThreads);
-    mbar_init(bar_xch + 8, kMlaSoftmaxThreads);
-    mbar_init(bar_pre, kMlaSoftmaxThreads);
-    mbar_init(bar_post, kMlaSoftmaxThreads);
+    mbar_init(bar_qready, kMlaSoftmaxWarps);
+    mbar_init(bar_xch, kMlaSoftmaxWarps);
+    mbar_init(bar_xch + 8, kMlaSoftmaxWarps);
+    mbar_init(bar_pre, kMlaSoftmaxWarps);
+    mbar_init(bar_post, kMlaSoftmaxWarps);
     mbar_fence_init();
     prefetch_tensormap(&tm_kv);
   }
@@ -287,7 +288,8 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
         tmem_st_wait();
         tc_fence_before_sync();
       }
-      mbar_arrive(bar_qready);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_qready);
     }
     // (2) largest token scale of the sequence: P is multiplied by 128 * scale[t] / max_scale before
     //     it is cut to e4m3, which keeps it inside (0, 256]
@@ -300,8 +302,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     bool ok = true;
     {
       float* pre = exch + 1024;                     // its own 8 floats, apart from the per-tile area
-      if (lane == 0) pre[warp - 4] = max_ts;
-      mbar_arrive(bar_pre);
+      if (lane == 0) { pre[warp - 4] = max_ts; mbar_arrive(bar_pre); }
       ok = mbar_wait(bar_pre, 0, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       max_ts = 0.f;
@@ -324,25 +325,36 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       uint32_t sv[32];
       tmem_ld_32x32(t_s + wg * 32, sv);
       tmem_ld_wait();
-      const float* ts = reinterpret_cast<const float*>(base_ptr + (stage_addr(j % kMlaStages) - base) + kMlaTile) + wg * 32;
+      const float4* ts4 = reinterpret_cast<const float4*>(base_ptr + (stage_addr(j % kMlaStages) - base) + kMlaTile) + wg * 8;
       const int valid = seqlen - j * kMlaBN - wg * 32;      // tokens of this half tile that exist
-      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      float tsv[32];
+      // sp = acc * token_scale (packed pairs); the per-head factor s_scale > 0 is applied inside the
+      // exponent, so the row maximum can be taken on sp
+      float2 sp[16];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        tsv[c] = ts[c];
-        float s = __uint_as_float(sv[c]) * (s_scale * tsv[c]);
-        s = (c < valid) ? s : -INFINITY;
-        sv[c] = __float_as_uint(s);
-        m4[c & 3] = fmaxf(m4[c & 3], s);
+      for (int i = 0; i < 8; ++i) {
+        const float4 t = ts4[i];
+        sp[2 * i] = mul2(make_float2(__uint_as_float(sv[4 * i]), __uint_as_float(sv[4 * i + 1])), make_float2(t.x, t.y));
+        sp[2 * i + 1] = mul2(make_float2(__uint_as_float(sv[4 * i + 2]), __uint_as_float(sv[4 * i + 3])), make_float2(t.z, t.w));
+      }
+      if (valid < 32) {                                      // last tile of the sequence only
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          if (c >= valid) reinterpret_cast<float*>(sp)[c] = -INFINITY;
+      }
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) {
+        m4[0] = fmaxf(m4[0], sp[i].x); m4[1] = fmaxf(m4[1], sp[i].y);
+        m4[2] = fmaxf(m4[2], sp[i + 1].x); m4[3] = fmaxf(m4[3], sp[i + 1].y);
       }
       float* ex = exch + (j & 1) * 256;
       ex[wg * 128 + h] = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      mbar_arrive(bar_xch + 8 * (j & 1));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_xch + 8 * (j & 1));
       ok = mbar_wait(bar_xch + 8 * (j & 1), (j >> 1) & 1, abort_flag);   // also: all of S is in registers now
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      const float m_tile = fmaxf(ex[h], ex[128 + h]);
+      const float m_tile = fmaxf(ex[h], ex[128 + h]) * s_scale;
       const float m_new = fmaxf(m_used, m_tile);
       // e4m3 has little dynamic range (smallest normal 2^-6), so P is kept in (0, 2] - the running
       // maximum may lag by at most one binade - and scaled by kPScale before it is cut to e4m3
@@ -367,29 +379,49 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       }
       if (grow) m_used = m_new;
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      const float2 k2 = make_float2(s_scale, s_scale), nm2 = make_float2(-m_safe, -m_safe);
+      const float2 n2 = make_float2(ts_norm, ts_norm);
+      float2 sum2a = make_float2(0.f, 0.f), sum2b = make_float2(0.f, 0.f);
       uint32_t hi[8], lo[8];
+      // value + residual e4m3 terms of a pair.  Float conversions share the slow XU pipe with
+      // ex2, so only the two float->e4m3 cuts use it; the value term is decoded back with integer
+      // and FMA-pipe work: (byte << 20) as a float is the e4m3 value times 2^-120, exactly.
+      auto split = [](float2 w, uint32_t& v8, uint32_t& r8) {
+        v8 = __nv_cvt_float2_to_fp8x2(w, __NV_SATFINITE, __NV_E4M3);
+        const float2 dec = mul2(make_float2(__uint_as_float((v8 & 0xffu) << 20), __uint_as_float((v8 & 0xff00u) << 12)),
+                                make_float2(0x1p120f, 0x1p120f));
+        r8 = __nv_cvt_float2_to_fp8x2(make_float2(w.x - dec.x, w.y - dec.y), __NV_SATFINITE, __NV_E4M3);
+      };
 #pragma unroll
-      for (int c = 0; c < 32; c += 4) {
-        float w[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float pr = ex2_approx(__uint_as_float(sv[c + i]) - m_safe);
-          sum4[i] += pr;
-          w[i] = (c + i < valid) ? pr * (tsv[c + i] * ts_norm) : 0.f;
+      for (int i = 0; i < 8; ++i) {
+        const float4 t = ts4[i];
+        const float2 a0 = fma2(sp[2 * i], k2, nm2), a1 = fma2(sp[2 * i + 1], k2, nm2);
+        const float2 p0 = make_float2(ex2_approx(a0.x), ex2_approx(a0.y));
+        const float2 p1 = make_float2(ex2_approx(a1.x), ex2_approx(a1.y));
+        sum2a = add2(sum2a, p0);
+        sum2b = add2(sum2b, p1);
+        float2 w0 = mul2(p0, mul2(make_float2(t.x, t.y), n2));
+        float2 w1 = mul2(p1, mul2(make_float2(t.z, t.w), n2));
+        if (valid < 32) {        // token scales of slots past the end are arbitrary bytes
+          if (4 * i >= valid) w0.x = 0.f;
+          if (4 * i + 1 >= valid) w0.y = 0.f;
+          if (4 * i + 2 >= valid) w1.x = 0.f;
+          if (4 * i + 3 >= valid) w1.y = 0.f;
         }
-        const uint32_t hq = pack_e4m3x4(w[0], w[1], w[2], w[3]);
-        const float2 h01 = e4m3x2_to_float2(hq), h23 = e4m3x2_to_float2(hq >> 16);
-        hi[c / 4] = hq;
-        lo[c / 4] = pack_e4m3x4(w[0] - h01.x, w[1] - h01.y, w[2] - h23.x, w[3] - h23.y);
+        uint32_t v0, r0, v1, r1;
+        split(w0, v0, r0);
+        split(w1, v1, r1);
+        hi[i] = v0 | (v1 << 16);
+        lo[i] = r0 | (r1 << 16);
       }
-      row_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      row_sum += (sum2a.x + sum2a.y) + (sum2b.x + sum2b.y);
       // P row: value term of the 64 tokens in columns 0..15, residual term in columns 16..31
       tmem_st_32x8(t_s + wg * 8, hi);
       tmem_st_32x8(t_s + 16 + wg * 8, lo);
       tmem_st_wait();
       tc_fence_before_sync();
-      mbar_arrive(bar_pfull + 8 * (j & 1));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_pfull + 8 * (j & 1));
     }
     // (4) epilogue: each warpgroup writes 128 of this CTA's 256 output columns
     TQ* out = reinterpret_cast<TQ*>(p.out) + ((int64_t)b * p.heads + h) * kMlaDV + half * 256 + wg * 128;
@@ -401,7 +433,8 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       ok = __all_sync(0xffffffffu, ok);
       float* ex = exch + 512;
       ex[wg * 128 + h] = row_sum;
-      mbar_arrive(bar_post);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_post);
       ok = mbar_wait(bar_post, 0, abort_flag) && ok;
       ok = __all_sync(0xffffffffu, ok);
       const float total = ex[h] + ex[128 + h];
