@@ -291,7 +291,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_qready);
     }
-    // (2) largest token scale of the sequence: P is multiplied by 128 * scale[t] / max_scale before
+    // (2) largest token scale of the sequence: P is multiplied by 32 * scale[t] / max_scale before
     //     it is cut to e4m3, which keeps it inside (0, 256]
     float max_ts = 0.f;
     for (int t = st_id; t < seqlen; t += kMlaSoftmaxThreads) {
@@ -309,7 +309,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
 #pragma unroll
       for (int i = 0; i < 8; ++i) max_ts = fmaxf(max_ts, pre[i]);
     }
-    constexpr float kPScale = 128.0f;
+    constexpr float kPScale = 32.0f;
     const float ts_norm = max_ts > 0.f ? kPScale / max_ts : kPScale;
     const float s_scale = q_scale * p.scale_log2;
 
@@ -356,9 +356,10 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       if (!ok) break;
       const float m_tile = fmaxf(ex[h], ex[128 + h]) * s_scale;
       const float m_new = fmaxf(m_used, m_tile);
-      // e4m3 has little dynamic range (smallest normal 2^-6), so P is kept in (0, 2] - the running
-      // maximum may lag by at most one binade - and scaled by kPScale before it is cut to e4m3
-      const bool grow = (j == 0) || (m_new - m_used > 1.0f);
+      // e4m3 has little dynamic range (largest 448, smallest normal 2^-6), so P is kept in (0, 8] -
+      // the running maximum may lag by at most three binades - and scaled by kPScale = 32 before it
+      // is cut to its two e4m3 terms
+      const bool grow = (j == 0) || (m_new - m_used > 3.0f);
       if (j > 0 && __any_sync(0xffffffffu, grow && m_used != -INFINITY)) {
         ok = mbar_wait(bar_pvdone + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
