@@ -177,6 +177,13 @@ int tl_b200_mla_decode_dense(const void* q, const void* q_pe, const void* kv, co
  * buffer of tl_b200_mla_decode_paged_workspace_bytes(batch) bytes, 16-byte aligned, that it may
  * overwrite (sequence ordering); other cases ignore it.                                       */
 int64_t tl_b200_mla_decode_paged_workspace_bytes(int64_t batch);
+/* Workspace size that additionally lets small batches be split along the sequence (split-KV with
+ * an LSE combine, as examples/deepseek_mla/example_mla_decode_paged.py:99-221 does): when the
+ * batch alone gives fewer CTAs than SMs and the workspace passed to tl_b200_mla_decode_paged is
+ * at least this large, every sequence is cut into chunks handled by separate CTAs and a second
+ * kernel combines their partial results.  Equals the plain size when no split would be used.  */
+int64_t tl_b200_mla_decode_paged_split_workspace_bytes(int64_t batch, int64_t max_pages_per_seq,
+                                                       int64_t page_size);
 int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, const float* kv_scale,
                              const int32_t* block_table, const int32_t* cache_seqlens, void* out,
                              int64_t batch, int64_t heads, int64_t d, int64_t dv, int64_t page_size,

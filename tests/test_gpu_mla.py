@@ -84,6 +84,21 @@ def test_peaked_attention_rows(cuda_device):
     assert_close(out, oracle(w))
 
 
+def test_split_along_the_sequence_matches_unsplit(cuda_device):
+    """A small batch is cut into chunks (split-KV + combine); a batch that fills the GPU is not.
+    The same sequences must give the same answers either way."""
+    small = workloads.mla_fp8_paged(batch=3, heads=128, min_len=1500, max_len=4000, seed=12)
+    out_split = run(small, cuda_device)
+    big = dict(small)
+    reps = 30                                         # 90 sequences -> 180 CTAs: no split
+    big["q"] = small["q"].repeat(reps, 1, 1, 1)
+    big["block_table"] = small["block_table"].repeat(reps, 1)
+    big["cache_seqlens"] = small["cache_seqlens"].repeat(reps)
+    out_big = run(big, cuda_device)
+    assert torch.allclose(out_split.float(), out_big[:3].float(), atol=2e-3, rtol=2e-3)
+    assert_close(out_split, oracle(small))
+
+
 def test_run_to_run_determinism(cuda_device):
     w = workloads.mla_fp8_paged(batch=4, heads=128, min_len=500, max_len=1500, seed=10)
     a = run(w, cuda_device)

@@ -38,7 +38,8 @@ def test_noalloc_matches_workspace_entry_point_twice(cuda_device):
         torch.cuda.synchronize()
         assert torch.isfinite(out.float()).all()
         assert torch.allclose(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
-        assert torch.equal(out.view(torch.int16), ref.view(torch.int16))    # same kernels, same order
+        # (the workspace entry point may split short batches along the sequence; this one never does)
+        assert (out.float() - ref.float()).norm() <= 5e-3 * ref.float().norm()
 
 
 def test_noalloc_rejects_oversized_batch(cuda_device):

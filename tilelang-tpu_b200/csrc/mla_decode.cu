@@ -54,6 +54,11 @@ struct MlaParams {
   int batch, heads, page_size, max_pages;
   float scale_log2;
   int* status;
+  // split-KV: a sequence is cut into chunks of chunk_tiles key tiles, one CTA pair per chunk; with
+  // more than one chunk the CTAs write normalised fp32 partial outputs and their log2-sum-exp
+  int chunk_tiles, max_chunks;
+  float* part_o;               // [batch, max_chunks, 128, 512]
+  float* part_lse;             // [batch, max_chunks, 128]
 };
 
 __global__ void mla_order_kernel(const int* __restrict__ seqlens, int* __restrict__ order, int batch) {
@@ -110,11 +115,15 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
   float* exch = reinterpret_cast<float*>(base_ptr + kMlaOffBar + 1024);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int item = blockIdx.x;
-  const int b = p.order[item >> 1];
-  const int half = item & 1;
+  const int per_seq = 2 * p.max_chunks;
+  const int b = p.order[blockIdx.x / per_seq];
+  const int chunk = (blockIdx.x % per_seq) >> 1;
+  const int half = blockIdx.x & 1;
   const int seqlen = max(p.seqlens[b], 0);
-  const int n_tiles = (seqlen + kMlaBN - 1) / kMlaBN;
+  const int n_tiles_seq = (seqlen + kMlaBN - 1) / kMlaBN;
+  const int n_chunks = max(1, (n_tiles_seq + p.chunk_tiles - 1) / p.chunk_tiles);
+  const int tile0 = chunk * p.chunk_tiles;                       // first key tile of this CTA
+  const int n_tiles = max(0, min(p.chunk_tiles, n_tiles_seq - tile0));
   const int* table = p.block_table + (int64_t)b * p.max_pages;
 
   if (threadIdx.x == 0) {
@@ -155,7 +164,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
         const int st = j % kMlaStages;
         const uint32_t ph = (j / kMlaStages) & 1;
         if (!(ok = mbar_wait(bar_kvempty + 8 * st, ph ^ 1, abort_flag))) break;
-        const int tok = j * kMlaBN;
+        const int tok = (tile0 + j) * kMlaBN;
         const int page = __ldg(table + tok / p.page_size);
         const int row = page * p.page_size + tok % p.page_size;      // row of the flattened cache
         const uint32_t full = bar_kvfull + 8 * st;
@@ -294,7 +303,8 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     // (2) largest token scale of the sequence: P is multiplied by 32 * scale[t] / max_scale before
     //     it is cut to e4m3, which keeps it inside (0, 256]
     float max_ts = 0.f;
-    for (int t = st_id; t < seqlen; t += kMlaSoftmaxThreads) {
+    const int tok_end = min(seqlen, (tile0 + n_tiles) * kMlaBN);
+    for (int t = tile0 * kMlaBN + st_id; t < tok_end; t += kMlaSoftmaxThreads) {
       const int page = __ldg(table + t / p.page_size);
       max_ts = fmaxf(max_ts, __ldg(p.kv_scale + (int64_t)page * p.page_size + t % p.page_size));
     }
@@ -326,7 +336,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       tmem_ld_32x32(t_s + wg * 32, sv);
       tmem_ld_wait();
       const float4* ts4 = reinterpret_cast<const float4*>(base_ptr + (stage_addr(j % kMlaStages) - base) + kMlaTile) + wg * 8;
-      const int valid = seqlen - j * kMlaBN - wg * 32;      // tokens of this half tile that exist
+      const int valid = seqlen - (tile0 + j) * kMlaBN - wg * 32;      // tokens of this half tile that exist
       // sp = acc * token_scale (packed pairs); the per-head factor s_scale > 0 is applied inside the
       // exponent, so the row maximum can be taken on sp
       float2 sp[16];
@@ -427,7 +437,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     // (4) epilogue: each warpgroup writes 128 of this CTA's 256 output columns
     TQ* out = reinterpret_cast<TQ*>(p.out) + ((int64_t)b * p.heads + h) * kMlaDV + half * 256 + wg * 128;
     if (n_tiles == 0) {
-      if (h < p.heads)
+      if (h < p.heads && chunk == 0)          // an empty sequence: zeros (later chunks own no keys at all)
         for (int c = 0; c < 128 / 8; ++c) reinterpret_cast<uint4*>(out)[c] = make_uint4(0, 0, 0, 0);
     } else {
       ok = ok && mbar_wait(bar_pvdone + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
@@ -442,12 +452,14 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       if (ok) {
         tc_fence_after_sync();
         const float inv = total > 0.f ? max_ts / (kPScale * total) : 0.f;     // undo the P normalisation
+        if (n_chunks > 1 && half == 0 && wg == 0 && h < p.heads)
+          p.part_lse[((int64_t)b * p.max_chunks + chunk) * kMlaHeads + h] = total > 0.f ? m_used + log2f(total) : -INFINITY;
 #pragma unroll 1
         for (int c = 0; c < 128 / 32; ++c) {
           uint32_t ov[32];
           tmem_ld_32x32(t_o + c * 32, ov);
           tmem_ld_wait();
-          if (h < p.heads) {
+          if (h < p.heads && n_chunks == 1) {
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
               Vec16<TQ> v;
@@ -455,6 +467,13 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
               for (int i = 0; i < 8; ++i) v.e[i] = from_f32<TQ>(__uint_as_float(ov[e + i]) * inv);
               *reinterpret_cast<uint4*>(out + c * 32 + e) = v.raw;
             }
+          } else if (h < p.heads) {
+            float* po = p.part_o + (((int64_t)b * p.max_chunks + chunk) * kMlaHeads + h) * kMlaDV + half * 256 + wg * 128;
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              *reinterpret_cast<float4*>(po + c * 32 + e) =
+                  make_float4(__uint_as_float(ov[e]) * inv, __uint_as_float(ov[e + 1]) * inv,
+                              __uint_as_float(ov[e + 2]) * inv, __uint_as_float(ov[e + 3]) * inv);
           }
         }
       }
@@ -472,6 +491,53 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kMlaTmemCols);
   }
+}
+
+// Combines the chunk partials of sequences that were split: out = sum_c 2^(lse_c - M) O_c / sum_c 2^(lse_c - M).
+template <typename TQ>
+__global__ void __launch_bounds__(128)
+mla_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                   const int* __restrict__ seqlens, TQ* __restrict__ out, int heads, int max_chunks,
+                   int chunk_tiles) {
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int n_tiles = (max(seqlens[b], 0) + kMlaBN - 1) / kMlaBN;
+  const int n_chunks = max(1, (n_tiles + chunk_tiles - 1) / chunk_tiles);
+  if (n_chunks == 1) return;                    // written directly by the decode kernel
+  const float* lse = part_lse + ((int64_t)b * max_chunks) * kMlaHeads + h;
+  float m = -INFINITY;
+  for (int c = 0; c < n_chunks; ++c) m = fmaxf(m, lse[c * kMlaHeads]);
+  float denom = 0.f;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c = 0; c < n_chunks; ++c) {
+    const float w = exp2f(lse[c * kMlaHeads] - m);
+    denom += w;
+    const float4 v = *reinterpret_cast<const float4*>(
+        part_o + (((int64_t)b * max_chunks + c) * kMlaHeads + h) * kMlaDV + threadIdx.x * 4);
+    acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+  }
+  const float inv = 1.0f / denom;
+  TQ* o = out + ((int64_t)b * heads + h) * kMlaDV + threadIdx.x * 4;
+  o[0] = from_f32<TQ>(acc.x * inv); o[1] = from_f32<TQ>(acc.y * inv);
+  o[2] = from_f32<TQ>(acc.z * inv); o[3] = from_f32<TQ>(acc.w * inv);
+}
+
+// Split configuration: no split while the batch alone fills the GPU (2 CTAs per sequence);
+// otherwise chunks of at least 8 key tiles so that about two CTAs per SM exist.
+struct MlaSplit { int chunk_tiles, max_chunks; };
+static MlaSplit mla_split_config(int64_t batch, int64_t max_pages, int64_t page_size) {
+  const int tiles_max = (int)((max_pages * page_size + kMlaBN - 1) / kMlaBN);
+  MlaSplit s{tiles_max > 0 ? tiles_max : 1, 1};
+  const int sms = sm_count();
+  if (2 * batch >= sms || tiles_max <= 8) return s;
+  const int want = (int)((2 * sms + 2 * batch - 1) / (2 * batch));      // chunks per sequence
+  int ct = (tiles_max + want - 1) / want;
+  if (ct < 8) ct = 8;
+  s.chunk_tiles = ct;
+  s.max_chunks = (tiles_max + ct - 1) / ct;
+  return s;
+}
+static int64_t mla_split_bytes(int64_t batch, int max_chunks) {
+  return max_chunks > 1 ? batch * max_chunks * kMlaHeads * (int64_t)(kMlaDV + 1) * 4 : 0;
 }
 
 // =================================================================================
@@ -554,6 +620,13 @@ extern "C" int64_t tl_b200_mla_decode_paged_workspace_bytes(int64_t batch) {
   return batch > 0 ? ((batch * 4 + 255) / 256) * 256 : 0;
 }
 
+extern "C" int64_t tl_b200_mla_decode_paged_split_workspace_bytes(int64_t batch, int64_t max_pages_per_seq,
+                                                                 int64_t page_size) {
+  if (batch <= 0 || max_pages_per_seq <= 0 || page_size <= 0) return 0;
+  const MlaSplit split = mla_split_config(batch, max_pages_per_seq, page_size);
+  return tl_b200_mla_decode_paged_workspace_bytes(batch) + mla_split_bytes(batch, split.max_chunks);
+}
+
 extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, const float* kv_scale,
                                         const int32_t* block_table, const int32_t* cache_seqlens, void* out,
                                         int64_t batch, int64_t heads, int64_t d, int64_t dv, int64_t page_size,
@@ -589,16 +662,37 @@ extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, con
     p.batch = (int)batch; p.heads = (int)heads; p.page_size = (int)page_size; p.max_pages = (int)max_pages_per_seq;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.status = device_status_word();
+    // split-KV only if the caller's workspace has room for the partials
+    const int64_t order_bytes = tl_b200_mla_decode_paged_workspace_bytes(batch);
+    MlaSplit split = mla_split_config(batch, max_pages_per_seq, page_size);
+    if (split.max_chunks > 1 && workspace_bytes < order_bytes + mla_split_bytes(batch, split.max_chunks)) {
+      split.max_chunks = 1;
+      split.chunk_tiles = 1 << 30;
+    }
+    p.chunk_tiles = split.chunk_tiles; p.max_chunks = split.max_chunks;
+    p.part_lse = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + order_bytes);
+    p.part_o = p.part_lse + batch * split.max_chunks * kMlaHeads;
+    const unsigned grid = (unsigned)(2 * batch * split.max_chunks);
     if (q_dtype == TL_BF16) {
       auto kernel = mla_decode_fp8_kernel<__nv_bfloat16>;
       TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
-      kernel<<<(unsigned)(2 * batch), kMlaThreads, kMlaSmem, s>>>(tm, p);
+      kernel<<<grid, kMlaThreads, kMlaSmem, s>>>(tm, p);
     } else {
       auto kernel = mla_decode_fp8_kernel<__half>;
       TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
-      kernel<<<(unsigned)(2 * batch), kMlaThreads, kMlaSmem, s>>>(tm, p);
+      kernel<<<grid, kMlaThreads, kMlaSmem, s>>>(tm, p);
     }
     TL_LAUNCH_CHECK("mla_decode_fp8_kernel");
+    if (split.max_chunks > 1) {
+      dim3 cgrid((unsigned)batch, (unsigned)heads);
+      if (q_dtype == TL_BF16)
+        mla_combine_kernel<__nv_bfloat16><<<cgrid, 128, 0, s>>>(p.part_o, p.part_lse, cache_seqlens, (__nv_bfloat16*)out,
+                                                              (int)heads, split.max_chunks, split.chunk_tiles);
+      else
+        mla_combine_kernel<__half><<<cgrid, 128, 0, s>>>(p.part_o, p.part_lse, cache_seqlens, (__half*)out, (int)heads,
+                                                       split.max_chunks, split.chunk_tiles);
+      TL_LAUNCH_CHECK("mla_combine_kernel");
+    }
     return TL_B200_OK;
   }
   TL_REQUIRE(dv <= 512, "mla_decode_paged: dv above 512 is not supported");
@@ -674,6 +768,7 @@ extern "C" int tl_b200_mla_decode_paged_noalloc(const void* q, const void* kv_ca
   p.batch = (int)batch; p.heads = (int)heads; p.page_size = (int)page_size; p.max_pages = (int)max_pages_per_seq;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = nullptr;      // the host-visible status word is allocated on demand; this path allocates nothing
+  p.chunk_tiles = 1 << 30; p.max_chunks = 1; p.part_o = nullptr; p.part_lse = nullptr;   // never split
   if (q_dtype == TL_BF16) {
     auto kernel = mla_decode_fp8_kernel<__nv_bfloat16>;
     TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));

@@ -39,6 +39,7 @@ PROTOTYPES = {
     "tl_b200_mla_decode_dense": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                          c_int64, c_int64, c_int64, c_float, c_int, c_void_p]),
     "tl_b200_mla_decode_paged_workspace_bytes": (c_int64, [c_int64]),
+    "tl_b200_mla_decode_paged_split_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64]),
     "tl_b200_mla_decode_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_void_p,
                                          c_int64, c_void_p]),

@@ -308,7 +308,8 @@ def mla_decode_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torch.Te
         softmax_scale = d ** -0.5
     s = _prepare(q, kv_cache, kv_scale, block_table, cache_seqlens, out)
     lib = N.load()
-    ws = _workspace(q.device, int(lib.tl_b200_mla_decode_paged_workspace_bytes(b)))
+    # sized so that small batches can be split along the sequence (the library decides)
+    ws = _workspace(q.device, int(lib.tl_b200_mla_decode_paged_split_workspace_bytes(b, block_table.shape[1], page)))
     return N.check(lib.tl_b200_mla_decode_paged(_ptr(q), _ptr(kv_cache), _ptr(kv_scale), _ptr(block_table),
                                                _ptr(cache_seqlens), _ptr(out), b, h, d, dv, page,
                                                block_table.shape[1], num_pages, float(softmax_scale),
