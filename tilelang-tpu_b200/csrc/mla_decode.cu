@@ -109,7 +109,8 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
   const uint32_t bar_xch = bar_qready + 8;                   // [2 tile parities]
   const uint32_t bar_pre = bar_xch + 16;
   const uint32_t bar_post = bar_pre + 8;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kMlaOffBar + 8 * (2 * kMlaStages + 11));
+  const uint32_t bar_qpark = bar_post + 8;                   // all residual bytes of Q are parked
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + kMlaOffBar + 8 * (2 * kMlaStages + 12));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   // exchange area of the two softmax warpgroups: [2 tile parities][2 warpgroups][128 rows] floats
   float* exch = reinterpret_cast<float*>(base_ptr + kMlaOffBar + 1024);
@@ -124,6 +125,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
   const int n_chunks = max(1, (n_tiles_seq + p.chunk_tiles - 1) / p.chunk_tiles);
   const int tile0 = chunk * p.chunk_tiles;                       // first key tile of this CTA
   const int n_tiles = max(0, min(p.chunk_tiles, n_tiles_seq - tile0));
+  if (chunk > 0 && n_tiles == 0) return;      // the grid is sized for the longest possible sequence
   const int* table = p.block_table + (int64_t)b * p.max_pages;
 
   if (threadIdx.x == 0) {
@@ -142,6 +144,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     mbar_init(bar_xch + 8, kMlaSoftmaxWarps);
     mbar_init(bar_pre, kMlaSoftmaxWarps);
     mbar_init(bar_post, kMlaSoftmaxWarps);
+    mbar_init(bar_qpark, kMlaSoftmaxWarps);
     mbar_fence_init();
     prefetch_tensormap(&tm_kv);
   }
@@ -164,6 +167,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
         const int st = j % kMlaStages;
         const uint32_t ph = (j / kMlaStages) & 1;
         if (!(ok = mbar_wait(bar_kvempty + 8 * st, ph ^ 1, abort_flag))) break;
+        if (j == 1 && !(ok = mbar_wait(bar_qready, 0, abort_flag))) break;   // stages 1-2 park Q's residual until then
         const int tok = (tile0 + j) * kMlaBN;
         const int page = __ldg(table + tok / p.page_size);
         const int row = page * p.page_size + tok % p.page_size;      // row of the flattened cache
@@ -238,82 +242,107 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     const int h = quarter * 32 + lane;            // head = TMEM lane
     const int st_id = threadIdx.x - 128;          // 0..255 among the softmax threads
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
-    // (1) quantise this head's query row: q ~ (v + r) * q_scale with v, r in e4m3
-    float q_scale = 1.f;
-    {
-      const TQ* qrow = reinterpret_cast<const TQ*>(p.q) + ((int64_t)b * p.heads + h) * kMlaD;
-      float amax = 0.f;
-      if (h < p.heads)
-        for (int c = 0; c < kMlaD / 8; ++c) {
-          Vec16<TQ> v;
-          v.raw = __ldg(reinterpret_cast<const uint4*>(qrow) + c);
+    // (1) quantise the 128 query rows: q ~ (v + r) * q_scale with v, r in e4m3.  A warp takes
+    //     one row at a time so the global reads are coalesced: 36 units of 16 columns, lanes 0-31
+    //     take units 0-31, lanes 0-3 also units 32-35.  The value term goes straight to its place in
+    //     shared memory; the residual of columns 0..511 is parked in key/value stages 1-2 (the
+    //     producer fills them only after this phase) and moved to tensor memory by the row's owner.
+    float* q_scales = exch + 1040;                                   // 128 floats
+    constexpr int kLoPitch = 528;                                    // 512 + 16: conflict-free 16-byte reads
+    uint8_t* park = base_ptr + (stage_addr(1) - base);
+    auto quant16 = [](const float (&f)[16], uint32_t (&val)[4], uint32_t (&res)[4]) {
 #pragma unroll
-          for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(to_f32(v.e[e])));
+      for (int w = 0; w < 4; ++w) {
+        val[w] = pack_e4m3x4(f[4 * w], f[4 * w + 1], f[4 * w + 2], f[4 * w + 3]);
+        const float2 a = e4m3x2_to_float2(val[w]), c = e4m3x2_to_float2(val[w] >> 16);
+        res[w] = pack_e4m3x4(f[4 * w] - a.x, f[4 * w + 1] - a.y, f[4 * w + 2] - c.x, f[4 * w + 3] - c.y);
+      }
+    };
+    for (int r = warp - 4; r < kMlaHeads; r += kMlaSoftmaxWarps) {
+      const bool live = r < p.heads;
+      const uint4* qrow = reinterpret_cast<const uint4*>(reinterpret_cast<const TQ*>(p.q) + ((int64_t)b * p.heads + r) * kMlaD);
+      Vec16<TQ> in[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) in[i].raw = make_uint4(0, 0, 0, 0);
+      if (live) {
+        in[0].raw = __ldg(qrow + 2 * lane);
+        in[1].raw = __ldg(qrow + 2 * lane + 1);
+        if (lane < 4) {
+          in[2].raw = __ldg(qrow + 64 + 2 * lane);
+          in[3].raw = __ldg(qrow + 65 + 2 * lane);
         }
-      amax = fmaxf(amax, 1e-10f);
-      q_scale = amax / 448.0f;
+      }
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(to_f32(in[i].e[e])));
+      amax = fmaxf(warp_max(amax), 1e-10f);
       const float inv = 448.0f / amax;
-      // 16 columns -> 4 words of value term and 4 words of residual term
-      auto quant16 = [&](int c16, uint32_t (&val)[4], uint32_t (&res)[4]) {
-        Vec16<TQ> v0, v1;
-        v0.raw = __ldg(reinterpret_cast<const uint4*>(qrow) + 2 * c16);
-        v1.raw = __ldg(reinterpret_cast<const uint4*>(qrow) + 2 * c16 + 1);
+      if (lane == 0) q_scales[r] = amax / 448.0f;
+#pragma unroll
+      for (int u2 = 0; u2 < 2; ++u2) {
+        if (u2 == 1 && lane >= 4) break;
+        const int unit = u2 == 0 ? lane : 32 + lane;                 // 16 columns = 16 bytes of e4m3
         float f[16];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { f[e] = to_f32(v0.e[e]) * inv; f[8 + e] = to_f32(v1.e[e]) * inv; }
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          val[w] = pack_e4m3x4(f[4 * w], f[4 * w + 1], f[4 * w + 2], f[4 * w + 3]);
-          const float2 a = e4m3x2_to_float2(val[w]), c = e4m3x2_to_float2(val[w] >> 16);
-          res[w] = pack_e4m3x4(f[4 * w] - a.x, f[4 * w + 1] - a.y, f[4 * w + 2] - c.x, f[4 * w + 3] - c.y);
+        for (int e = 0; e < 8; ++e) {
+          f[e] = to_f32(in[2 * u2].e[e]) * inv;
+          f[8 + e] = to_f32(in[2 * u2 + 1].e[e]) * inv;
         }
-      };
-      if (wg == 0) {
-        // value term -> shared memory (K-major, 128-byte swizzle), 36 chunks of 16 columns; the
-        // residual of columns 512..575 goes to chunks 4..7 of slab 4
-        for (int c16 = 0; c16 < kMlaD / 16; ++c16) {
-          uint32_t val[4] = {0, 0, 0, 0}, res[4] = {0, 0, 0, 0};
-          if (h < p.heads) quant16(c16, val, res);
-          const int slab = c16 / 8, c = c16 % 8;
-          const uint32_t row_addr = sm_q + slab * (kMlaHeads * 128) + h * 128;
-          st_shared_v4(row_addr + ((c ^ (h & 7)) << 4), val[0], val[1], val[2], val[3]);
-          if (slab == 4) st_shared_v4(row_addr + (((c + 4) ^ (h & 7)) << 4), res[0], res[1], res[2], res[3]);
-        }
-        fence_proxy_async_smem();
-      } else {
-        // residual term of columns 0..511 -> tensor memory, 4 words per 16 columns
-#pragma unroll 1
-        for (int c128 = 0; c128 < 4; ++c128) {
-          uint32_t words[32];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            uint32_t val[4] = {0, 0, 0, 0}, res[4] = {0, 0, 0, 0};
-            if (h < p.heads) quant16(c128 * 8 + i, val, res);
-#pragma unroll
-            for (int w = 0; w < 4; ++w) words[4 * i + w] = res[w];
-          }
-          tmem_st_32x32(tmem_base + kMlaColQlo + c128 * 32 + lane_off, words);
-        }
-        tmem_st_wait();
-        tc_fence_before_sync();
+        uint32_t val[4], res[4];
+        quant16(f, val, res);
+        const int slab = unit / 8, c = unit % 8;
+        const uint32_t row_addr = sm_q + slab * (kMlaHeads * 128) + r * 128;
+        st_shared_v4(row_addr + ((c ^ (r & 7)) << 4), val[0], val[1], val[2], val[3]);
+        if (slab == 4)
+          st_shared_v4(row_addr + (((c + 4) ^ (r & 7)) << 4), res[0], res[1], res[2], res[3]);
+        else
+          *reinterpret_cast<uint4*>(park + r * kLoPitch + unit * 16) = make_uint4(res[0], res[1], res[2], res[3]);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_qready);
     }
+    fence_proxy_async_smem();                    // the value term is read by the tensor core from shared memory
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_qpark);
+    bool ok = mbar_wait(bar_qpark, 0, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    const float q_scale = q_scales[h];
+    if (wg == 1 && ok) {
+      // residual term of columns 0..511 of row h -> tensor memory, 32 words per store
+#pragma unroll 1
+      for (int c128 = 0; c128 < 4; ++c128) {
+        uint32_t words[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 v = *reinterpret_cast<const uint4*>(park + h * kLoPitch + (c128 * 8 + i) * 16);
+          words[4 * i] = v.x; words[4 * i + 1] = v.y; words[4 * i + 2] = v.z; words[4 * i + 3] = v.w;
+        }
+        tmem_st_32x32(tmem_base + kMlaColQlo + c128 * 32 + lane_off, words);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar_qready);
     // (2) largest token scale of the sequence: P is multiplied by 32 * scale[t] / max_scale before
     //     it is cut to e4m3, which keeps it inside (0, 256]
     float max_ts = 0.f;
     const int tok_end = min(seqlen, (tile0 + n_tiles) * kMlaBN);
-    for (int t = tile0 * kMlaBN + st_id; t < tok_end; t += kMlaSoftmaxThreads) {
+    // four tokens per load: a page holds a multiple of 64 tokens, so a group of four never straddles pages
+#pragma unroll 4
+    for (int t = tile0 * kMlaBN + st_id * 4; t < tok_end; t += kMlaSoftmaxThreads * 4) {
       const int page = __ldg(table + t / p.page_size);
-      max_ts = fmaxf(max_ts, __ldg(p.kv_scale + (int64_t)page * p.page_size + t % p.page_size));
+      const float4 v = __ldg(reinterpret_cast<const float4*>(p.kv_scale + (int64_t)page * p.page_size + t % p.page_size));
+      max_ts = fmaxf(max_ts, v.x);                              // slots past the end hold arbitrary bytes
+      if (t + 1 < tok_end) max_ts = fmaxf(max_ts, v.y);
+      if (t + 2 < tok_end) max_ts = fmaxf(max_ts, v.z);
+      if (t + 3 < tok_end) max_ts = fmaxf(max_ts, v.w);
     }
     max_ts = warp_max(max_ts);
-    bool ok = true;
     {
       float* pre = exch + 1024;                     // its own 8 floats, apart from the per-tile area
       if (lane == 0) { pre[warp - 4] = max_ts; mbar_arrive(bar_pre); }
-      ok = mbar_wait(bar_pre, 0, abort_flag);
+      ok = mbar_wait(bar_pre, 0, abort_flag) && ok;
       ok = __all_sync(0xffffffffu, ok);
       max_ts = 0.f;
 #pragma unroll
@@ -479,7 +508,6 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       }
     }
   }
-
   tc_fence_before_sync();
   __syncthreads();
   if (*abort_flag) {
@@ -522,16 +550,16 @@ mla_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ p
 }
 
 // Split configuration: no split while the batch alone fills the GPU (2 CTAs per sequence);
-// otherwise chunks of at least 8 key tiles so that about two CTAs per SM exist.
+// otherwise chunks of at least 16 key tiles so that about three CTAs per SM exist.
 struct MlaSplit { int chunk_tiles, max_chunks; };
 static MlaSplit mla_split_config(int64_t batch, int64_t max_pages, int64_t page_size) {
   const int tiles_max = (int)((max_pages * page_size + kMlaBN - 1) / kMlaBN);
   MlaSplit s{tiles_max > 0 ? tiles_max : 1, 1};
   const int sms = sm_count();
-  if (2 * batch >= sms || tiles_max <= 8) return s;
-  const int want = (int)((2 * sms + 2 * batch - 1) / (2 * batch));      // chunks per sequence
+  if (2 * batch >= sms || tiles_max <= 16) return s;
+  const int want = (int)((3 * sms + 2 * batch - 1) / (2 * batch));      // chunks per sequence
   int ct = (tiles_max + want - 1) / want;
-  if (ct < 8) ct = 8;
+  if (ct < 16) ct = 16;
   s.chunk_tiles = ct;
   s.max_chunks = (tiles_max + ct - 1) / ct;
   return s;
