@@ -19,30 +19,11 @@
 // Sequences are ordered longest-first by a small pre-kernel (scratch: one int32 per sequence).
 //
 // Other shapes / cache dtypes run a one-thread-per-(sequence, head) FMA kernel.
-#include "sm100.cuh"
+#include "mla_common.cuh"
 
 #include <type_traits>
 
 namespace tl {
-using namespace sm100;
-
-constexpr int kMlaD = 576, kMlaDV = 512, kMlaHeads = 128, kMlaBN = 64;
-constexpr int kMlaSlabs = 5;                     // 128-byte column slabs per token row (last one half used)
-constexpr int kMlaStages = 3;
-constexpr int kMlaTile = kMlaSlabs * kMlaBN * 128;          // 40 KB of cache bytes per stage
-constexpr int kMlaStageBytes = kMlaTile + kMlaBN * 4;       // + 64 token scales
-constexpr int kMlaQBytes = kMlaSlabs * kMlaHeads * 128;     // 80 KB: e4m3 Q (value term; slab 4 also holds
-                                                            // the residual term of columns 512..575)
-constexpr int kMlaOffKV = kMlaQBytes;
-constexpr int kMlaOffBar = kMlaOffKV + kMlaStages * (kMlaTile + 1024);   // scale area padded to 1 KB
-constexpr int kMlaSmem = kMlaOffBar + 6144 + 1024;
-constexpr int kMlaThreads = 384;                 // warp 0 TMA, warp 1 MMA, warp 2 TMEM alloc, warps 4-11 softmax
-constexpr int kMlaSoftmaxThreads = 256;          // two warpgroups: tokens 0-31 and 32-63 of every tile
-constexpr int kMlaSoftmaxWarps = kMlaSoftmaxThreads / 32;   // barriers count one arrival per warp
-constexpr int kMlaTmemCols = 512;
-// tensor memory: S buffers [0,64) and [64,128) (P overwrites the first 32 columns of its S buffer),
-// residual term of Q for columns 0..511 in [128,256), O in [256,512)
-constexpr int kMlaColS = 0, kMlaColQlo = 128, kMlaColO = 256;
 
 struct MlaParams {
   const void* q;               // [batch, heads, 576]
@@ -54,11 +35,6 @@ struct MlaParams {
   int batch, heads, page_size, max_pages;
   float scale_log2;
   int* status;
-  // split-KV: a sequence is cut into chunks of chunk_tiles key tiles, one CTA pair per chunk; with
-  // more than one chunk the CTAs write normalised fp32 partial outputs and their log2-sum-exp
-  int chunk_tiles, max_chunks;
-  float* part_o;               // [batch, max_chunks, 128, 512]
-  float* part_lse;             // [batch, max_chunks, 128]
 };
 
 __global__ void mla_order_kernel(const int* __restrict__ seqlens, int* __restrict__ order, int batch) {
@@ -71,22 +47,6 @@ __global__ void mla_order_kernel(const int* __restrict__ seqlens, int* __restric
     }
     order[rank] = b;
   }
-}
-
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
-}
-
-__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
-  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
-  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
-  return lo | (hi << 16);
-}
-__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t v) {
-  __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v & 0xffffu), __NV_E4M3);
-  return __half22float2(*reinterpret_cast<__half2*>(&h));
 }
 
 template <typename TQ>
@@ -116,16 +76,10 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
   float* exch = reinterpret_cast<float*>(base_ptr + kMlaOffBar + 1024);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-  const int per_seq = 2 * p.max_chunks;
-  const int b = p.order[blockIdx.x / per_seq];
-  const int chunk = (blockIdx.x % per_seq) >> 1;
+  const int b = p.order[blockIdx.x >> 1];
   const int half = blockIdx.x & 1;
   const int seqlen = max(p.seqlens[b], 0);
-  const int n_tiles_seq = (seqlen + kMlaBN - 1) / kMlaBN;
-  const int n_chunks = max(1, (n_tiles_seq + p.chunk_tiles - 1) / p.chunk_tiles);
-  const int tile0 = chunk * p.chunk_tiles;                       // first key tile of this CTA
-  const int n_tiles = max(0, min(p.chunk_tiles, n_tiles_seq - tile0));
-  if (chunk > 0 && n_tiles == 0) return;      // the grid is sized for the longest possible sequence
+  const int n_tiles = (seqlen + kMlaBN - 1) / kMlaBN;
   const int* table = p.block_table + (int64_t)b * p.max_pages;
 
   if (threadIdx.x == 0) {
@@ -168,7 +122,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
         const uint32_t ph = (j / kMlaStages) & 1;
         if (!(ok = mbar_wait(bar_kvempty + 8 * st, ph ^ 1, abort_flag))) break;
         if (j == 1 && !(ok = mbar_wait(bar_qready, 0, abort_flag))) break;   // stages 1-2 park Q's residual until then
-        const int tok = (tile0 + j) * kMlaBN;
+        const int tok = j * kMlaBN;
         const int page = __ldg(table + tok / p.page_size);
         const int row = page * p.page_size + tok % p.page_size;      // row of the flattened cache
         const uint32_t full = bar_kvfull + 8 * st;
@@ -327,10 +281,10 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     // (2) largest token scale of the sequence: P is multiplied by 32 * scale[t] / max_scale before
     //     it is cut to e4m3, which keeps it inside (0, 256]
     float max_ts = 0.f;
-    const int tok_end = min(seqlen, (tile0 + n_tiles) * kMlaBN);
+    const int tok_end = seqlen;
     // four tokens per load: a page holds a multiple of 64 tokens, so a group of four never straddles pages
 #pragma unroll 4
-    for (int t = tile0 * kMlaBN + st_id * 4; t < tok_end; t += kMlaSoftmaxThreads * 4) {
+    for (int t = st_id * 4; t < tok_end; t += kMlaSoftmaxThreads * 4) {
       const int page = __ldg(table + t / p.page_size);
       const float4 v = __ldg(reinterpret_cast<const float4*>(p.kv_scale + (int64_t)page * p.page_size + t % p.page_size));
       max_ts = fmaxf(max_ts, v.x);                              // slots past the end hold arbitrary bytes
@@ -365,7 +319,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       tmem_ld_32x32(t_s + wg * 32, sv);
       tmem_ld_wait();
       const float4* ts4 = reinterpret_cast<const float4*>(base_ptr + (stage_addr(j % kMlaStages) - base) + kMlaTile) + wg * 8;
-      const int valid = seqlen - (tile0 + j) * kMlaBN - wg * 32;      // tokens of this half tile that exist
+      const int valid = seqlen - j * kMlaBN - wg * 32;      // tokens of this half tile that exist
       // sp = acc * token_scale (packed pairs); the per-head factor s_scale > 0 is applied inside the
       // exponent, so the row maximum can be taken on sp
       float2 sp[16];
@@ -466,7 +420,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     // (4) epilogue: each warpgroup writes 128 of this CTA's 256 output columns
     TQ* out = reinterpret_cast<TQ*>(p.out) + ((int64_t)b * p.heads + h) * kMlaDV + half * 256 + wg * 128;
     if (n_tiles == 0) {
-      if (h < p.heads && chunk == 0)          // an empty sequence: zeros (later chunks own no keys at all)
+      if (h < p.heads)                        // an empty sequence: zeros
         for (int c = 0; c < 128 / 8; ++c) reinterpret_cast<uint4*>(out)[c] = make_uint4(0, 0, 0, 0);
     } else {
       ok = ok && mbar_wait(bar_pvdone + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
@@ -481,14 +435,12 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       if (ok) {
         tc_fence_after_sync();
         const float inv = total > 0.f ? max_ts / (kPScale * total) : 0.f;     // undo the P normalisation
-        if (n_chunks > 1 && half == 0 && wg == 0 && h < p.heads)
-          p.part_lse[((int64_t)b * p.max_chunks + chunk) * kMlaHeads + h] = total > 0.f ? m_used + log2f(total) : -INFINITY;
 #pragma unroll 1
         for (int c = 0; c < 128 / 32; ++c) {
           uint32_t ov[32];
           tmem_ld_32x32(t_o + c * 32, ov);
           tmem_ld_wait();
-          if (h < p.heads && n_chunks == 1) {
+          if (h < p.heads) {
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
               Vec16<TQ> v;
@@ -496,13 +448,6 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
               for (int i = 0; i < 8; ++i) v.e[i] = from_f32<TQ>(__uint_as_float(ov[e + i]) * inv);
               *reinterpret_cast<uint4*>(out + c * 32 + e) = v.raw;
             }
-          } else if (h < p.heads) {
-            float* po = p.part_o + (((int64_t)b * p.max_chunks + chunk) * kMlaHeads + h) * kMlaDV + half * 256 + wg * 128;
-#pragma unroll
-            for (int e = 0; e < 32; e += 4)
-              *reinterpret_cast<float4*>(po + c * 32 + e) =
-                  make_float4(__uint_as_float(ov[e]) * inv, __uint_as_float(ov[e + 1]) * inv,
-                              __uint_as_float(ov[e + 2]) * inv, __uint_as_float(ov[e + 3]) * inv);
           }
         }
       }
@@ -519,53 +464,6 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, kMlaTmemCols);
   }
-}
-
-// Combines the chunk partials of sequences that were split: out = sum_c 2^(lse_c - M) O_c / sum_c 2^(lse_c - M).
-template <typename TQ>
-__global__ void __launch_bounds__(128)
-mla_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
-                   const int* __restrict__ seqlens, TQ* __restrict__ out, int heads, int max_chunks,
-                   int chunk_tiles) {
-  const int b = blockIdx.x, h = blockIdx.y;
-  const int n_tiles = (max(seqlens[b], 0) + kMlaBN - 1) / kMlaBN;
-  const int n_chunks = max(1, (n_tiles + chunk_tiles - 1) / chunk_tiles);
-  if (n_chunks == 1) return;                    // written directly by the decode kernel
-  const float* lse = part_lse + ((int64_t)b * max_chunks) * kMlaHeads + h;
-  float m = -INFINITY;
-  for (int c = 0; c < n_chunks; ++c) m = fmaxf(m, lse[c * kMlaHeads]);
-  float denom = 0.f;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int c = 0; c < n_chunks; ++c) {
-    const float w = exp2f(lse[c * kMlaHeads] - m);
-    denom += w;
-    const float4 v = *reinterpret_cast<const float4*>(
-        part_o + (((int64_t)b * max_chunks + c) * kMlaHeads + h) * kMlaDV + threadIdx.x * 4);
-    acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
-  }
-  const float inv = 1.0f / denom;
-  TQ* o = out + ((int64_t)b * heads + h) * kMlaDV + threadIdx.x * 4;
-  o[0] = from_f32<TQ>(acc.x * inv); o[1] = from_f32<TQ>(acc.y * inv);
-  o[2] = from_f32<TQ>(acc.z * inv); o[3] = from_f32<TQ>(acc.w * inv);
-}
-
-// Split configuration: no split while the batch alone fills the GPU (2 CTAs per sequence);
-// otherwise chunks of at least 16 key tiles so that about three CTAs per SM exist.
-struct MlaSplit { int chunk_tiles, max_chunks; };
-static MlaSplit mla_split_config(int64_t batch, int64_t max_pages, int64_t page_size) {
-  const int tiles_max = (int)((max_pages * page_size + kMlaBN - 1) / kMlaBN);
-  MlaSplit s{tiles_max > 0 ? tiles_max : 1, 1};
-  const int sms = sm_count();
-  if (2 * batch >= sms || tiles_max <= 16) return s;
-  const int want = (int)((3 * sms + 2 * batch - 1) / (2 * batch));      // chunks per sequence
-  int ct = (tiles_max + want - 1) / want;
-  if (ct < 16) ct = 16;
-  s.chunk_tiles = ct;
-  s.max_chunks = (tiles_max + ct - 1) / ct;
-  return s;
-}
-static int64_t mla_split_bytes(int64_t batch, int max_chunks) {
-  return max_chunks > 1 ? batch * max_chunks * kMlaHeads * (int64_t)(kMlaDV + 1) * 4 : 0;
 }
 
 // =================================================================================
@@ -589,7 +487,7 @@ __global__ void __launch_bounds__(128)
 mla_rows_kernel(const MlaRowParams p) {
   const int idx = blockIdx.x * 128 + threadIdx.x;
   if (idx >= p.batch * p.heads) return;
-  const int b = idx / p.heads, h = idx % p.heads;
+  const int b = idx / p.heads;
   const TQ* q = (const TQ*)p.q + (int64_t)idx * p.d;
   const int* table = p.block_table + (int64_t)b * p.max_pages;
   const int seqlen = p.seqlens[b];
@@ -651,8 +549,10 @@ extern "C" int64_t tl_b200_mla_decode_paged_workspace_bytes(int64_t batch) {
 extern "C" int64_t tl_b200_mla_decode_paged_split_workspace_bytes(int64_t batch, int64_t max_pages_per_seq,
                                                                  int64_t page_size) {
   if (batch <= 0 || max_pages_per_seq <= 0 || page_size <= 0) return 0;
-  const MlaSplit split = mla_split_config(batch, max_pages_per_seq, page_size);
-  return tl_b200_mla_decode_paged_workspace_bytes(batch) + mla_split_bytes(batch, split.max_chunks);
+  const int64_t plain = tl_b200_mla_decode_paged_workspace_bytes(batch);
+  if (!mla_persistent_supported(batch)) return plain;
+  const int64_t full = mla_persistent_workspace_bytes(batch);
+  return full > plain ? full : plain;
 }
 
 extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, const float* kv_scale,
@@ -672,6 +572,10 @@ extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, con
   const bool tc = cache_dtype == TL_E4M3 && d == kMlaD && dv == kMlaDV && heads <= kMlaHeads && page_size % kMlaBN == 0 &&
                   aligned16(q) && aligned16(out) && aligned16(kv_cache) && aligned16(kv_scale);
   if (tc) {
+    // with the large workspace: the persistent, work-balanced kernel; with the small one: one CTA pair per sequence
+    if (workspace && mla_persistent_supported(batch) && workspace_bytes >= mla_persistent_workspace_bytes(batch))
+      return mla_persistent_launch(q, kv_cache, kv_scale, block_table, cache_seqlens, out, batch, heads, page_size,
+                                   max_pages_per_seq, num_pages, softmax_scale, q_dtype, workspace, s);
     TL_REQUIRE(workspace && workspace_bytes >= tl_b200_mla_decode_paged_workspace_bytes(batch),
                "mla_decode_paged: workspace of %lld bytes required (tl_b200_mla_decode_paged_workspace_bytes)",
                (long long)tl_b200_mla_decode_paged_workspace_bytes(batch));
@@ -690,17 +594,7 @@ extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, con
     p.batch = (int)batch; p.heads = (int)heads; p.page_size = (int)page_size; p.max_pages = (int)max_pages_per_seq;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.status = device_status_word();
-    // split-KV only if the caller's workspace has room for the partials
-    const int64_t order_bytes = tl_b200_mla_decode_paged_workspace_bytes(batch);
-    MlaSplit split = mla_split_config(batch, max_pages_per_seq, page_size);
-    if (split.max_chunks > 1 && workspace_bytes < order_bytes + mla_split_bytes(batch, split.max_chunks)) {
-      split.max_chunks = 1;
-      split.chunk_tiles = 1 << 30;
-    }
-    p.chunk_tiles = split.chunk_tiles; p.max_chunks = split.max_chunks;
-    p.part_lse = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + order_bytes);
-    p.part_o = p.part_lse + batch * split.max_chunks * kMlaHeads;
-    const unsigned grid = (unsigned)(2 * batch * split.max_chunks);
+    const unsigned grid = (unsigned)(2 * batch);
     if (q_dtype == TL_BF16) {
       auto kernel = mla_decode_fp8_kernel<__nv_bfloat16>;
       TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));
@@ -711,16 +605,6 @@ extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, con
       kernel<<<grid, kMlaThreads, kMlaSmem, s>>>(tm, p);
     }
     TL_LAUNCH_CHECK("mla_decode_fp8_kernel");
-    if (split.max_chunks > 1) {
-      dim3 cgrid((unsigned)batch, (unsigned)heads);
-      if (q_dtype == TL_BF16)
-        mla_combine_kernel<__nv_bfloat16><<<cgrid, 128, 0, s>>>(p.part_o, p.part_lse, cache_seqlens, (__nv_bfloat16*)out,
-                                                              (int)heads, split.max_chunks, split.chunk_tiles);
-      else
-        mla_combine_kernel<__half><<<cgrid, 128, 0, s>>>(p.part_o, p.part_lse, cache_seqlens, (__half*)out, (int)heads,
-                                                       split.max_chunks, split.chunk_tiles);
-      TL_LAUNCH_CHECK("mla_combine_kernel");
-    }
     return TL_B200_OK;
   }
   TL_REQUIRE(dv <= 512, "mla_decode_paged: dv above 512 is not supported");
@@ -796,7 +680,6 @@ extern "C" int tl_b200_mla_decode_paged_noalloc(const void* q, const void* kv_ca
   p.batch = (int)batch; p.heads = (int)heads; p.page_size = (int)page_size; p.max_pages = (int)max_pages_per_seq;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = nullptr;      // the host-visible status word is allocated on demand; this path allocates nothing
-  p.chunk_tiles = 1 << 30; p.max_chunks = 1; p.part_o = nullptr; p.part_lse = nullptr;   // never split
   if (q_dtype == TL_BF16) {
     auto kernel = mla_decode_fp8_kernel<__nv_bfloat16>;
     TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));

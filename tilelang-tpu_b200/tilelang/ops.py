@@ -284,10 +284,12 @@ def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def mla_decode_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torch.Tensor | None, block_table: torch.Tensor,
                      cache_seqlens: torch.Tensor, out: torch.Tensor, dv: int | None = None,
-                     softmax_scale: float | None = None) -> int:
+                     softmax_scale: float | None = None, balanced: bool = True) -> int:
     """Paged MLA decode.  q (B, H, D) or (B, 1, H, D); kv_cache (num_pages, page, D) or
     (num_pages, page, 1, D) in e4m3 / fp16 / bf16; kv_scale (num_pages, page) fp32 for e4m3;
-    block_table (B, max_pages) int32; cache_seqlens (B,) int32; out (B, H, DV) or (B, 1, H, DV)."""
+    block_table (B, max_pages) int32; cache_seqlens (B,) int32; out (B, H, DV) or (B, 1, H, DV).
+    `balanced` hands the library the large workspace of its persistent, work-balanced kernel;
+    False passes only the small one (one CTA pair per sequence)."""
     b, h, d = q.shape[0], q.shape[-2], q.shape[-1]
     if q.numel() != b * h * d or kv_cache.shape[-1] != d:
         raise ValueError("mla_decode_paged: q must hold one token per sequence and share D with the cache")
@@ -308,10 +310,13 @@ def mla_decode_paged(q: torch.Tensor, kv_cache: torch.Tensor, kv_scale: torch.Te
         softmax_scale = d ** -0.5
     s = _prepare(q, kv_cache, kv_scale, block_table, cache_seqlens, out)
     lib = N.load()
-    # sized so that small batches can be split along the sequence (the library decides)
-    ws = _workspace(q.device, int(lib.tl_b200_mla_decode_paged_split_workspace_bytes(b, block_table.shape[1], page)))
+    if balanced:
+        ws_bytes = int(lib.tl_b200_mla_decode_paged_split_workspace_bytes(b, block_table.shape[1], page))
+    else:
+        ws_bytes = int(lib.tl_b200_mla_decode_paged_workspace_bytes(b))
+    ws = _workspace(q.device, ws_bytes)
     return N.check(lib.tl_b200_mla_decode_paged(_ptr(q), _ptr(kv_cache), _ptr(kv_scale), _ptr(block_table),
                                                _ptr(cache_seqlens), _ptr(out), b, h, d, dv, page,
                                                block_table.shape[1], num_pages, float(softmax_scale),
-                                               dtype_code(q.dtype), dtype_code(kv_cache.dtype), _ptr(ws), ws.numel(), s),
+                                               dtype_code(q.dtype), dtype_code(kv_cache.dtype), _ptr(ws), ws_bytes, s),
                    "tl_b200_mla_decode_paged")
