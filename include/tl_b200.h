@@ -174,14 +174,17 @@ int tl_b200_mla_decode_dense(const void* q, const void* q_pe, const void* kv, co
  * examples/deepseek_mla/example_mla_decode_paged.py:20-97 (block table, cache_seqlens, masked tail)
  * with h_kv = 1; the FP8 cache with per-token scales is the benchmark's extension of it.
  * The tensor-core path (e4m3, d 576, dv 512, heads <= 128, page_size % 64 == 0) needs a scratch
- * buffer of tl_b200_mla_decode_paged_workspace_bytes(batch) bytes, 16-byte aligned, that it may
- * overwrite (sequence ordering); other cases ignore it.                                       */
+ * buffer, 16-byte aligned, that it may overwrite; other cases ignore it.  Two sizes are accepted:
+ * tl_b200_mla_decode_paged_workspace_bytes(batch), the minimum (one int32 per sequence), runs one
+ * CTA pair per sequence, longest first;                                                        */
 int64_t tl_b200_mla_decode_paged_workspace_bytes(int64_t batch);
-/* Workspace size that additionally lets small batches be split along the sequence (split-KV with
- * an LSE combine, as examples/deepseek_mla/example_mla_decode_paged.py:99-221 does): when the
- * batch alone gives fewer CTAs than SMs and the workspace passed to tl_b200_mla_decode_paged is
- * at least this large, every sequence is cut into chunks handled by separate CTAs and a second
- * kernel combines their partial results.  Equals the plain size when no split would be used.  */
+/* ... and this larger size (about 145 KB per sequence plus 39 MB) selects the persistent kernel:
+ * the query is cut into its two e4m3 terms once per call, the (sequence, 64-token tile) pairs are
+ * dealt out in equal contiguous ranges to one CTA pair per two SMs whatever the batch size, and
+ * sequences cut by a range boundary are merged from fp32 partials by their log-sum-exp (split-KV
+ * as in examples/deepseek_mla/example_mla_decode_paged.py:99-221).  Equals the minimum when the
+ * persistent kernel cannot be used (batch above 4096).  max_pages_per_seq and page_size are
+ * accepted for symmetry with the call and do not change the size.                              */
 int64_t tl_b200_mla_decode_paged_split_workspace_bytes(int64_t batch, int64_t max_pages_per_seq,
                                                        int64_t page_size);
 int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, const float* kv_scale,

@@ -14,9 +14,14 @@
 // de-quantised elementwise.  The per-token scale multiplies the S columns after the first MMA
 // and the P columns before the second.  Q (bf16/fp16) and P are each split into two e4m3 terms
 // (value + residual, one scale per head for Q), so both products keep ~8 mantissa bits; Q's
-// residual term and P live in tensor memory and enter the MMAs as the A operand from there.  The fp32 O accumulator for 128 heads x 512 columns alone would fill tensor
-// memory, so two CTAs share a sequence, each owning 256 output columns (S is computed by both).
-// Sequences are ordered longest-first by a small pre-kernel (scratch: one int32 per sequence).
+// residual term and P live in tensor memory and enter the MMAs as the A operand from there.
+// The fp32 O accumulator for 128 heads x 512 columns alone would fill tensor memory, so two CTAs
+// share a sequence, each owning 256 output columns (S is computed by both).
+//
+// Two kernels run this arithmetic.  The one in this file takes one CTA pair per sequence, longest
+// sequence first (a small pre-kernel orders them; scratch: one int32 per sequence), and cuts the
+// query inside every CTA; it needs almost no workspace and serves the allocation-free entry point.
+// mla_persistent.cu holds the persistent, work-balanced kernel that the large workspace selects.
 //
 // Other shapes / cache dtypes run a one-thread-per-(sequence, head) FMA kernel.
 #include "mla_common.cuh"

@@ -119,9 +119,9 @@ def mla_decode(dev, rank, world, peaks, batch=128, heads=128, d=576, dv=512, pag
     tokens = int(lens_all.sum())
     flops = 2.0 * tokens * heads * (d + dv)
     nbytes = tokens * (d + 4) + batch * heads * (d + dv) * 2
-    e = _entry("mla_decode_fp8_kernel", f"e4m3 paged cache, batch {batch}, {heads} heads, d {d}, dv {dv}, page {page}, "
+    e = _entry("mla_decode_persistent_kernel", f"e4m3 paged cache, batch {batch}, {heads} heads, d {d}, dv {dv}, page {page}, "
                f"lengths U[{lo_len},{hi_len}] ({tokens} tokens)", nbytes, 1e9, "GB/s", ms, ms_g, peaks["hbm_gbs"],
-               peaks["note"], f"sequences / {world} (balanced by length)", 2)
+               peaks["note"], f"sequences / {world} (balanced by length)", 3)     # prepare, decode, merge
     e["tflops"] = flops / (ms * 1e-3) / 1e12
     e["frac_of_bf16_tensor_peak"] = e["tflops"] / peaks["bf16_tflops"]
     return e
