@@ -33,6 +33,12 @@ for _p in (str(ROOT / "tilelang-tpu_b200"), str(ROOT)):
 
 import torch  # noqa: E402
 
+# DRAM bytes one SwiGLU launch moves per token, from one ncu capture of the 4096-token case
+# (profiles/swiglu_rope_rmsnorm_llama8b_4096tok.md: 301.8 MB for 4096 tokens; 86 016 algorithmic bytes
+# per token - the part of the output still dirty in L2 when the kernel ends is not counted).  Traffic
+# grows in proportion to the token count, so a launch is scaled from it.
+SWIGLU_DRAM_BYTES_PER_TOKEN = 301.8e6 / 4096
+
 METRIC = "GEMM/attn TFLOP/s and norm/RoPE GB/s vs B200 roofline at 1/2/4/8 GPUs"
 WORKLOAD = ("llama3-8b memory-bound ops, bf16, 8192 tokens: rmsnorm[8192x4096] + "
             "rope(Q[8192,32,128],K[8192,8,128]) + swiglu[8192x14336]")
@@ -321,7 +327,9 @@ def main():
                        "bytes_per_step_per_gpu": bytes_per_step},
             "roofline": {"bound": "hbm", "kernel": "swiglu_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
-                         "traffic": None, "avg_launch_ms": swiglu_ms},
+                         "traffic": SWIGLU_DRAM_BYTES_PER_TOKEN * tokens,
+                         "traffic_source": "dram__bytes of one ncu capture at 4096 tokens, scaled by the token count",
+                         "avg_launch_ms": swiglu_ms},
             "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms, "steps": e2e_steps},
             "gpu_launches": int(launches),
