@@ -278,26 +278,52 @@ def main():
     h2d = sum(v.numel() * v.element_size() for v in hin.values())
     d2h = sum(v.numel() * v.element_size() for v in hout.values())
 
-    def e2e_step():
-        dd = {k: v.to(dev, non_blocking=True) for k, v in hin.items()}
-        ops.rmsnorm(dd["x"], y, dd["weight"], eps=w["eps"])
-        ops.rope(dd["q"], dd["cos"], dd["sin"], qo)
-        ops.rope(dd["k"], dd["cos"], dd["sin"], ko)
-        ops.swiglu(dd["gate"], dd["up"], so)
-        hout["y"].copy_(y, non_blocking=True)
-        hout["qo"].copy_(qo, non_blocking=True)
-        hout["ko"].copy_(ko, non_blocking=True)
-        hout["so"].copy_(so, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+    # Three streams and two sets of device buffers: the host->device copy of step i+1 and the
+    # device->host copy of step i-1 run while step i computes (PCIe is full duplex).  Every step's copies
+    # are inside the timed region; nothing is reused from one step to the next.
+    s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    din = [{k: torch.empty_like(v, device=dev) for k, v in hin.items()} for _ in range(2)]
+    dout = [{"y": torch.empty_like(y), "qo": torch.empty_like(qo), "ko": torch.empty_like(ko), "so": torch.empty_like(so)}
+            for _ in range(2)]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_cmp = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
 
-    e2e_steps = max(1, min(steps, 10))
-    for _ in range(2):
-        e2e_step()
+    def e2e_steps_run(n):
+        for i in range(n):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(ev_cmp[b])            # the step that last read these inputs has computed
+                for k, v in hin.items():
+                    din[b][k].copy_(v, non_blocking=True)
+                ev_in[b].record(s_in)
+            with torch.cuda.stream(s_cmp):
+                s_cmp.wait_event(ev_in[b])
+                if i >= 2:
+                    s_cmp.wait_event(ev_out[b])           # its previous results are on the host
+                dd, oo = din[b], dout[b]
+                ops.rmsnorm(dd["x"], oo["y"], dd["weight"], eps=w["eps"])
+                ops.rope(dd["q"], dd["cos"], dd["sin"], oo["qo"])
+                ops.rope(dd["k"], dd["cos"], dd["sin"], oo["ko"])
+                ops.swiglu(dd["gate"], dd["up"], oo["so"])
+                ev_cmp[b].record(s_cmp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_cmp[b])
+                for k in ("y", "qo", "ko", "so"):
+                    hout[k].copy_(dout[b][k], non_blocking=True)
+                ev_out[b].record(s_out)
+        for st in (s_in, s_cmp, s_out):
+            torch.cuda.current_stream().wait_stream(st)
+
+    e2e_steps = max(2, min(steps, 20))
+    e2e_steps_run(2)
     barrier()
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
-    for _ in range(e2e_steps):
-        e2e_step()
+    for st in (s_in, s_cmp, s_out):
+        st.wait_event(s2)
+    e2e_steps_run(e2e_steps)
     e2.record()
     barrier()
     t2 = torch.tensor([s2.elapsed_time(e2)], dtype=torch.float64, device=dev)
@@ -307,7 +333,7 @@ def main():
     e2e_value = world * bytes_per_step / (e2e_ms * 1e-3) / 1e9
 
     # hand the big buffers back before the per-kernel section allocates its own
-    del hin, hout, d, y, qo, ko, so
+    del hin, hout, din, dout, d, y, qo, ko, so
     torch.cuda.empty_cache()
     peaks = measured_peaks()
     kernels = None

@@ -48,6 +48,7 @@ __global__ void __launch_bounds__(256, 2)
 mla_prepare_kernel(const MlaPrepParams p) {
   __shared__ __align__(16) uint8_t stage[32 * 528];       // residual units of 32 rows, pitch 33 units
   __shared__ float red[8];
+  dependency_release();                          // the decode kernel may set up its barriers and tensor memory meanwhile
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   if (blockIdx.x == 0) {
     // ---------------------------------------------------------------- schedule
@@ -287,7 +288,7 @@ mla_decode_persistent_kernel(const __grid_constant__ CUtensorMap tm_kv, const __
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int worker = blockIdx.x >> 1, half = blockIdx.x & 1;
-  const int4 sc = p.sched[worker];
+  dependency_release();                          // lets the merge kernel's blocks take their places early
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
@@ -319,6 +320,8 @@ mla_decode_persistent_kernel(const __grid_constant__ CUtensorMap tm_kv, const __
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
   auto stage_addr = [&](int s) { return sm_kv + s * (kMlaTile + 1024); };
+  dependency_wait();                             // everything below reads what the preparation kernel wrote
+  const int4 sc = p.sched[worker];
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -698,6 +701,7 @@ template <typename TQ>
 __global__ void __launch_bounds__(256)
 mla_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, const int4* __restrict__ sched,
                  const int2* __restrict__ seq_info, TQ* __restrict__ out, int heads) {
+  dependency_wait();                             // partials and schedule come from the kernels before
   const int4 sc = sched[blockIdx.x];
   if (sc.y == 0 || sc.z == sc.x) return;        // the first piece starts a sequence, or does not finish it
   const int b = sc.x;
@@ -771,13 +775,31 @@ static int mla_persistent_launch_t(const CUtensorMap& tm_kv, const CUtensorMap& 
                                    const MlaSchedParams& sp, const int2* seq_info, cudaStream_t s) {
   mla_prepare_kernel<TQ><<<(unsigned)(5 * pp.batch + 1), 256, 0, s>>>(pp);
   TL_LAUNCH_CHECK("mla_prepare_kernel");
+  // the decode and merge kernels are launched with programmatic stream serialization: each starts
+  // while its predecessor runs and waits inside (dependency_wait) before it reads the predecessor's output
+  cudaLaunchAttribute overlap[1];
+  overlap[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  overlap[0].val.programmaticStreamSerializationAllowed = 1;
   auto kernel = mla_decode_persistent_kernel<TQ>;
   TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmemP));
-  kernel<<<(unsigned)(2 * pp.workers), kMlaThreads, kMlaSmemP, s>>>(tm_kv, tm_q, sp);
-  TL_LAUNCH_CHECK("mla_decode_persistent_kernel");
-  dim3 mgrid((unsigned)pp.workers, (unsigned)((pp.heads + 7) / 8));
-  mla_merge_kernel<TQ><<<mgrid, 256, 0, s>>>(sp.part_o, sp.part_lse, sp.sched, seq_info, (TQ*)sp.out, pp.heads);
-  TL_LAUNCH_CHECK("mla_merge_kernel");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pp.workers));
+  cfg.blockDim = dim3(kMlaThreads);
+  cfg.dynamicSmemBytes = kMlaSmemP;
+  cfg.stream = s;
+  cfg.attrs = overlap;
+  cfg.numAttrs = 1;
+  TL_CUDA(cudaLaunchKernelEx(&cfg, kernel, tm_kv, tm_q, sp));
+  count_launch();
+  cudaLaunchConfig_t mcfg = {};
+  mcfg.gridDim = dim3((unsigned)pp.workers, (unsigned)((pp.heads + 7) / 8));
+  mcfg.blockDim = dim3(256);
+  mcfg.stream = s;
+  mcfg.attrs = overlap;
+  mcfg.numAttrs = 1;
+  TL_CUDA(cudaLaunchKernelEx(&mcfg, mla_merge_kernel<TQ>, (const float*)sp.part_o, (const float*)sp.part_lse,
+                             (const int4*)sp.sched, seq_info, (TQ*)sp.out, (int)pp.heads));
+  count_launch();
   return TL_B200_OK;
 }
 
