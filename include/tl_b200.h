@@ -132,6 +132,19 @@ int tl_b200_topk(const void* src, void* out_vals, int32_t* out_idx, int64_t rows
 int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
                  int in_dtype, int out_dtype, void* stream);
 
+/* ---- gated MLP, front half -----------------------------------------------------
+ * out[m,n] = silu(x Wg^T) * (x Wu^T) with x [m,k] and w_gate, w_up [n,k] row-major, all of
+ * `dtype`.  The arithmetic of the reference's MLP program up to its down projection
+ * (tpu_demo/ppl/mlp/mlp_bf16.py:103-125, mlp_fp32.py): both GEMMs accumulate in fp32 and
+ * deliver tiles of `dtype`, SiLU (g / (1 + exp(-g))) and the product run in fp32, and the
+ * result is rounded once more.  The two GEMMs share the x tiles and the SiLU-product is their
+ * epilogue, so neither intermediate is written to memory.  The down projection is
+ * tl_b200_gemm(out, w_down [hidden, n], y, m, hidden, n, trans_b = 1, ...).
+ * TL_F16 / TL_BF16 run on tcgen05 tensor cores when x, w_gate, w_up are 16-byte aligned and
+ * k % 8 == 0; other shapes and TL_F32 use an FMA kernel.                                  */
+int tl_b200_mlp_gate_up(const void* x, const void* w_gate, const void* w_up, void* out, int64_t m,
+                        int64_t n, int64_t k, int dtype, void* stream);
+
 /* ---- FP8 GEMM with 128-granular scales --------------------------------------------
  * c[m,n] = sum_kb scales_a[m,kb] * scales_b[n/128,kb] * (a[m, kb*128:(kb+1)*128] . b[n, same]),
  * a [m,k] and b [n,k] row-major e4m3, scales_a [m, k/128] and scales_b [ceil(n/128), k/128]

@@ -155,6 +155,21 @@ def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return (up.float() * F.silu(gate.float())).to(gate.dtype)
 
 
+# ---------------------------------------------------------------------------- gated MLP
+def mlp_gate_up(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """silu(x Wg^T) * (x Wu^T) with the roundings of the MLP program
+    (tpu_demo/ppl/mlp/mlp_bf16.py:103-125): both `ppl_gemm`s deliver tiles of the input dtype
+    (:103, :113), SiLU = g / (exp(-g) + 1) and the product run in fp32 (:44-54, :118), and the
+    product is cast back (:121).  The reference has no check function for this program; this is
+    the composition of `matmul` and `swiglu`, which are pinned to theirs."""
+    return swiglu(matmul(x, w_gate, transpose_b=True), matmul(x, w_up, transpose_b=True))
+
+
+def mlp(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """The whole tile program: down projection of `mlp_gate_up` (mlp_bf16.py:123-128), w_down (hidden, inter)."""
+    return matmul(mlp_gate_up(x, w_gate, w_up), w_down, transpose_b=True)
+
+
 # ---------------------------------------------------------------------------- reductions / elementwise
 def reduce_sum(x: torch.Tensor) -> torch.Tensor:
     """tpu_demo/tpu_test_reduce_sum.py:36 — row sum, keepdim; fp32 accumulate, cast back."""

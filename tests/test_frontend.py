@@ -59,6 +59,55 @@ def matmul_program(M, N, K, bm, bn, bk, dtype="float16", trans_b=False):
     return main_kernel_inner
 
 
+def mlp_program(rows, hidden, inter, block_rows, block_h=None, block_i=None, dtype="bfloat16"):
+    """Gated MLP written with the tile ops in the order of the reference's program: gate GEMM, SiLU
+    in fp32 (g / (exp(-g) + 1)), up GEMM, product, down GEMM; weights are (out_features, in_features)."""
+    bh, bi = block_h or hidden, block_i or inter
+
+    @T.prim_func
+    def main_kernel_inner(Y: T.Tensor((rows, hidden), dtype), X: T.Tensor((rows, hidden), dtype),
+                          Wg: T.Tensor((inter, hidden), dtype), Wu: T.Tensor((inter, hidden), dtype),
+                          Wd: T.Tensor((hidden, inter), dtype)):
+        with T.Kernel(T.ceildiv(rows, block_rows), T.ceildiv(hidden, bh), T.ceildiv(inter, bi), is_cpu=True) as (bx, by, bz):
+            x_t = T.alloc_shared((block_rows, bh), dtype)
+            wg_t = T.alloc_shared((bi, bh), dtype)
+            wu_t = T.alloc_shared((bi, bh), dtype)
+            wd_t = T.alloc_shared((bh, bi), dtype)
+            gate16 = T.alloc_shared((block_rows, bi), dtype)
+            up16 = T.alloc_shared((block_rows, bi), dtype)
+            act16 = T.alloc_shared((block_rows, bi), dtype)
+            y16 = T.alloc_shared((block_rows, bh), dtype)
+            gate = T.alloc_shared((block_rows, bi), "float32")
+            up = T.alloc_shared((block_rows, bi), "float32")
+            neg = T.alloc_shared((block_rows, bi), "float32")
+            one = T.alloc_shared((block_rows, bi), "float32")
+            den = T.alloc_shared((block_rows, bi), "float32")
+            silu = T.alloc_shared((block_rows, bi), "float32")
+            act = T.alloc_shared((block_rows, bi), "float32")
+            w0 = T.alloc_shared((block_rows, bi), "float32")
+            w1 = T.alloc_shared((block_rows, bi), "float32")
+            coeff = T.alloc_shared((64, 32), "float32")
+            table = T.alloc_shared((64, 192), "float32")
+            T.ppl_fill(one, T.float32(1.0))
+            T.ppl_copy(X[bx * block_rows:(bx + 1) * block_rows, by * bh:(by + 1) * bh], x_t)
+            T.ppl_copy(Wg[bz * bi:(bz + 1) * bi, by * bh:(by + 1) * bh], wg_t)
+            T.ppl_copy(Wu[bz * bi:(bz + 1) * bi, by * bh:(by + 1) * bh], wu_t)
+            T.ppl_copy(Wd[by * bh:(by + 1) * bh, bz * bi:(bz + 1) * bi], wd_t)
+            T.ppl_gemm(x_t, wg_t, gate16, transpose_B=True)
+            T.ppl_copy(gate16, gate)
+            T.ppl_mul_C(neg, gate, T.float32(-1.0))
+            T.ppl_exp2(neg, w0, w1, coeff, table)
+            T.ppl_add(den, neg, one)
+            T.ppl_div(silu, gate, den)
+            T.ppl_gemm(x_t, wu_t, up16, transpose_B=True)
+            T.ppl_copy(up16, up)
+            T.ppl_mul(act, silu, up)
+            T.ppl_copy(act, act16)
+            T.ppl_gemm(act16, wd_t, y16, transpose_B=True)
+            T.ppl_copy(y16, Y[bx * block_rows:(bx + 1) * block_rows, by * bh:(by + 1) * bh])
+    return main_kernel_inner
+
+
 def topk_program(length, K, descended=True):
     @T.prim_func
     def main_kernel_inner(Input: T.Tensor((length,), "float32"), Output: T.Tensor((length,), "float32"),
@@ -214,6 +263,16 @@ def test_compile_is_cached_per_program_object():
     assert tilelang.compile(f, out_idx=[1, 2], target="b200") is tilelang.compile(f, out_idx=[1, 2], target="b200")
 
 
+def test_mlp_program_binds_only_in_its_single_tile_form():
+    bound = bind(mlp_program(128, 256, 512, 64))
+    assert bound.program == "mlp" and bound.facts == dict(M=128, hidden=256, intermediate=512, dtype="bfloat16")
+    # tiles along the hidden or intermediate dimension overwrite each other in the program (no accumulator)
+    with pytest.raises(UnsupportedProgram, match="does not accumulate"):
+        bind(mlp_program(16, 16, 16, 8, 8, 8))
+    with pytest.raises(UnsupportedProgram, match="no tail masking"):
+        bind(mlp_program(100, 256, 512, 64))
+
+
 # ------------------------------------------------------------------ the reference's own demo programs
 def _reference_builder(rel_path: str, func_name: str):
     """Lift one program-builder function out of a reference demo script (the script itself builds
@@ -242,6 +301,7 @@ DEMOS = [
     ("tpu_demo/tpu_test_topk_fp32.py", "topk_kernel", (1024, 8), "topk"),
     ("tpu_demo/tpu_test_gather_fp32.py", "gather_kernel", (128, 64, 8), "gather"),
     ("tpu_demo/tpu_test_sigmoid_fp32.py", "sigmoid_kernel", (32, 32, 1024, 1024), "sigmoid"),
+    ("tpu_demo/ppl/mlp/mlp_bf16.py", "deepseek_v3_mlp_bf16", (64, 256, 512, 128, 256, 512), "mlp"),
     ("tpu_demo/ppl/elementwise_add_kernel/elementwise_add.py", "elementwise_add",
      (128, 128, 32, 32, "float32", "float32", 128), "elementwise_add"),
 ]

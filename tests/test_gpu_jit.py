@@ -6,7 +6,7 @@ import torch
 import oracle.ops as O
 import tilelang
 import tilelang.language as T
-from test_frontend import matmul_program, rms_norm_program, topk_program
+from test_frontend import matmul_program, mlp_program, rms_norm_program, topk_program
 
 pytestmark = pytest.mark.gpu
 
@@ -93,3 +93,17 @@ def test_profiler_consistency_and_bench(cuda_device):
     prof = kernel.get_profiler()
     prof.assert_consistent(repeat=3)
     assert prof.do_bench(rep=3) > 0
+
+
+def test_mlp_program(cuda_device):
+    """Output first in the parameter list, as in the reference's MLP program."""
+    rows, hidden, inter = 128, 256, 512
+    kernel = tilelang.compile(mlp_program(rows, hidden, inter, 64), out_idx=0, target="b200")
+    g = gen(8)
+    x = torch.randn(rows, hidden, generator=g).bfloat16()
+    wg = (torch.randn(inter, hidden, generator=g) / hidden ** 0.5).bfloat16()
+    wu = (torch.randn(inter, hidden, generator=g) / hidden ** 0.5).bfloat16()
+    wd = (torch.randn(hidden, inter, generator=g) / inter ** 0.5).bfloat16()
+    y = torch.zeros(rows, hidden).bfloat16()
+    assert kernel(y, x, wg, wu, wd) == 0
+    assert torch.allclose(y.float(), O.mlp(x, wg, wu, wd).float(), atol=2e-2, rtol=2e-2)

@@ -46,6 +46,7 @@ PROTOTYPES = {
     "tl_b200_mla_decode_paged_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                                  c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_void_p]),
     "tl_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
+    "tl_b200_mlp_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
 }
 
 

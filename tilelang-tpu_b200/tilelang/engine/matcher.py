@@ -215,6 +215,64 @@ def _match_swiglu(func: PrimFunc):
     return BoundKernel("swiglu", "tl_b200_swiglu", run, dict(shape=list(G.shape), dtype=G.dtype))
 
 
+_MLP = ["ppl.fill", "ppl.copy", "ppl.copy", "ppl.copy", "ppl.copy", "ppl.gemm", "ppl.copy", "ppl.mul_C", "ppl.exp",
+        "ppl.add", "ppl.div", "ppl.gemm", "ppl.copy", "ppl.mul", "ppl.copy", "ppl.gemm", "ppl.copy"]
+
+
+def _match_mlp(func: PrimFunc):
+    """The gated MLP tile program (tpu_demo/ppl/mlp/mlp_bf16.py:56-137): gate GEMM -> SiLU, up GEMM,
+    product, down GEMM.  Bound to the fused gate/up kernel plus one GEMM."""
+    if _names(func.ops) != _MLP or len(func.params) != 5:
+        return None
+    (fill, ld_x, ld_g, ld_u, ld_d, gemm_g, cv_g, neg, ex, add1, div, gemm_u, cv_u, mul, cv_a, gemm_d, store) = func.ops
+    ones = fill.args[0]
+    x_t, g_t, u_t, d_t = (_buf(o.args[1]) for o in (ld_x, ld_g, ld_u, ld_d))
+    g32, u32 = _buf(cv_g.args[1]), _buf(cv_u.args[1])
+    silu = div.args[0]
+    ok = (fill.args[1] == 1.0
+          and gemm_g.args[0] is x_t and gemm_g.args[1] is g_t and _buf(cv_g.args[0]) is gemm_g.args[2]
+          and neg.args[1] is g32 and neg.args[2] == -1.0 and ex.args[0] is neg.args[0]
+          and add1.args[1] is neg.args[0] and add1.args[2] is ones
+          and div.args[1] is g32 and div.args[2] is add1.args[0]
+          and gemm_u.args[0] is x_t and gemm_u.args[1] is u_t and _buf(cv_u.args[0]) is gemm_u.args[2]
+          and {id(mul.args[1]), id(mul.args[2])} == {id(silu), id(u32)}
+          and _buf(cv_a.args[0]) is mul.args[0] and gemm_d.args[0] is _buf(cv_a.args[1]) and gemm_d.args[1] is d_t
+          and _buf(store.args[0]) is gemm_d.args[2])
+    if not ok:
+        return None
+    srcs = [ld_x.args[0], ld_g.args[0], ld_u.args[0], ld_d.args[0], store.args[1]]
+    if not all(_is_param(r, func) for r in srcs):
+        return None
+    for g in (gemm_g, gemm_u, gemm_d):
+        _require(g.attrs["transpose_B"] and not g.attrs["transpose_A"],
+                 "mlp: the weights are (out_features, in_features) tiles used with transpose_B=True")
+    X, Wg, Wu, Wd, Out = (_buf(r) for r in srcs)
+    _require(all(len(b.shape) == 2 for b in (X, Wg, Wu, Wd, Out)), "mlp: tensors must be 2-D")
+    M, H = X.shape
+    I = Wg.shape[0]
+    _require(tuple(Wg.shape) == (I, H) and tuple(Wu.shape) == (I, H) and tuple(Wd.shape) == (H, I)
+             and tuple(Out.shape) == (M, H), "mlp: inconsistent x / weight / output shapes")
+    _require(len({b.dtype for b in (X, Wg, Wu, Wd, Out)}) == 1, "mlp: one 16-bit dtype for all tensors")
+    bs, bh = x_t.shape
+    bi = g_t.shape[0]
+    _check_tiling(func, "mlp", [(M, bs)])
+    # The program keeps no accumulator across tiles of the hidden or intermediate dimension (every
+    # (by, bz) tile overwrites the same output block), so only its single-tile form is the MLP.
+    _require(bh == H and bi == I, "mlp: the program does not accumulate across hidden / intermediate tiles; "
+                                  "Block_h and Block_i must span the whole dimensions")
+    _require(sorted(_grid(func)) == sorted([M // bs, 1, 1]), "mlp: the grid must cover the rows")
+    ix, ig, iu, idn, io = (b.param_index for b in (X, Wg, Wu, Wd, Out))
+    from .. import ops as native
+
+    def run(*t):
+        act = torch.empty((M, I), dtype=t[ix].dtype, device=t[ix].device)     # silu(gate) * up, never a kernel output
+        rc = native.mlp_gate_up(t[ix], t[ig], t[iu], act)
+        return rc or native.gemm(act, t[idn], t[io], transpose_b=True)
+
+    return BoundKernel("mlp", "tl_b200_mlp_gate_up + tl_b200_gemm", run,
+                       dict(M=M, hidden=H, intermediate=I, dtype=X.dtype))
+
+
 def _match_reduce(func: PrimFunc):
     n = [x for x in _names(func.ops) if x != "ppl.fill"]
     if len(n) != 3 or n[0] != "ppl.copy" or n[2] != "ppl.copy" or n[1] not in ("ppl.reduce_sum", "ppl.reduce_max"):
@@ -384,7 +442,7 @@ def _match_mla_decode(func: PrimFunc):
                        dict(batch=b, heads=h, seqlen_kv=s, dim=dim, pe_dim=pe, scale=scale, dtype=Q.dtype))
 
 
-_MATCHERS = [_match_matmul, _match_rmsnorm, _match_rope, _match_swiglu, _match_reduce, _match_topk, _match_gather,
+_MATCHERS = [_match_matmul, _match_rmsnorm, _match_rope, _match_swiglu, _match_mlp, _match_reduce, _match_topk, _match_gather,
              _match_elementwise, _match_flash_attention, _match_mla_decode]
 
 
@@ -396,5 +454,5 @@ def bind(func: PrimFunc) -> BoundKernel:
             return bound
     raise UnsupportedProgram(
         "this ppl_* program does not match any kernel of the b200 library (matmul, rmsnorm, "
-        "rmsnorm split-K, rope, swiglu, row reduce, top-k, gather, sigmoid, elementwise, flash "
+        "rmsnorm split-K, rope, swiglu, gated MLP, row reduce, top-k, gather, sigmoid, elementwise, flash "
         "attention forward, MLA decode); there is no CPU fallback.  Recorded program:\n" + func.script())

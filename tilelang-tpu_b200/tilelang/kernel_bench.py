@@ -71,6 +71,33 @@ def gemm_fp8(dev, rank, world, peaks, m=8192, n=28672, k=8192):
                   "2 x " + peaks["note"] + " (no FP8 peak was measured)", f"N columns / {world}", 1)
 
 
+def mlp_gate_up(dev, rank, world, peaks, m=8192, n=14336, k=4096):
+    """Front half of the Llama-3-8B MLP: silu(x Wg^T) * (x Wu^T) in one kernel, against the two GEMMs plus the
+    SwiGLU pass it replaces.  Sharded by output columns like the GEMM."""
+    lo, hi = parallel.partition(n, world, rank, 128)
+    nl = hi - lo
+    g = torch.Generator(device=dev).manual_seed(5)
+    x = torch.randn(m, k, generator=g, device=dev).bfloat16()
+    wg = (torch.randn(nl, k, generator=g, device=dev) * k ** -0.5).bfloat16()
+    wu = (torch.randn(nl, k, generator=g, device=dev) * k ** -0.5).bfloat16()
+    out = torch.empty(m, nl, dtype=torch.bfloat16, device=dev)
+    gate, up = torch.empty_like(out), torch.empty_like(out)
+    ms = _time(lambda: ops.mlp_gate_up(x, wg, wu, out), world)
+
+    def unfused():
+        ops.gemm(x, wg, gate, True)
+        ops.gemm(x, wu, up, True)
+        ops.swiglu(gate, up, out)
+
+    ms_u = _time(unfused, world)
+    ms_g = _time(lambda: (ops.mlp_gate_up(x, wg, wu, out), parallel.all_gather_cat(out, 1)), world, reps=2, warmup=1) \
+        if world > 1 else ms
+    e = _entry("mlp_gate_up_tcgen05_kernel", f"bf16 M{m} K{k} N{n}: silu(x Wg^T) * (x Wu^T), weights [N,K]",
+               4.0 * m * n * k, 1e12, "TFLOP/s", ms, ms_g, peaks["bf16_tflops"], peaks["note"], f"N columns / {world}", 1)
+    e["ms_unfused_two_gemms_plus_swiglu"] = ms_u
+    return e
+
+
 def flash_attn(dev, rank, world, peaks, b=4, s=4096, h=32, d=128):
     lo, hi = parallel.partition(h, world, rank)
     hl = hi - lo
@@ -129,7 +156,7 @@ def mla_decode(dev, rank, world, peaks, batch=128, heads=128, d=576, dv=512, pag
 
 def run_all(dev, rank, world, peaks):
     out = []
-    for fn in (gemm_bf16, gemm_fp8, flash_attn, mla_decode):
+    for fn in (gemm_bf16, gemm_fp8, mlp_gate_up, flash_attn, mla_decode):
         try:
             out.append(fn(dev, rank, world, peaks))
         except Exception as exc:       # a failing extra must not lose the headline line
@@ -141,6 +168,7 @@ def run_all(dev, rank, world, peaks):
 SMALL = {      # reduced shapes for profiler captures: inputs above the 126 MB L2, a few hundred MB on the device
     "gemm_bf16": dict(m=4096, n=8192, k=4096),
     "gemm_fp8": dict(m=4096, n=8192, k=4096),
+    "mlp_gate_up": dict(m=4096, n=4096, k=4096),
     "flash_attn": dict(b=2, s=4096, h=16, d=128),
     "mla_decode": dict(batch=32),
 }

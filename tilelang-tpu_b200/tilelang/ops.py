@@ -203,6 +203,26 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, transpose_b: bool = 
                                         dtype_code(a.dtype), dtype_code(c.dtype), s), "tl_b200_gemm")
 
 
+def mlp_gate_up(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, out: torch.Tensor) -> int:
+    """out = silu(x @ w_gate.T) * (x @ w_up.T): x (M, K), w_gate and w_up (N, K), out (M, N), one dtype.
+    Both products are rounded to that dtype before the fp32 SiLU-product, as the MLP program does."""
+    if x.dim() != 2 or w_gate.dim() != 2 or tuple(w_up.shape) != tuple(w_gate.shape):
+        raise ValueError("mlp_gate_up: x (M, K), w_gate and w_up (N, K)")
+    m, k = x.shape
+    n = w_gate.shape[0]
+    if w_gate.shape[1] != k:
+        raise ValueError("gemm K shape check failed")          # message of ppl_gemm's assert
+    if tuple(out.shape) != (m, n):
+        raise ValueError(f"mlp_gate_up: out must be ({m}, {n})")
+    if not (x.dtype == w_gate.dtype == w_up.dtype == out.dtype):
+        raise ValueError("mlp_gate_up: all tensors must share a dtype")
+    if x.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+        raise ValueError(f"mlp_gate_up: unsupported dtype {x.dtype}")
+    s = _prepare(x, w_gate, w_up, out)
+    return N.check(N.load().tl_b200_mlp_gate_up(_ptr(x), _ptr(w_gate), _ptr(w_up), _ptr(out), m, n, k,
+                                               dtype_code(x.dtype), s), "tl_b200_mlp_gate_up")
+
+
 _MASK_MODES = {False: 0, None: 0, "none": 0, True: 1, "causal": 1, "block": 2}
 
 
