@@ -175,29 +175,29 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       const uint32_t idesc_o = make_idesc(p.in_fmt, p.in_fmt, false, true, kFaBM, HD);       // O += P V
       bool ok = mbar_wait(bar_q, 0, abort_flag);
 
+      // descriptors are built once; every MMA's operands are a constant byte offset further on
+      const uint64_t q_desc = smem_desc_sw128(sm_q, 16, 1024), k_desc = smem_desc_sw128(sm_k, 16, 1024);
+      const uint64_t v_desc = smem_desc_sw128(sm_v, kFaBN * 128, 1024);
       auto s_col = [&](int l, int j) { return tmem_base + Cfg::kColS + l * 128 + (j & 1) * kFaBN; };
       auto issue_s = [&](int l, int j) {       // S_l(j) = Q_l K_j^T, K dimension = head dim
-        const int st = j % kFaStages;
+        const uint64_t a0 = desc_at(q_desc, l * Cfg::kQLane), b0 = desc_at(k_desc, (j % kFaStages) * Cfg::kKV);
+        const uint32_t d = s_col(l, j);
 #pragma unroll
         for (int s = 0; s < Cfg::kSlabs; ++s)
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t a = smem_desc_sw128(sm_q + l * Cfg::kQLane + s * (kFaBM * 128) + kk * 32, 16, 1024);
-            const uint64_t bd = smem_desc_sw128(sm_k + st * Cfg::kKV + s * (kFaBN * 128) + kk * 32, 16, 1024);
-            mma_f16_ss(s_col(l, j), a, bd, idesc_s, (s | kk) ? 1u : 0u);
-          }
+          for (int kk = 0; kk < 4; ++kk)
+            mma_f16_ss(d, desc_at(a0, s * (kFaBM * 128) + kk * 32), desc_at(b0, s * (kFaBN * 128) + kk * 32), idesc_s,
+                       (s | kk) ? 1u : 0u);
         mma_commit(bar_sfull + 8 * (2 * l + (j & 1)));
       };
       auto issue_pv = [&](int l, int j) {      // O_l += P_l(j) V_j; P comes from tensor memory
-        const int st = j % kFaStages;
-        const uint32_t d = tmem_base + Cfg::kColO + l * HD;
+        const uint64_t b0 = desc_at(v_desc, (j % kFaStages) * Cfg::kKV);
+        const uint32_t d = tmem_base + Cfg::kColO + l * HD, a = s_col(l, j);
 #pragma unroll
-        for (int kk = 0; kk < kFaBN / 16; ++kk) {
+        for (int kk = 0; kk < kFaBN / 16; ++kk)
           // A: 16 keys of P = 8 columns of packed 16-bit pairs.  B: V tile, 64-column slabs
           // (leading offset), 8-key groups 1 KB apart, 16 keys = 2 KB
-          const uint64_t bd = smem_desc_sw128(sm_v + st * Cfg::kKV + kk * 2048, kFaBN * 128, 1024);
-          mma_f16_ts(d, s_col(l, j) + kk * 8, bd, idesc_o, (j | kk) ? 1u : 0u);
-        }
+          mma_f16_ts(d, a + kk * 8, desc_at(b0, kk * 2048), idesc_o, (j | kk) ? 1u : 0u);
         mma_commit(bar_pvdone + 8 * (2 * l + (j & 1)));
       };
       auto last_lane = [&](int j) { return j < n_lane[1] ? 1 : 0; };   // issue order is lane 0, lane 1

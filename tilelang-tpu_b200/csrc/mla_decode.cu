@@ -144,32 +144,32 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     if (elect_one() && n_tiles > 0) {
       const uint32_t idesc_s = make_idesc(kFmtE4M3, kFmtE4M3, false, false, kMlaHeads, kMlaBN);
       const uint32_t idesc_o = make_idesc(kFmtE4M3, kFmtE4M3, false, true, kMlaHeads, 256);
+      // descriptors are built once; every MMA's operands are a constant byte offset further on
+      const uint64_t q_desc = smem_desc_sw128(sm_q, 16, 1024), k_desc = smem_desc_sw128(sm_kv, 16, 1024);
+      const uint64_t v_desc = smem_desc_sw128(sm_kv, kMlaBN * 128, 1024);
       bool ok = true;
       auto issue_s = [&](int j) {
         const int st = j % kMlaStages;
         if (!(ok = mbar_wait(bar_kvfull + 8 * st, (j / kMlaStages) & 1, abort_flag))) return;
         tc_fence_after_sync();
-        const uint32_t kv = stage_addr(st);
+        const uint64_t kd = desc_at(k_desc, st * (kMlaTile + 1024));        // this stage, K-major view
         const uint32_t d = tmem_base + kMlaColS + (j & 1) * kMlaBN;
         // value term of Q (shared memory) x K, all 576 columns
 #pragma unroll
         for (int kk = 0; kk < kMlaD / 32; ++kk) {
-          const uint64_t a = smem_desc_sw128(sm_q + (kk / 4) * (kMlaHeads * 128) + (kk % 4) * 32, 16, 1024);
-          const uint64_t bd = smem_desc_sw128(kv + (kk / 4) * (kMlaBN * 128) + (kk % 4) * 32, 16, 1024);
-          mma_f8_ss(d, a, bd, idesc_s, kk ? 1u : 0u);
+          mma_f8_ss(d, desc_at(q_desc, (kk / 4) * (kMlaHeads * 128) + (kk % 4) * 32),
+                    desc_at(kd, (kk / 4) * (kMlaBN * 128) + (kk % 4) * 32), idesc_s, kk ? 1u : 0u);
         }
         // residual term of Q x K: columns 0..511 from tensor memory (8 columns per 32-byte step) ...
 #pragma unroll
         for (int kk = 0; kk < 16; ++kk) {
-          const uint64_t bd = smem_desc_sw128(kv + (kk / 4) * (kMlaBN * 128) + (kk % 4) * 32, 16, 1024);
-          mma_f8_ts(d, tmem_base + kMlaColQlo + kk * 8, bd, idesc_s, 1u);
+          mma_f8_ts(d, tmem_base + kMlaColQlo + kk * 8, desc_at(kd, (kk / 4) * (kMlaBN * 128) + (kk % 4) * 32), idesc_s, 1u);
         }
         // ... columns 512..575 from the upper half of Q slab 4
 #pragma unroll
         for (int kk = 0; kk < 2; ++kk) {
-          const uint64_t a = smem_desc_sw128(sm_q + 4 * (kMlaHeads * 128) + 64 + kk * 32, 16, 1024);
-          const uint64_t bd = smem_desc_sw128(kv + 4 * (kMlaBN * 128) + kk * 32, 16, 1024);
-          mma_f8_ss(d, a, bd, idesc_s, 1u);
+          mma_f8_ss(d, desc_at(q_desc, 4 * (kMlaHeads * 128) + 64 + kk * 32), desc_at(kd, 4 * (kMlaBN * 128) + kk * 32),
+                    idesc_s, 1u);
         }
         mma_commit(bar_sfull + 8 * (j & 1));
       };
@@ -179,15 +179,14 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (!(ok = mbar_wait(bar_pfull + 8 * (j & 1), (j >> 1) & 1, abort_flag))) break;
         tc_fence_after_sync();
-        const uint32_t kv = stage_addr(j % kMlaStages);
+        const uint64_t vd = desc_at(v_desc, (j % kMlaStages) * (kMlaTile + 1024) + (2 * half) * (kMlaBN * 128));
         const uint32_t pa = tmem_base + kMlaColS + (j & 1) * kMlaBN;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           // A: P row = [value(64 tokens) | residual(64 tokens)] in 32 columns, 8 columns per step.
           // B: this half's 256 V columns = two 128-column slabs (8 KB apart), 32 tokens = 4 KB per
           // step; the residual steps reuse the same tokens.
-          const uint64_t bd = smem_desc_sw128(kv + (2 * half) * (kMlaBN * 128) + (kk & 1) * 4096, kMlaBN * 128, 1024);
-          mma_f8_ts(tmem_base + kMlaColO, pa + kk * 8, bd, idesc_o, (j | kk) ? 1u : 0u);
+          mma_f8_ts(tmem_base + kMlaColO, pa + kk * 8, desc_at(vd, (kk & 1) * 4096), idesc_o, (j | kk) ? 1u : 0u);
         }
         mma_commit(bar_pvdone + 8 * (j & 1));
         mma_commit(bar_kvempty + 8 * (j % kMlaStages));

@@ -148,6 +148,17 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_
   return d;
 }
 
+// The descriptor of the same layout `byte_offset` further on (a multiple of 16 that stays inside
+// the 256 KB window): only the start-address field changes, so this is one 32-bit add on the low
+// word.  The single MMA-issuing thread runs a few instructions per MMA; building every descriptor
+// from scratch costs more issue time than a small MMA takes on the tensor core.
+__device__ __forceinline__ uint64_t desc_at(uint64_t base_desc, uint32_t byte_offset) {
+  const uint32_t lo = (uint32_t)base_desc + (byte_offset >> 4), hi = (uint32_t)(base_desc >> 32);
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // Instruction descriptor for kind::f16 / kind::f8f6f4 with fp32 accumulation:
 // c_format (bits 4-5) = 1 (F32); a_format bits 7-9, b_format bits 10-12; a_major bit 15, b_major
 // bit 16 (0 = K-major, 1 = MN-major); N >> 3 in bits 17-22; M >> 4 in bits 24-28.
