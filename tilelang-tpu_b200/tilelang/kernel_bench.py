@@ -158,7 +158,14 @@ def run_all(dev, rank, world, peaks):
     out = []
     for fn in (gemm_bf16, gemm_fp8, mlp_gate_up, flash_attn, mla_decode):
         try:
-            out.append(fn(dev, rank, world, peaks))
+            e = fn(dev, rank, world, peaks)
+            if world > 1 and e.get("peak"):       # `value` is the whole job: compare with the peak of all GPUs
+                e["peak"] *= world
+                e["frac_of_peak"] = e["value"] / e["peak"]
+                e["peak_source"] += f", x {world} GPUs"
+                if "frac_of_bf16_tensor_peak" in e:
+                    e["frac_of_bf16_tensor_peak"] /= world
+            out.append(e)
         except Exception as exc:       # a failing extra must not lose the headline line
             out.append({"kernel": fn.__name__, "error": f"{type(exc).__name__}: {exc}"})
         torch.cuda.empty_cache()
