@@ -42,6 +42,30 @@ void count_launch(int n = 1);
     ::tl::count_launch();                                                                  \
   } while (0)
 
+// Programmatic dependent launch.  A kernel launched through launch_overlapped() may be scheduled
+// while the kernel before it in the stream still runs; it calls dependency_wait() before it touches
+// global memory (returns once that whole grid has finished and its writes are visible; returns at
+// once when the predecessor was launched normally), so dependent chains stay correct and what
+// overlaps is launch latency and CTA ramp-up.  dependency_release() lets the successor start.
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                                     Args... args) {
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline int dtype_bytes(int dtype) {

@@ -47,6 +47,8 @@ template <typename T, int VB, int TPR, int VPT>
 __global__ void __launch_bounds__(kThreads)
 rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y, int64_t rows,
                int nvec, float inv_cols, float eps) {
+  dependency_wait();             // launched so that it may start under its predecessor's tail
+  dependency_release();
   using V = VecT<T, VB>;
   constexpr int VN = V::N;
   constexpr int ROWS_PER_CTA = kThreads / TPR;
@@ -142,8 +144,8 @@ static int launch_rmsnorm(const void* x, const void* w, void* y, int64_t rows, i
                           float eps, cudaStream_t s) {
   constexpr int RPC = kThreads / TPR;
   int64_t grid = (rows + RPC - 1) / RPC;
-  rmsnorm_kernel<T, VB, TPR, VPT><<<(unsigned)grid, kThreads, 0, s>>>(
-      (const T*)x, (const T*)w, (T*)y, rows, nvec, inv_cols, eps);
+  TL_CUDA(launch_overlapped(rmsnorm_kernel<T, VB, TPR, VPT>, dim3((unsigned)grid), dim3(kThreads), 0, s, (const T*)x,
+                            (const T*)w, (T*)y, rows, nvec, inv_cols, eps));
   TL_LAUNCH_CHECK("rmsnorm_kernel");
   return TL_B200_OK;
 }
@@ -236,6 +238,8 @@ template <typename T, int VB, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
 rope_kernel(const T* __restrict__ x, const T* __restrict__ cos_tab, const T* __restrict__ sin_tab,
             T* __restrict__ out, uint32_t total_vec, uint32_t vec_per_row, uint32_t vec_per_table_row) {
+  dependency_wait();             // launched so that it may start under its predecessor's tail
+  dependency_release();
   using V = VecT<T, VB>;
   constexpr int VN = V::N;
   const uint32_t stride = gridDim.x * kThreads;
@@ -313,8 +317,8 @@ static int launch_rope(const void* x, const void* c, const void* sn, void* out, 
   const int64_t total_vec = rows * vpr;
   auto kernel = rope_kernel<T, VB, UNROLL>;
   unsigned grid = resident_grid(kernel, total_vec, kThreads * UNROLL);
-  kernel<<<grid, kThreads, 0, s>>>((const T*)x, (const T*)c, (const T*)sn, (T*)out, (uint32_t)total_vec,
-                                   (uint32_t)vpr, (uint32_t)(vpr * rptr));
+  TL_CUDA(launch_overlapped(kernel, dim3(grid), dim3(kThreads), 0, s, (const T*)x, (const T*)c, (const T*)sn, (T*)out,
+                            (uint32_t)total_vec, (uint32_t)vpr, (uint32_t)(vpr * rptr)));
   TL_LAUNCH_CHECK("rope_kernel");
   return TL_B200_OK;
 }
@@ -354,6 +358,8 @@ template <typename T, int VB, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
 swiglu_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out, int64_t nvec,
               int64_t n_elems) {
+  dependency_wait();             // launched so that it may start under its predecessor's tail
+  dependency_release();
   using V = VecT<T, VB>;
   constexpr int VN = V::N;
   const int64_t stride = (int64_t)gridDim.x * kThreads;
@@ -400,7 +406,7 @@ static int launch_swiglu(const void* g, const void* u, void* o, int64_t n, cudaS
   int64_t nvec = n * (int64_t)sizeof(T) / VB;
   auto kernel = swiglu_kernel<T, VB, UNROLL>;
   unsigned grid = resident_grid(kernel, nvec, kThreads * UNROLL);
-  kernel<<<grid, kThreads, 0, s>>>((const T*)g, (const T*)u, (T*)o, nvec, n);
+  TL_CUDA(launch_overlapped(kernel, dim3(grid), dim3(kThreads), 0, s, (const T*)g, (const T*)u, (T*)o, nvec, n));
   TL_LAUNCH_CHECK("swiglu_kernel");
   return TL_B200_OK;
 }

@@ -299,12 +299,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
-// start while the kernel before it in the stream still runs; it must not touch that kernel's results
-// before dependency_wait() returns (which is when that whole grid has finished and its writes are
-// visible).  The earlier kernel lets the later one begin launching with dependency_release().
-__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
