@@ -10,6 +10,8 @@ when causal (examples/flash_attention/example_mha_fwd_bshd.py:197-200), MLA deco
 """
 from __future__ import annotations
 
+import time
+
 import torch
 import torch.distributed as dist
 
@@ -169,6 +171,7 @@ def run_all(dev, rank, world, peaks):
         except Exception as exc:       # a failing extra must not lose the headline line
             out.append({"kernel": fn.__name__, "error": f"{type(exc).__name__}: {exc}"})
         torch.cuda.empty_cache()
+        time.sleep(1.0)                # each entry is a burst figure: let the power limiter settle after the last one
     return out
 
 
