@@ -128,9 +128,24 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       mbar_init(bar_pvdone + 8 * i, 1);
     }
     mbar_fence_init();
-    prefetch_tensormap(&tm_q);
-    prefetch_tensormap(&tm_k);
-    prefetch_tensormap(&tm_v);
+    // Q and the first ring of K and V tiles are requested here, before the CTA meets for the tensor
+    // memory allocation: fresh stages need no empty-wait, and only this thread has seen the barriers.
+    mbar_expect_tx(bar_q, 2 * Cfg::kQLane);
+#pragma unroll
+    for (int l = 0; l < 2; ++l)
+#pragma unroll
+      for (int s = 0; s < Cfg::kSlabs; ++s)
+        tma_load_4d(sm_q + l * Cfg::kQLane + s * (kFaBM * 128), &tm_q, bar_q, s * 64, head, q0 + l * kFaBM, b);
+    for (int j = 0; j < min(n_total, kFaStages); ++j) {
+      mbar_expect_tx(bar_kfull + 8 * j, Cfg::kKV);
+#pragma unroll
+      for (int s = 0; s < Cfg::kSlabs; ++s)
+        tma_load_4d(sm_k + j * Cfg::kKV + s * (kFaBN * 128), &tm_k, bar_kfull + 8 * j, s * 64, head, j * kFaBN, b);
+      mbar_expect_tx(bar_vfull + 8 * j, Cfg::kKV);
+#pragma unroll
+      for (int s = 0; s < Cfg::kSlabs; ++s)
+        tma_load_4d(sm_v + j * Cfg::kKV + s * (kFaBN * 128), &tm_v, bar_vfull + 8 * j, s * 64, head, j * kFaBN, b);
+    }
   }
   if (warp == 2) {
     tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
@@ -144,14 +159,8 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (elect_one()) {
-      mbar_expect_tx(bar_q, 2 * Cfg::kQLane);
-#pragma unroll
-      for (int l = 0; l < 2; ++l)
-#pragma unroll
-        for (int s = 0; s < Cfg::kSlabs; ++s)
-          tma_load_4d(sm_q + l * Cfg::kQLane + s * (kFaBM * 128), &tm_q, bar_q, s * 64, head, q0 + l * kFaBM, b);
       bool ok = true;
-      for (int j = 0; j < n_total && ok; ++j) {
+      for (int j = kFaStages; j < n_total && ok; ++j) {      // the first ring was requested during set-up
         const int st = j % kFaStages;
         const uint32_t ph = (j / kFaStages) & 1;
         if (!(ok = mbar_wait(bar_kempty + 8 * st, ph ^ 1, abort_flag))) break;
@@ -316,21 +325,39 @@ flash_attn_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       if (ok) {
         tc_fence_after_sync();
         const float inv = row_sum > 0.f ? 1.0f / row_sum : 0.f;
-        T* out = reinterpret_cast<T*>(p.o) + (((int64_t)b * p.seq_q + q) * p.heads + head) * HD;
+        // A thread owns a row, so storing straight from registers would touch 32 different lines per
+        // instruction.  The warp's 32 rows are laid out in the lane's Q tile (no MMA reads it any more),
+        // 16-byte units XOR-swizzled by the row, and stored whole rows at a time.
+        constexpr int UPR = HD * 2 / 16;                     // 16-byte units per output row
+        const uint32_t stg = sm_q + l * Cfg::kQLane + quarter * (32 * HD * 2);
 #pragma unroll 1
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t ov[32];
           tmem_ld_32x32(t_o + c * 32, ov);
           tmem_ld_wait();
-          if (q < p.seq_q) {
 #pragma unroll
-            for (int e = 0; e < 32; e += 8) {
-              Vec16<T> v;
+          for (int k = 0; k < 4; ++k) {
+            uint32_t w[4];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) v.e[i] = from_f32<T>(__uint_as_float(ov[e + i]) * inv);
-              *reinterpret_cast<uint4*>(out + c * 32 + e) = v.raw;
+            for (int e = 0; e < 4; ++e) {
+              Vec16<T> two;      // only the first two elements are used
+              two.e[0] = from_f32<T>(__uint_as_float(ov[8 * k + 2 * e]) * inv);
+              two.e[1] = from_f32<T>(__uint_as_float(ov[8 * k + 2 * e + 1]) * inv);
+              w[e] = two.raw.x;
             }
+            const int u = c * 4 + k;
+            st_shared_v4(stg + lane_id * (HD * 2) + ((u ^ (lane_id & (UPR - 1))) << 4), w[0], w[1], w[2], w[3]);
           }
+        }
+        __syncwarp();
+        const int row0 = q0 + l * kFaBM + quarter * 32;      // first row of this warp
+        char* out_w = reinterpret_cast<char*>(reinterpret_cast<T*>(p.o) + (((int64_t)b * p.seq_q + row0) * p.heads + head) * HD);
+        const int64_t row_pitch = (int64_t)p.heads * HD * sizeof(T);
+#pragma unroll
+        for (int i = 0; i < UPR; ++i) {
+          const int idx = i * 32 + lane_id, rr = idx / UPR, u = idx % UPR;
+          const uint4 v = ld_shared_v4(stg + rr * (HD * 2) + ((u ^ (rr & (UPR - 1))) << 4));
+          if (row0 + rr < p.seq_q) *reinterpret_cast<uint4*>(out_w + rr * row_pitch + u * 16) = v;
         }
       }
     }
