@@ -498,14 +498,20 @@ template <typename TI, typename TO, int OP>
 __global__ void __launch_bounds__(kThreads)
 unary_kernel(const TI* __restrict__ x, TO* __restrict__ y, int64_t n) {
   const int64_t stride = (int64_t)gridDim.x * kThreads;
-  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
-    float f = to_f32(x[i]);
-    float r;
-    if constexpr (OP == 0) r = 1.0f / (1.0f + expf(-f));
-    else if constexpr (OP == 1) r = expf(f);
-    else if constexpr (OP == 2) r = 1.0f / sqrtf(f);
-    else r = f;
-    y[i] = from_f32<TO>(r);
+  constexpr int U = 4;                          // four independent loads in flight per thread
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride * U) {
+    float f[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) f[u] = i + u * stride < n ? to_f32(x[i + u * stride]) : 0.f;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float r;
+      if constexpr (OP == 0) r = 1.0f / (1.0f + expf(-f[u]));
+      else if constexpr (OP == 1) r = expf(f[u]);
+      else if constexpr (OP == 2) r = 1.0f / sqrtf(f[u]);
+      else r = f[u];
+      if (i + u * stride < n) y[i + u * stride] = from_f32<TO>(r);
+    }
   }
 }
 

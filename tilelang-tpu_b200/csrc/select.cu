@@ -49,31 +49,41 @@ gather_byte_kernel(const uint8_t* __restrict__ param, const uint32_t* __restrict
 }
 
 // =================================================================================
-// top-k.  Every element gets a unique 64-bit key (order-preserving image of the value in the
-// high word, inverted position in the low word), so "the next winner" is simply the largest
-// key strictly below the previous winner's: k rounds of a max-reduction, no marking, no
-// scratch memory, and ties resolve to the lower index.
+// top-k.  Values are mapped to an order-preserving unsigned image (inverted for an ascending
+// search); candidates compare by (image, position): larger image first, lower position on ties.
+// k rounds of an arg-max reduction; a taken element is masked out in its owner's registers, the
+// winners are recovered from their images (no second read of the row) and stay in registers - result
+// r in lane r % 32 - until they are written out, 32 at a time.
 // =================================================================================
 template <int DTYPE> __device__ __forceinline__ uint32_t order_bits(uint32_t b) {
   if constexpr (DTYPE == TL_F32) return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
   else if constexpr (DTYPE == TL_I32) return b ^ 0x80000000u;
   else return b;
 }
-
-__device__ __forceinline__ uint64_t make_key(uint32_t ord, uint32_t pos) {
-  return ((uint64_t)ord << 32) | (uint64_t)(0xffffffffu - pos);
+template <int DTYPE> __device__ __forceinline__ uint32_t value_bits(uint32_t o) {      // inverse of order_bits
+  if constexpr (DTYPE == TL_F32) return (o & 0x80000000u) ? (o ^ 0x80000000u) : ~o;
+  else if constexpr (DTYPE == TL_I32) return o ^ 0x80000000u;
+  else return o;
 }
 
-__device__ __forceinline__ uint64_t warp_max_u64(uint64_t v) {
+constexpr uint32_t kNoPos = 0xffffffffu;       // "no candidate": loses every comparison
+
+// (o, p) <- the better of (o, p) and (o2, p2)
+__device__ __forceinline__ void take_better(uint32_t& o, uint32_t& p, uint32_t o2, uint32_t p2) {
+  const bool other = (p2 != kNoPos) && (p == kNoPos || o2 > o || (o2 == o && p2 < p));
+  o = other ? o2 : o;
+  p = other ? p2 : p;
+}
+__device__ __forceinline__ void warp_argmax(uint32_t& o, uint32_t& p) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    uint64_t other = __shfl_xor_sync(0xffffffffu, v, o);
-    v = other > v ? other : v;
+  for (int d = 16; d > 0; d >>= 1) {
+    const uint32_t o2 = __shfl_xor_sync(0xffffffffu, o, d), p2 = __shfl_xor_sync(0xffffffffu, p, d);
+    take_better(o, p, o2, p2);
   }
-  return v;
 }
 
-// One warp per row, the row's keys in registers (length <= 32 * ITEMS).
+// One warp per row, the row's images in registers (length <= 32 * ITEMS); element j of a lane sits at
+// position lane + 32 j, so a lane's candidates are scanned in increasing position.
 template <int DTYPE, int ITEMS>
 __global__ void __launch_bounds__(kThreads)
 topk_warp_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ out_vals, int32_t* __restrict__ out_idx,
@@ -83,67 +93,111 @@ topk_warp_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ out_va
   if (row >= rows) return;
   const uint32_t* in = src + row * length;
   uint32_t ord[ITEMS];
+  uint32_t live = 0;                            // bit j: element j exists and has not been taken
 #pragma unroll
   for (int j = 0; j < ITEMS; ++j) {
-    int pos = lane + 32 * j;
+    const int pos = lane + 32 * j;
     uint32_t o = 0;
     if (pos < length) {
-      o = order_bits<DTYPE>(in[pos]);
+      o = order_bits<DTYPE>(__ldg(in + pos));
       if (!descending) o = ~o;
+      live |= 1u << j;
     }
     ord[j] = o;
   }
-  uint64_t prev = ~0ull;
+  uint32_t res_o = 0, res_p = 0;
   for (int r = 0; r < k; ++r) {
-    uint64_t best = 0;
+    uint32_t bo = 0, bj = ITEMS;
 #pragma unroll
-    for (int j = 0; j < ITEMS; ++j) {
-      int pos = lane + 32 * j;
-      uint64_t key = make_key(ord[j], (uint32_t)pos);
-      if (pos < length && key < prev && key > best) best = key;
+    for (int j = 0; j < ITEMS; ++j) {           // first of the equal images wins: lowest position of the lane
+      const bool better = ((live >> j) & 1u) && (bj == ITEMS || ord[j] > bo);
+      bo = better ? ord[j] : bo;
+      bj = better ? j : bj;
     }
-    best = warp_max_u64(best);
-    prev = best;
-    if (lane == 0) {
-      uint32_t pos = 0xffffffffu - (uint32_t)(best & 0xffffffffu);
-      out_idx[row * out_stride + r] = (int32_t)pos;
-      out_vals[row * out_stride + r] = in[pos];
+    uint32_t wo = bo, wp = bj == ITEMS ? kNoPos : (uint32_t)(lane + 32 * bj);
+    warp_argmax(wo, wp);
+    if ((wp & 31u) == (uint32_t)lane) live &= ~(1u << (wp >> 5));       // k <= length: a winner always exists
+    if ((r & 31) == lane) { res_o = wo; res_p = wp; }
+    if ((r & 31) == 31 || r == k - 1) {         // write the last (up to) 32 winners, one per lane
+      const int first = r & ~31;
+      if (first + lane <= r) {
+        out_idx[row * out_stride + first + lane] = (int32_t)res_p;
+        out_vals[row * out_stride + first + lane] = value_bits<DTYPE>(descending ? res_o : ~res_o);
+      }
     }
   }
 }
 
-// One CTA per row; keys are rebuilt from the row on every round (the row stays in L1/L2).
-template <int DTYPE>
+// One CTA per row of up to 256 * ITEMS elements, images in registers (element j of a thread sits at
+// position thread + 256 j); longer rows are re-read from L1/L2 on every round (ITEMS == 0).
+template <int DTYPE, int ITEMS>
 __global__ void __launch_bounds__(kThreads)
 topk_cta_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ out_vals, int32_t* __restrict__ out_idx,
                 int64_t length, int k, bool descending, int64_t out_stride) {
-  __shared__ uint64_t warp_best[kThreads / 32];
-  __shared__ uint64_t round_best;
+  __shared__ uint32_t warp_o[2][kThreads / 32], warp_p[2][kThreads / 32];
   const int64_t row = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x / 32;
   const uint32_t* in = src + row * length;
-  uint64_t prev = ~0ull;
-  for (int r = 0; r < k; ++r) {
-    uint64_t best = 0;
-    for (int64_t pos = threadIdx.x; pos < length; pos += kThreads) {
-      uint32_t o = order_bits<DTYPE>(__ldg(in + pos));
-      if (!descending) o = ~o;
-      uint64_t key = make_key(o, (uint32_t)pos);
-      if (key < prev && key > best) best = key;
-    }
-    best = warp_max_u64(best);
-    if ((threadIdx.x & 31) == 0) warp_best[threadIdx.x / 32] = best;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      uint64_t b = 0;
+  constexpr int NREG = ITEMS > 0 ? ITEMS : 1;
+  uint32_t ord[NREG];
+  uint32_t live = 0;
+  if constexpr (ITEMS > 0) {
 #pragma unroll
-      for (int w = 0; w < kThreads / 32; ++w) b = warp_best[w] > b ? warp_best[w] : b;
-      round_best = b;
-      uint32_t pos = 0xffffffffu - (uint32_t)(b & 0xffffffffu);
-      out_idx[row * out_stride + r] = (int32_t)pos;
-      out_vals[row * out_stride + r] = in[pos];
+    for (int j = 0; j < ITEMS; ++j) {
+      const int64_t pos = threadIdx.x + (int64_t)kThreads * j;
+      uint32_t o = 0;
+      if (pos < length) {
+        o = order_bits<DTYPE>(__ldg(in + pos));
+        if (!descending) o = ~o;
+        live |= 1u << j;
+      }
+      ord[j] = o;
     }
+  }
+  uint32_t prev_o = 0, prev_p = kNoPos;          // generic path: the last winner; everything at or above it is gone
+  uint32_t res_o = 0, res_p = 0;
+  for (int r = 0; r < k; ++r) {
+    uint32_t bo = 0, bp = kNoPos;
+    if constexpr (ITEMS > 0) {
+      uint32_t bj = ITEMS;
+#pragma unroll
+      for (int j = 0; j < ITEMS; ++j) {
+        const bool better = ((live >> j) & 1u) && (bj == ITEMS || ord[j] > bo);
+        bo = better ? ord[j] : bo;
+        bj = better ? j : bj;
+      }
+      bp = bj == ITEMS ? kNoPos : (uint32_t)(threadIdx.x + kThreads * bj);
+    } else {
+      for (int64_t pos = threadIdx.x; pos < length; pos += kThreads) {
+        uint32_t o = order_bits<DTYPE>(__ldg(in + pos));
+        if (!descending) o = ~o;
+        // still available: strictly after the previous winner in (image desc, position asc) order
+        const bool avail = prev_p == kNoPos || o < prev_o || (o == prev_o && (uint32_t)pos > prev_p);
+        if (avail) take_better(bo, bp, o, (uint32_t)pos);
+      }
+    }
+    warp_argmax(bo, bp);
+    const int buf = r & 1;                      // two exchange buffers: one barrier per round is enough
+    if (lane == 0) { warp_o[buf][warp] = bo; warp_p[buf][warp] = bp; }
     __syncthreads();
-    prev = round_best;
+    uint32_t wo = warp_o[buf][0], wp = warp_p[buf][0];
+#pragma unroll
+    for (int w = 1; w < kThreads / 32; ++w) take_better(wo, wp, warp_o[buf][w], warp_p[buf][w]);
+    if constexpr (ITEMS > 0) {
+      if ((wp % kThreads) == threadIdx.x) live &= ~(1u << (wp / kThreads));
+    } else {
+      prev_o = wo; prev_p = wp;
+    }
+    if (warp == 0) {
+      if ((r & 31) == lane) { res_o = wo; res_p = wp; }
+      if ((r & 31) == 31 || r == k - 1) {
+        const int first = r & ~31;
+        if (first + lane <= r) {
+          out_idx[row * out_stride + first + lane] = (int32_t)res_p;
+          out_vals[row * out_stride + first + lane] = value_bits<DTYPE>(descending ? res_o : ~res_o);
+        }
+      }
+    }
   }
 }
 
@@ -164,7 +218,10 @@ static int topk_dispatch(const void* src, void* vals, int32_t* idx, int64_t rows
     TL_LAUNCH_CHECK("topk_warp_kernel");
   } else {
     TL_REQUIRE(rows < (1ll << 31), "topk: too many rows");
-    topk_cta_kernel<DTYPE><<<(unsigned)rows, kThreads, 0, s>>>(in, ov, idx, length, k, desc, out_stride);
+    if (length <= 16 * kThreads)
+      topk_cta_kernel<DTYPE, 16><<<(unsigned)rows, kThreads, 0, s>>>(in, ov, idx, length, k, desc, out_stride);
+    else
+      topk_cta_kernel<DTYPE, 0><<<(unsigned)rows, kThreads, 0, s>>>(in, ov, idx, length, k, desc, out_stride);
     TL_LAUNCH_CHECK("topk_cta_kernel");
   }
   return TL_B200_OK;

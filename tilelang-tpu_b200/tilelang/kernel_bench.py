@@ -156,6 +156,43 @@ def mla_decode(dev, rank, world, peaks, batch=128, heads=128, d=576, dv=512, pag
     return e
 
 
+def small_ops(dev, rank, world, peaks, rows=8192, cols=4096):
+    """The remaining tile-op programs (row reductions, sigmoid, elementwise add, gather, top-k) at sizes well
+    above the L2, one entry each: algorithmic bytes / device time against the measured copy bandwidth."""
+    g = torch.Generator(device=dev).manual_seed(6)
+    out = []
+
+    def add(name, config, nbytes, fn):
+        ms = _time(fn, 1, reps=10)
+        out.append(_entry(name, config, nbytes, 1e9, "GB/s", ms, ms, peaks["hbm_gbs"], peaks["note"], "none", 1))
+
+    xb = torch.randn(rows, cols, generator=g, device=dev).bfloat16()
+    yb = torch.empty(rows, 1, dtype=torch.bfloat16, device=dev)
+    add("reduce_rows_kernel", f"row sum bf16 [{rows}, {cols}]", xb.numel() * 2 + rows * 2, lambda: ops.reduce_rows(xb, yb, "sum"))
+    xf = torch.randn(4 * rows, cols, generator=g, device=dev)
+    yf = torch.empty(4 * rows, 1, device=dev)
+    add("reduce_rows_kernel", f"row max fp32 [{4 * rows}, {cols}]", xf.numel() * 4 + 4 * rows * 4, lambda: ops.reduce_rows(xf, yf, "max"))
+    zf = torch.empty_like(xf)
+    add("unary_kernel", f"sigmoid fp32 [{4 * rows}, {cols}]", xf.numel() * 8, lambda: ops.unary(xf, zf, "sigmoid"))
+    wf = torch.randn(4 * rows, cols, generator=g, device=dev)
+    add("binary_kernel", f"add fp32 [{4 * rows}, {cols}]", xf.numel() * 12, lambda: ops.binary(xf, wf, zf, "add"))
+    del wf
+    idx = torch.randint(0, 4 * rows, (4 * rows,), generator=g, device=dev, dtype=torch.int32)
+    add("gather_vec_kernel", f"gather {4 * rows} rows of {cols} fp32 from a [{4 * rows}, {cols}] table",
+        2 * 4 * rows * cols * 4 + 4 * rows * 4, lambda: ops.gather_rows(xf, idx, zf))
+    k = 8
+    tv = torch.empty(4 * rows, k, device=dev)
+    ti = torch.empty(4 * rows, k, dtype=torch.int32, device=dev)
+    xt = xf.view(4 * rows * 4, cols // 4)             # 1024-wide rows: the warp kernel
+    tv4 = torch.empty(xt.shape[0], k, device=dev)
+    ti4 = torch.empty(xt.shape[0], k, dtype=torch.int32, device=dev)
+    add("topk_warp_kernel", f"top-{k} of fp32 rows [{xt.shape[0]}, {xt.shape[1]}]", xt.numel() * 4 + xt.shape[0] * k * 8,
+        lambda: ops.topk(xt, tv4, ti4, k))
+    add("topk_cta_kernel", f"top-{k} of fp32 rows [{4 * rows}, {cols}]", xf.numel() * 4 + 4 * rows * k * 8,
+        lambda: ops.topk(xf, tv, ti, k))
+    return out
+
+
 def run_all(dev, rank, world, peaks):
     out = []
     for fn in (gemm_bf16, gemm_fp8, mlp_gate_up, flash_attn, mla_decode):
@@ -181,6 +218,7 @@ SMALL = {      # reduced shapes for profiler captures: inputs above the 126 MB L
     "mlp_gate_up": dict(m=4096, n=4096, k=4096),
     "flash_attn": dict(b=2, s=4096, h=16, d=128),
     "mla_decode": dict(batch=32),
+    "small_ops": dict(rows=2048),
 }
 
 
