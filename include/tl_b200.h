@@ -95,8 +95,18 @@ int tl_b200_reduce_rows(const void* x, void* y, int64_t rows, int64_t cols, int 
  * (ppl_copy with differing dtypes, round-to-nearest-even, :1138-1151).              */
 int tl_b200_unary(const void* x, void* y, int64_t n_elems, int op, int in_dtype, int out_dtype,
                   void* stream);
+/* Strided 2-D copy with a cast: dst[r, c] = cast(src[r, c]) for a rows x cols window; src_ld and
+ * dst_ld are the row pitches in elements.  What ppl_copy does between a window of a global tensor
+ * and a tile, or between two tiles of different dtypes (customize.py:136-207,
+ * codegen_ppl.cc:958-1243; round-to-nearest-even on narrowing).  Float dtypes convert freely;
+ * TL_I32 / TL_U32 copy bits.                                                              */
+int tl_b200_copy2d(const void* src, void* dst, int64_t rows, int64_t cols, int64_t src_ld, int64_t dst_ld,
+                   int src_dtype, int dst_dtype, void* stream);
+/* dst[r, c] = value over a rows x cols window with row pitch ld (ppl_fill, customize.py:210-231). */
+int tl_b200_fill(void* dst, int64_t rows, int64_t cols, int64_t ld, float value, int dtype, void* stream);
 /* Binary: out = a (op) b with op 0 add, 1 sub, 2 mul, 3 div (ppl_add/subtract/mul/div,
- * codegen_ppl.cc:891-913,1280-1287).  b_mode 0: b has the shape of a; 1: b is (rows,1)
+ * codegen_ppl.cc:891-913,1280-1287), 4 max (the running maximum that ppl_reduce_max keeps with
+ * clear=False, customize.py:519-560).  b_mode 0: b has the shape of a; 1: b is (rows,1)
  * and broadcasts across columns (:868-889); 2: b is ignored and `scalar` is used
  * (ppl_mul_C / ppl_add_C, :917-957).  fp32 arithmetic, rounded to `dtype`.          */
 int tl_b200_binary(const void* a, const void* b, void* out, int64_t rows, int64_t cols, int op,

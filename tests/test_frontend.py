@@ -212,16 +212,48 @@ def test_bind_matmul_both_layouts_and_tiling_rule():
         bind(matmul_program(100, 64, 64, 32, 32, 32))
 
 
-def test_unmatched_program_is_rejected_with_its_listing():
+def generic_program(M=64, N=96, bm=32, bn=32, dtype="bfloat16"):
+    """Not one of the fused programs: out = exp(x) * rsqrt(mean(x * x) + 1) + 0.5, row block by row
+    block (a block spans all columns), fp32 math on a 16-bit tensor."""
+    @T.prim_func
+    def main_kernel_inner(X: T.Tensor((M, N), dtype), Y: T.Tensor((M, N), dtype)):
+        with T.Kernel(T.ceildiv(M, bm), is_cpu=True) as (bx,):
+            x16 = T.alloc_shared((bm, N), dtype)
+            x = T.alloc_shared((bm, N), "float32")
+            sq = T.alloc_shared((bm, N), "float32")
+            ss = T.alloc_shared((bm, 1), "float32")
+            y = T.alloc_shared((bm, N), "float32")
+            y16 = T.alloc_shared((bm, N), dtype)
+            T.ppl_copy(X[bx * bm, 0], x16)
+            T.ppl_copy(x16, x)
+            T.ppl_mul(sq, x, x)
+            T.ppl_reduce_sum(sq, ss, dim=1)
+            T.ppl_mul_C(ss, ss, T.float32(1.0 / N))
+            T.ppl_add_C(ss, ss, T.float32(1.0))
+            T.ppl_rsqrt(ss, ss)
+            T.ppl_copy(x, y)
+            T.ppl_exp2(y, sq, sq, sq, sq)
+            T.ppl_mul(y, y, ss)
+            T.ppl_add_C(y, y, T.float32(0.5))
+            T.ppl_copy(y, y16)
+            T.ppl_copy(y16, Y[bx * bm, 0])
+    return main_kernel_inner
+
+
+def test_unmatched_program_binds_to_the_generic_executor():
+    bound = bind(generic_program())
+    assert bound.program == "generic" and bound.facts["grid"] == [2]
+
+
+def test_program_the_executor_cannot_run_is_rejected_with_its_listing():
     @T.prim_func
     def odd(A: T.Tensor((8, 8), "float32"), B: T.Tensor((8, 8), "float32")):
         with T.Kernel(1, is_cpu=True) as (bx,):
             t = T.alloc_shared((8, 8), "float32")
             T.ppl_copy(A[0, 0], t)
-            T.ppl_rsqrt(t, t)
-            T.ppl_rsqrt(t, t)
+            T.ppl_rope_add(t, t, t, t, t)
             T.ppl_copy(t, B[0, 0])
-    with pytest.raises(UnsupportedProgram, match="no CPU fallback"):
+    with pytest.raises(UnsupportedProgram, match="ppl.rope_add is not available.*no CPU fallback"):
         tilelang.compile(odd, out_idx=-1, target="b200")
 
 

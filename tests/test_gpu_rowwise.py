@@ -222,3 +222,35 @@ def test_run_to_run_determinism(cuda_device):
         y = torch.empty_like(x)
         ops.rmsnorm(x, y, eps=1e-6)
         assert torch.equal(y.view(torch.int16), y0.view(torch.int16))
+
+
+# ------------------------------------------------------------------ window copy / fill / running max
+@pytest.mark.parametrize("src_dt,dst_dt", [(torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32),
+                                           (torch.float16, torch.float16), (torch.float32, torch.float16),
+                                           (torch.int32, torch.int32)])
+def test_copy2d_windows_and_casts(cuda_device, src_dt, dst_dt):
+    g = torch.Generator(device="cpu").manual_seed(21)
+    big = (torch.randn(40, 72, generator=g) * 3).to(src_dt) if src_dt.is_floating_point else \
+        torch.randint(-1000, 1000, (40, 72), generator=g, dtype=src_dt)
+    src = big.to(cuda_device)
+    dst = torch.zeros(64, 48, dtype=dst_dt, device=cuda_device)
+    assert ops.copy2d(src[5:37, 8:40], dst[16:48, 3:35]) == 0           # window -> window
+    ref = torch.zeros(64, 48, dtype=dst_dt)
+    ref[16:48, 3:35] = big[5:37, 8:40].to(dst_dt)                        # round-to-nearest-even cast
+    assert torch.equal(dst.cpu(), ref)
+    assert ops.copy2d(src[:0, :48], dst[:0]) == 0                          # empty
+
+
+def test_fill_window_and_running_max(cuda_device):
+    t = torch.zeros(16, 32, dtype=torch.bfloat16, device=cuda_device)
+    assert ops.fill(t[4:12, 8:24], 1.5) == 0
+    ref = torch.zeros(16, 32, dtype=torch.bfloat16)
+    ref[4:12, 8:24] = 1.5
+    assert torch.equal(t.cpu(), ref)
+    g = torch.Generator(device="cpu").manual_seed(22)
+    a, b = torch.randn(8, 16, generator=g), torch.randn(8, 16, generator=g)
+    out = torch.empty(8, 16, device=cuda_device)
+    assert ops.binary(a.to(cuda_device), b.to(cuda_device), out, "max") == 0
+    assert torch.equal(out.cpu(), torch.maximum(a, b))
+    with pytest.raises(ValueError, match="contiguous rows"):
+        ops.fill(t.t()[0:4, 0:4], 0.0)

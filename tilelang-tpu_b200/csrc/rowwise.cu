@@ -3,6 +3,8 @@
 // touches tensor cores.
 #include "common.cuh"
 
+#include <type_traits>
+
 namespace tl {
 
 constexpr int kThreads = 256;
@@ -530,9 +532,49 @@ binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ 
     if constexpr (OP == 0) r = av + bv;
     else if constexpr (OP == 1) r = av - bv;
     else if constexpr (OP == 2) r = av * bv;
-    else r = av / bv;
+    else if constexpr (OP == 3) r = av / bv;
+    else r = fmaxf(av, bv);
     out[i] = from_f32<T>(r);
   }
+}
+
+// Strided 2-D copy with a cast (a tile <-> a window of a larger tensor), and a 2-D fill.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(kThreads)
+copy2d_kernel(const TI* __restrict__ src, TO* __restrict__ dst, int64_t rows, int64_t cols, int64_t src_ld,
+              int64_t dst_ld) {
+  const int64_t stride = (int64_t)gridDim.x * kThreads, n = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+    const int64_t r = i / cols, c = i - r * cols;
+    if constexpr (std::is_same<TI, TO>::value) dst[r * dst_ld + c] = src[r * src_ld + c];
+    else dst[r * dst_ld + c] = from_f32<TO>(to_f32(src[r * src_ld + c]));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+fill2d_kernel(T* __restrict__ dst, int64_t rows, int64_t cols, int64_t ld, T value) {
+  const int64_t stride = (int64_t)gridDim.x * kThreads, n = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
+    const int64_t r = i / cols, c = i - r * cols;
+    dst[r * ld + c] = value;
+  }
+}
+
+template <typename TI>
+static int copy2d_out(const void* src, void* dst, int64_t rows, int64_t cols, int64_t sld, int64_t dld, int out_dtype,
+                      cudaStream_t s) {
+  const unsigned grid = elementwise_grid(rows * cols, kThreads * 4);
+  switch (out_dtype) {
+    case TL_F32: copy2d_kernel<TI, float><<<grid, kThreads, 0, s>>>((const TI*)src, (float*)dst, rows, cols, sld, dld); break;
+    case TL_F16: copy2d_kernel<TI, __half><<<grid, kThreads, 0, s>>>((const TI*)src, (__half*)dst, rows, cols, sld, dld); break;
+    case TL_BF16:
+      copy2d_kernel<TI, __nv_bfloat16><<<grid, kThreads, 0, s>>>((const TI*)src, (__nv_bfloat16*)dst, rows, cols, sld, dld);
+      break;
+    default: return fail(TL_B200_EINVAL, "copy2d: unsupported output dtype %d", out_dtype);
+  }
+  TL_LAUNCH_CHECK("copy2d_kernel");
+  return TL_B200_OK;
 }
 
 template <typename TI, typename TO>
@@ -581,6 +623,7 @@ static int binary_op(const void* a, const void* b, void* o, int64_t n, int64_t c
     case 1: return binary_mode<T, 1>(a, b, o, n, cols, b_mode, sc, s);
     case 2: return binary_mode<T, 2>(a, b, o, n, cols, b_mode, sc, s);
     case 3: return binary_mode<T, 3>(a, b, o, n, cols, b_mode, sc, s);
+    case 4: return binary_mode<T, 4>(a, b, o, n, cols, b_mode, sc, s);
     default: return fail(TL_B200_EINVAL, "binary: unknown op %d", op);
   }
 }
@@ -643,6 +686,41 @@ int tl_b200_unary(const void* x, void* y, int64_t n_elems, int op, int in_dtype,
   TL_REQUIRE(x && y, "unary: null tensor pointer");
   cudaStream_t s = (cudaStream_t)stream;
   TL_FLOAT_DISPATCH(in_dtype, unary_out<T>(x, y, n_elems, op, out_dtype, s));
+}
+
+int tl_b200_copy2d(const void* src, void* dst, int64_t rows, int64_t cols, int64_t src_ld, int64_t dst_ld, int src_dtype,
+                   int dst_dtype, void* stream) {
+  TL_REQUIRE(rows >= 0 && cols >= 0, "copy2d: negative size");
+  if (rows == 0 || cols == 0) return TL_B200_OK;
+  TL_REQUIRE(src && dst, "copy2d: null tensor pointer");
+  TL_REQUIRE(src_ld >= cols && dst_ld >= cols, "copy2d: a leading dimension is smaller than the row length");
+  cudaStream_t s = (cudaStream_t)stream;
+  if ((src_dtype == TL_I32 || src_dtype == TL_U32) && (dst_dtype == TL_I32 || dst_dtype == TL_U32)) {   // index tiles: bits
+    copy2d_kernel<uint32_t, uint32_t><<<elementwise_grid(rows * cols, kThreads * 4), kThreads, 0, s>>>(
+        (const uint32_t*)src, (uint32_t*)dst, rows, cols, src_ld, dst_ld);
+    TL_LAUNCH_CHECK("copy2d_kernel");
+    return TL_B200_OK;
+  }
+  TL_FLOAT_DISPATCH(src_dtype, copy2d_out<T>(src, dst, rows, cols, src_ld, dst_ld, dst_dtype, s));
+}
+
+int tl_b200_fill(void* dst, int64_t rows, int64_t cols, int64_t ld, float value, int dtype, void* stream) {
+  TL_REQUIRE(rows >= 0 && cols >= 0, "fill: negative size");
+  if (rows == 0 || cols == 0) return TL_B200_OK;
+  TL_REQUIRE(dst, "fill: null tensor pointer");
+  TL_REQUIRE(ld >= cols, "fill: the leading dimension is smaller than the row length");
+  cudaStream_t s = (cudaStream_t)stream;
+  const unsigned grid = elementwise_grid(rows * cols, kThreads * 4);
+  switch (dtype) {
+    case TL_F32: fill2d_kernel<float><<<grid, kThreads, 0, s>>>((float*)dst, rows, cols, ld, value); break;
+    case TL_F16: fill2d_kernel<__half><<<grid, kThreads, 0, s>>>((__half*)dst, rows, cols, ld, __float2half_rn(value)); break;
+    case TL_BF16:
+      fill2d_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>((__nv_bfloat16*)dst, rows, cols, ld, __float2bfloat16_rn(value));
+      break;
+    default: return fail(TL_B200_EINVAL, "fill: unsupported dtype %d", dtype);
+  }
+  TL_LAUNCH_CHECK("fill2d_kernel");
+  return TL_B200_OK;
 }
 
 int tl_b200_binary(const void* a, const void* b, void* out, int64_t rows, int64_t cols, int op, int b_mode,

@@ -45,6 +45,8 @@ PROTOTYPES = {
                                          c_int64, c_void_p]),
     "tl_b200_mla_decode_paged_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                                  c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_void_p]),
+    "tl_b200_copy2d": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "tl_b200_fill": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_float, c_int, c_void_p]),
     "tl_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
     "tl_b200_mlp_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
 }

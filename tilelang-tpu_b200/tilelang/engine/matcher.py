@@ -452,7 +452,17 @@ def bind(func: PrimFunc) -> BoundKernel:
         bound = m(func)
         if bound is not None:
             return bound
+    # not one of the fused programs: run it tile op by tile op on the GPU (engine/interpreter.py)
+    from . import interpreter
+    try:
+        run = interpreter.build(func)
+    except interpreter.InterpreterError as why:
+        reason = str(why)
+    else:
+        return BoundKernel("generic", "tile-op executor (one tl_b200_* launch per op)", run,
+                           dict(ops=len(func.ops), grid=[int(const_value(g)) for g in func.grid]))
     raise UnsupportedProgram(
+        f"the generic tile-op executor cannot run it either ({reason}); "
         "this ppl_* program does not match any kernel of the b200 library (matmul, rmsnorm, "
         "rmsnorm split-K, rope, swiglu, gated MLP, row reduce, top-k, gather, sigmoid, elementwise, flash "
         "attention forward, MLA decode); there is no CPU fallback.  Recorded program:\n" + func.script())

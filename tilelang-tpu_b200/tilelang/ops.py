@@ -111,7 +111,7 @@ def reduce_rows(x: torch.Tensor, y: torch.Tensor, op: str) -> int:
 
 
 _UNARY = {"sigmoid": 0, "exp": 1, "rsqrt": 2, "copy": 3}
-_BINARY = {"add": 0, "sub": 1, "mul": 2, "div": 3}
+_BINARY = {"add": 0, "sub": 1, "mul": 2, "div": 3, "max": 4}
 
 
 def unary(x: torch.Tensor, y: torch.Tensor, op: str) -> int:
@@ -144,6 +144,36 @@ def binary(a: torch.Tensor, b, out: torch.Tensor, op: str) -> int:
         s = _prepare(a, out)
     return N.check(N.load().tl_b200_binary(_ptr(a), bp, _ptr(out), rows, cols, _BINARY[op], mode, scalar,
                                           dtype_code(a.dtype), s), "tl_b200_binary")
+
+
+def _window(t: torch.Tensor, what: str):
+    """(rows, cols, row pitch in elements) of a 2-D window whose rows are contiguous."""
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise ValueError(f"{what}: expected a 2-D window with contiguous rows")
+    return t.shape[0], t.shape[1], (t.stride(0) if t.shape[0] > 1 else max(t.shape[1], 1))
+
+
+def _prepare_windows(*tensors: torch.Tensor) -> int:
+    base = [t.view(-1) if t.is_contiguous() else t.as_strided((1,), (1,)) for t in tensors]
+    return _prepare(*base)
+
+
+def copy2d(src: torch.Tensor, dst: torch.Tensor) -> int:
+    """dst[r, c] = cast(src[r, c]) between two 2-D windows (views with contiguous rows) of equal shape."""
+    if src.shape != dst.shape:
+        raise ValueError("copy2d: shapes differ")
+    rows, cols, sld = _window(src, "copy2d")
+    _, _, dld = _window(dst, "copy2d")
+    s = _prepare_windows(src, dst)
+    return N.check(N.load().tl_b200_copy2d(_ptr(src), _ptr(dst), rows, cols, sld, dld, dtype_code(src.dtype),
+                                          dtype_code(dst.dtype), s), "tl_b200_copy2d")
+
+
+def fill(dst: torch.Tensor, value: float) -> int:
+    """dst[:, :] = value for a 2-D window with contiguous rows."""
+    rows, cols, ld = _window(dst, "fill")
+    s = _prepare_windows(dst)
+    return N.check(N.load().tl_b200_fill(_ptr(dst), rows, cols, ld, float(value), dtype_code(dst.dtype), s), "tl_b200_fill")
 
 
 def gather_rows(param: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> int:
