@@ -95,6 +95,12 @@ int tl_b200_reduce_rows(const void* x, void* y, int64_t rows, int64_t cols, int 
  * (ppl_copy with differing dtypes, round-to-nearest-even, :1138-1151).              */
 int tl_b200_unary(const void* x, void* y, int64_t n_elems, int op, int in_dtype, int out_dtype,
                   void* stream);
+/* The tile op ppl_rope_add on contiguous rows x cols tiles (cols even):
+ * out[:, 2i] = even1[:, 2i] + even2[:, 2i+1], out[:, 2i+1] = odd1[:, 2i+1] + odd2[:, 2i], one
+ * rounding to `dtype` (customize.py:563-603, codegen_ppl.cc:1809-1848).  The fused RoPE program is
+ * tl_b200_rope; this entry serves programs that assemble the rotation from their own terms.      */
+int tl_b200_rope_add(void* out, const void* even1, const void* even2, const void* odd1, const void* odd2,
+                     int64_t rows, int64_t cols, int dtype, void* stream);
 /* Strided 2-D copy with a cast: dst[r, c] = cast(src[r, c]) for a rows x cols window; src_ld and
  * dst_ld are the row pitches in elements.  What ppl_copy does between a window of a global tensor
  * and a tile, or between two tiles of different dtypes (customize.py:136-207,

@@ -249,11 +249,10 @@ def test_program_the_executor_cannot_run_is_rejected_with_its_listing():
     @T.prim_func
     def odd(A: T.Tensor((8, 8), "float32"), B: T.Tensor((8, 8), "float32")):
         with T.Kernel(1, is_cpu=True) as (bx,):
-            t = T.alloc_shared((8, 8), "float32")
-            T.ppl_copy(A[0, 0], t)
-            T.ppl_rope_add(t, t, t, t, t)
-            T.ppl_copy(t, B[0, 0])
-    with pytest.raises(UnsupportedProgram, match="ppl.rope_add is not available.*no CPU fallback"):
+            t = T.alloc_shared((2, 4, 8), "float32")
+            T.ppl_fill(t, T.float32(0))
+            T.ppl_rsqrt(t, t)
+    with pytest.raises(UnsupportedProgram, match="has rank 3.*no CPU fallback"):
         tilelang.compile(odd, out_idx=-1, target="b200")
 
 

@@ -98,3 +98,43 @@ def test_running_maximum_and_column_broadcast(cuda_device):
     x = torch.randn(M, N, generator=gen(6))
     y = run_generic(main_kernel_inner, [x, torch.zeros(M, N)], cuda_device)[1]
     assert torch.equal(y, x - x.max(dim=1, keepdim=True).values)
+
+
+def test_rope_from_its_terms_is_bit_exact_with_the_fused_kernel(cuda_device):
+    """x*cos, x*sin and -(x)*sin rounded to bf16 tiles, assembled by ppl_rope_add: the same rounding
+    points as the fused RoPE kernel and the reference's check function."""
+    import tilelang.language as T
+    from tilelang import ops
+    tokens, heads, dim, bt = 32, 4, 64, 8
+    rows = tokens * heads
+
+    @T.prim_func
+    def main_kernel_inner(X: T.Tensor((rows, dim), "bfloat16"), C: T.Tensor((rows, dim), "bfloat16"),
+                          S: T.Tensor((rows, dim), "bfloat16"), Y: T.Tensor((rows, dim), "bfloat16")):
+        with T.Kernel(rows // bt, is_cpu=True) as (bx,):
+            x = T.alloc_shared((bt, dim), "bfloat16")
+            c = T.alloc_shared((bt, dim), "bfloat16")
+            s = T.alloc_shared((bt, dim), "bfloat16")
+            xc = T.alloc_shared((bt, dim), "bfloat16")
+            xs = T.alloc_shared((bt, dim), "bfloat16")
+            xn = T.alloc_shared((bt, dim), "bfloat16")
+            y = T.alloc_shared((bt, dim), "bfloat16")
+            T.ppl_copy(X[bx * bt, 0], x)
+            T.ppl_copy(C[bx * bt, 0], c)
+            T.ppl_copy(S[bx * bt, 0], s)
+            T.ppl_mul(xc, x, c)
+            T.ppl_mul(xs, x, s)
+            T.ppl_mul_C(xn, x, T.float32(-1.0))
+            T.ppl_mul(xn, xn, s)
+            T.ppl_rope_add(y, xc, xn, xc, xs)
+            T.ppl_copy(y, Y[bx * bt, 0])
+
+    g = gen(7)
+    x = torch.randn(rows, dim, generator=g).to(BF)
+    cos, sin = O.make_rope_cos_sin(tokens, dim)
+    cos_r, sin_r = cos.to(BF).repeat_interleave(heads, dim=0), sin.to(BF).repeat_interleave(heads, dim=0)
+    y = run_generic(main_kernel_inner, [x, cos_r, sin_r, torch.zeros_like(x)], cuda_device)[3]
+    fused = torch.empty_like(x).to(cuda_device)
+    assert ops.rope(x.to(cuda_device), cos.to(BF).to(cuda_device), sin.to(BF).to(cuda_device), fused) == 0
+    assert torch.equal(y.view(torch.int16), fused.cpu().view(torch.int16))
+    assert torch.equal(y.view(torch.int16), O.rope(x, cos.to(BF), sin.to(BF)).view(torch.int16))

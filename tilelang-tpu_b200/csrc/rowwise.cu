@@ -561,6 +561,28 @@ fill2d_kernel(T* __restrict__ dst, int64_t rows, int64_t cols, int64_t ld, T val
   }
 }
 
+// out[:, 2i] = e1[:, 2i] + e2[:, 2i+1];  out[:, 2i+1] = o1[:, 2i+1] + o2[:, 2i]   (contiguous tiles)
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+rope_add_kernel(T* __restrict__ out, const T* __restrict__ e1, const T* __restrict__ e2, const T* __restrict__ o1,
+                const T* __restrict__ o2, int64_t pairs) {
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < pairs; i += stride) {
+    const int64_t c = 2 * i;
+    out[c] = from_f32<T>(__fadd_rn(to_f32(e1[c]), to_f32(e2[c + 1])));
+    out[c + 1] = from_f32<T>(__fadd_rn(to_f32(o1[c + 1]), to_f32(o2[c])));
+  }
+}
+
+template <typename T>
+static int rope_add_launch(void* out, const void* e1, const void* e2, const void* o1, const void* o2, int64_t pairs,
+                           cudaStream_t s) {
+  rope_add_kernel<T><<<elementwise_grid(pairs, kThreads * 4), kThreads, 0, s>>>((T*)out, (const T*)e1, (const T*)e2,
+                                                                               (const T*)o1, (const T*)o2, pairs);
+  TL_LAUNCH_CHECK("rope_add_kernel");
+  return TL_B200_OK;
+}
+
 template <typename TI>
 static int copy2d_out(const void* src, void* dst, int64_t rows, int64_t cols, int64_t sld, int64_t dld, int out_dtype,
                       cudaStream_t s) {
@@ -686,6 +708,16 @@ int tl_b200_unary(const void* x, void* y, int64_t n_elems, int op, int in_dtype,
   TL_REQUIRE(x && y, "unary: null tensor pointer");
   cudaStream_t s = (cudaStream_t)stream;
   TL_FLOAT_DISPATCH(in_dtype, unary_out<T>(x, y, n_elems, op, out_dtype, s));
+}
+
+int tl_b200_rope_add(void* out, const void* even1, const void* even2, const void* odd1, const void* odd2, int64_t rows,
+                     int64_t cols, int dtype, void* stream) {
+  TL_REQUIRE(rows >= 0 && cols >= 0, "rope_add: negative size");
+  TL_REQUIRE(cols % 2 == 0, "rope_add: the row length %lld must be even", (long long)cols);
+  if (rows == 0 || cols == 0) return TL_B200_OK;
+  TL_REQUIRE(out && even1 && even2 && odd1 && odd2, "rope_add: null tensor pointer");
+  cudaStream_t s = (cudaStream_t)stream;
+  TL_FLOAT_DISPATCH(dtype, rope_add_launch<T>(out, even1, even2, odd1, odd2, rows * cols / 2, s));
 }
 
 int tl_b200_copy2d(const void* src, void* dst, int64_t rows, int64_t cols, int64_t src_ld, int64_t dst_ld, int src_dtype,

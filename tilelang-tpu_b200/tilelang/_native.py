@@ -45,6 +45,7 @@ PROTOTYPES = {
                                          c_int64, c_void_p]),
     "tl_b200_mla_decode_paged_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                                  c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_void_p]),
+    "tl_b200_rope_add": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "tl_b200_copy2d": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
     "tl_b200_fill": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_float, c_int, c_void_p]),
     "tl_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),

@@ -16,6 +16,7 @@ Semantics follow tilelang/language/customize.py and the code generator:
   ppl.mul_C/add_C       out = in (op) constant, the constant first cast to the tile dtype   (:263-284, 400-420; codegen :917-957)
   ppl.exp       natural exponential in place;  ppl.sigmoid, ppl.rsqrt: out = f(in)          (:313-397)
   ppl.reduce_sum  out (M,1) = row sums;  ppl.reduce_max  out = max(out, row maxima)         (:476-560)
+  ppl.rope_add  out[2i] = e1[2i] + e2[2i+1], out[2i+1] = o1[2i+1] + o2[2i]                  (:563-603; codegen :1809-1848)
   ppl.gather / ppl.topk  on whole tensors                                                   (:353-362)
 """
 from __future__ import annotations
@@ -30,7 +31,7 @@ _BINARY_OPS = {"ppl.add": "add", "ppl.sub": "sub", "ppl.mul": "mul", "ppl.div": 
 _CONST_OPS = {"ppl.mul_C": "mul", "ppl.add_C": "add"}
 _SUPPORTED = set(_BINARY_OPS) | set(_CONST_OPS) | {
     "ppl.copy", "ppl.fill", "ppl.gemm", "ppl.exp", "ppl.sigmoid", "ppl.rsqrt", "ppl.reduce_sum", "ppl.reduce_max",
-    "ppl.gather", "ppl.topk", "loop.begin", "loop.end"}
+    "ppl.rope_add", "ppl.gather", "ppl.topk", "loop.begin", "loop.end"}
 _FLOATS = ("float32", "float16", "bfloat16")
 
 
@@ -74,6 +75,9 @@ def validate(func: PrimFunc) -> None:
             _need(out.shape == x.shape and out.dtype == x.dtype == y.dtype, f"{op.name}: out and in1 must agree in shape and dtype")
             _need(y.shape == x.shape or (len(x.shape) == 2 and tuple(y.shape) == (x.shape[0], 1)),
                   f"{op.name}: in2 must be shaped like in1 or (M, 1)")
+        if op.name == "ppl.rope_add":
+            _need(all(len(t.shape) == 2 and t.shape == op.args[0].shape and t.dtype == op.args[0].dtype for t in op.args)
+                  and op.args[0].shape[1] % 2 == 0, "ppl.rope_add: five 2-D tiles of one shape and dtype, even width")
         if op.name in ("ppl.reduce_sum", "ppl.reduce_max"):
             x, y = op.args[0], op.args[1]
             _need(len(x.shape) == 2 and y.dtype == x.dtype and y.shape[0] == x.shape[0] and
@@ -181,6 +185,8 @@ def build(func: PrimFunc) -> Callable[..., int]:
                 tmp = torch.empty_like(y)
                 y2, t2 = y.view(-1, 1), tmp.view(-1, 1)
                 return K.reduce_rows(x, tmp, "max") or K.binary(y2, t2, y2, "max")
+            if n == "ppl.rope_add":
+                return K.rope_add(*(tensor_of(t) for t in a))
             if n == "ppl.gather":
                 out, param, index = (tensor_of(_buf(t)) for t in a[:3])
                 return K.gather_rows(param.view(a[3], -1), index.view(-1), out.view(index.numel(), -1))

@@ -176,6 +176,16 @@ def fill(dst: torch.Tensor, value: float) -> int:
     return N.check(N.load().tl_b200_fill(_ptr(dst), rows, cols, ld, float(value), dtype_code(dst.dtype), s), "tl_b200_fill")
 
 
+def rope_add(out: torch.Tensor, even1: torch.Tensor, even2: torch.Tensor, odd1: torch.Tensor, odd2: torch.Tensor) -> int:
+    """out[:, 2i] = even1[:, 2i] + even2[:, 2i+1]; out[:, 2i+1] = odd1[:, 2i+1] + odd2[:, 2i] on 2-D tiles."""
+    ts = (out, even1, even2, odd1, odd2)
+    if out.dim() != 2 or any(t.shape != out.shape or t.dtype != out.dtype for t in ts):
+        raise ValueError("rope_add: five 2-D tiles of one shape and dtype")
+    s = _prepare(*ts)
+    return N.check(N.load().tl_b200_rope_add(_ptr(out), _ptr(even1), _ptr(even2), _ptr(odd1), _ptr(odd2), out.shape[0],
+                                            out.shape[1], dtype_code(out.dtype), s), "tl_b200_rope_add")
+
+
 def gather_rows(param: torch.Tensor, index: torch.Tensor, out: torch.Tensor) -> int:
     """out[i, :] = param[index[i], :]; index holds uint32 (or non-negative int32) row ids."""
     if param.dim() != 2 or out.dim() != 2 or out.shape[1] != param.shape[1] or out.dtype != param.dtype:
