@@ -6,7 +6,8 @@ import torch
 import oracle.ops as O
 import tilelang
 import tilelang.language as T
-from test_frontend import matmul_program, mlp_program, rms_norm_program, topk_program
+from test_frontend import (matmul_program, mlp_program, rms_norm_program, rms_norm_program_f32, swiglu_program_f32,
+                           topk_program)
 
 pytestmark = pytest.mark.gpu
 
@@ -107,3 +108,15 @@ def test_mlp_program(cuda_device):
     y = torch.zeros(rows, hidden).bfloat16()
     assert kernel(y, x, wg, wu, wd) == 0
     assert torch.allclose(y.float(), O.mlp(x, wg, wu, wd).float(), atol=2e-2, rtol=2e-2)
+
+
+def test_float32_program_forms(cuda_device):
+    g = gen(9)
+    x = torch.randn(64, 128, generator=g)
+    y = torch.zeros(64, 128)
+    assert tilelang.compile(rms_norm_program_f32(64, 128, 32, eps=1e-6), out_idx=-1, target="b200")(x, y) == 0
+    assert torch.allclose(y, O.rmsnorm(x, eps=1e-6), atol=1e-5, rtol=1e-5)
+    gate, up = torch.randn(64, 128, generator=g), torch.randn(64, 128, generator=g)
+    out = torch.zeros(64, 128)
+    assert tilelang.compile(swiglu_program_f32(64, 128, 32, 64), out_idx=0, target="b200")(out, gate, up) == 0
+    assert torch.allclose(out, O.swiglu(gate, up), atol=1e-5, rtol=1e-5)
