@@ -58,7 +58,8 @@ def test_topk_golden(cuda_device):
 
 @pytest.mark.parametrize("desc", [True, False])
 @pytest.mark.parametrize("rows,length,k", [(1, 1024, 8), (8192, 256, 8), (5, 37, 37), (3, 1000, 16),
-                                           (2, 5000, 10), (1, 70000, 4), (4, 1, 1), (9, 257, 3)])
+                                           (2, 5000, 10), (1, 70000, 4), (4, 1, 1), (9, 257, 3), (3, 3000, 40),
+                                           (2, 2048, 8), (2, 4096, 33), (1, 6000, 70)])
 def test_topk_fp32_shapes(cuda_device, rows, length, k, desc):
     # a random permutation of distinct values: tie-free, so positions are pinned
     g = gen(rows * 3 + length + k)
