@@ -177,7 +177,9 @@ mlp_gate_up_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
           for (int j = 0; j < 32; ++j) {
             // the program's gate and up GEMMs deliver 16-bit tiles; SiLU and the product run in fp32
             const float gv = round_through<T>(__uint_as_float(g[j])), uv = round_through<T>(__uint_as_float(u[j]));
-            r[j] = uv * __fdividef(gv, 1.0f + __expf(-gv));
+            float th;                                       // same expression as the SwiGLU kernel: bit-identical results
+            asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.5f * gv));
+            r[j] = gv < -17.0f ? 0.0f * uv : uv * (0.5f * gv * (1.0f + th));
           }
           if (vec_ok && valid == 32) {
 #pragma unroll
