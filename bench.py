@@ -34,8 +34,8 @@ for _p in (str(ROOT / "tilelang-tpu_b200"), str(ROOT)):
 import torch  # noqa: E402
 
 # DRAM bytes one SwiGLU launch moves per token, from one ncu capture of the 4096-token case
-# (profiles/swiglu_rope_rmsnorm_llama8b_4096tok.md: 301.8 MB for 4096 tokens; 86 016 algorithmic bytes
-# per token - the part of the output still dirty in L2 when the kernel ends is not counted).  Traffic
+# (301.8 MB for 4096 tokens; 86 016 algorithmic bytes per token - the part of the output still
+# dirty in L2 when the kernel ends is not counted).  Traffic
 # grows in proportion to the token count, so a launch is scaled from it.
 SWIGLU_DRAM_BYTES_PER_TOKEN = 301.8e6 / 4096
 
@@ -338,7 +338,7 @@ def main():
     peaks = measured_peaks()
     kernels = None
     if not args.no_kernels:
-        from tilelang import kernel_bench
+        import kernel_bench
         kernels = kernel_bench.run_all(dev, rank, world, peaks)
 
     if rank == 0:

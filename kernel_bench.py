@@ -10,12 +10,19 @@ when causal (examples/flash_attention/example_mha_fwd_bshd.py:197-200), MLA deco
 """
 from __future__ import annotations
 
+import sys
 import time
+from pathlib import Path
 
-import torch
-import torch.distributed as dist
+ROOT = Path(__file__).resolve().parent
+for _p in (str(ROOT / "tilelang-tpu_b200"), str(ROOT)):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
 
-from . import ops, parallel
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from tilelang import ops, parallel  # noqa: E402
 
 
 def _time(fn, world, reps=5, warmup=3):
@@ -223,10 +230,9 @@ SMALL = {      # reduced shapes for profiler captures: inputs above the 126 MB L
 
 
 def main(argv=None):
-    """`python -m tilelang.kernel_bench --kernel flash_attn [--small]` on one GPU."""
+    """`python kernel_bench.py --kernel flash_attn [--small]` on one GPU."""
     import argparse
     import json
-    from pathlib import Path
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", required=True, choices=sorted(SMALL))
     ap.add_argument("--small", action="store_true", help="reduced shape (for profiler captures)")
@@ -234,7 +240,7 @@ def main(argv=None):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "note": "of fallback"}
-    f = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    f = ROOT / "MEASURED_PEAKS.json"
     if f.exists():
         d = json.loads(f.read_text())
         peaks = {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "note": "of measured"}

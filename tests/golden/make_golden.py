@@ -8,7 +8,7 @@ inputs in this process, and stores inputs and outputs.  tests/test_oracle_golden
 oracle/ops.py to these vectors.
 
 Run from the repository root, with the reference tree available:
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 16-bit tensors are stored as uint16 bit patterns, e4m3 as uint8.
 """
 from __future__ import annotations
@@ -22,7 +22,10 @@ import numpy as np
 import torch
 import torch.nn.functional as F
 
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+import os
+if len(sys.argv) < 2 and "TILELANG_TPU_REFERENCE" not in os.environ:
+    raise SystemExit("usage: make_golden.py /path/to/reference   (or set TILELANG_TPU_REFERENCE)")
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["TILELANG_TPU_REFERENCE"])
 OUT = Path(__file__).resolve().parent
 
 
