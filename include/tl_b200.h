@@ -233,8 +233,9 @@ int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, const float* k
  * batches are rejected with TL_B200_EINVAL).  It calls no allocating routine.  The first call on
  * a device looks up the array's device address; make that call before any stream capture.  All
  * calls on a device share the array, so calls that may overlap on the GPU (different streams)
- * race on it; within one stream they are ordered.  A bounded wait that gives up is not
- * reported through tl_b200_device_status() by this variant.                                   */
+ * race on it; within one stream they are ordered.  A bounded wait that gives up is reported
+ * through tl_b200_device_status() only if tl_b200_init() (which creates the host-mapped status
+ * word) ran in this process before; this entry point never creates it.                        */
 int tl_b200_mla_decode_paged_noalloc(const void* q, const void* kv_cache, const float* kv_scale,
                                      const int32_t* block_table, const int32_t* cache_seqlens,
                                      void* out, int64_t batch, int64_t heads, int64_t page_size,

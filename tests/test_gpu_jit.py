@@ -39,15 +39,22 @@ def test_rmsnorm_program_device_tensors_and_pinned_host(cuda_device):
     assert torch.equal(bp, bd.cpu())
 
 
-@pytest.mark.parametrize("trans_b", [False, True])
-def test_matmul_program(cuda_device, trans_b):
-    kernel = tilelang.compile(matmul_program(64, 64, 64, 32, 32, 32, trans_b=trans_b), out_idx=-1, target="b200")
+@pytest.mark.parametrize("trans_b,bk", [(False, 32), (True, 64), (True, 32)])
+def test_matmul_program(cuda_device, trans_b, bk):
+    kernel = tilelang.compile(matmul_program(64, 64, 64, 32, 32, bk, trans_b=trans_b), out_idx=-1, target="b200")
     g = gen(3)
     a = torch.randn(64, 64, generator=g).half()
     b = torch.randn(64, 64, generator=g).half()
     c = torch.zeros(64, 64).half()
     assert kernel(a, b, c) == 0
-    ref = O.matmul(a, b, transpose_b=trans_b)
+    if trans_b and bk < 64:
+        # `C = A B^T` overwrites C on every K iteration in the reference's generated code
+        # (src/target/codegen_ppl.cc:1276-1279): what is left is the product over the last K tile
+        assert kernel.adapter.bound.program == "generic"
+        ref = O.matmul(a[:, -bk:].contiguous(), b[:, -bk:].contiguous(), transpose_b=True)
+    else:
+        assert kernel.adapter.bound.program == "matmul"
+        ref = O.matmul(a, b, transpose_b=trans_b)
     assert torch.allclose(c, ref, atol=1e-2, rtol=1e-2)                      # the demo's tolerance
 
 

@@ -81,7 +81,7 @@ int make_tensor_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const 
 // ---- device status word ----------------------------------------------------------------------
 // Host-mapped so the host can read it without a device allocation or a copy.
 static int* g_status_host = nullptr;
-static int* g_status_dev = nullptr;
+static std::atomic<int*> g_status_dev{nullptr};   // published once; read without the once-flag by paths that must not allocate
 static std::once_flag g_status_once;
 
 int* device_status_word() {
@@ -91,11 +91,15 @@ int* device_status_word() {
       g_status_host = (int*)h;
       g_status_host[0] = 0;
       void* d = nullptr;
-      if (cudaHostGetDevicePointer(&d, h, 0) == cudaSuccess) g_status_dev = (int*)d;
+      if (cudaHostGetDevicePointer(&d, h, 0) == cudaSuccess) g_status_dev.store((int*)d, std::memory_order_release);
     }
   });
-  return g_status_dev;
+  return g_status_dev.load(std::memory_order_acquire);
 }
+
+// The status word if some earlier call created it (tl_b200_init does), nullptr otherwise: for
+// paths that must not allocate.
+int* device_status_word_if_created() { return g_status_dev.load(std::memory_order_acquire); }
 
 int take_device_status() {
   if (!g_status_host) return 0;
@@ -121,6 +125,9 @@ int tl_b200_init(int device) {
                     "tl_b200_init: device %d is sm_%d%d; this library holds sm_100a code only", device,
                     major, minor);
   TL_CUDA(cudaFree(0));
+  // created here, where allocating is allowed, so that entry points that must not allocate can still
+  // report a kernel that gave up a bounded wait
+  tl::device_status_word();
   return TL_B200_OK;
 }
 

@@ -39,6 +39,18 @@ __device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t v) {
   return __half22float2(*reinterpret_cast<__half2*>(&h));
 }
 
+// Sequence lengths and page ids live in device memory, so the host cannot validate them.  A length is
+// clamped to what the block-table row and the cache can hold; a page id outside the cache marks its tile
+// as masked (the loads are redirected to row 0 of the cache and the scores of the tile become -inf).
+__device__ __forceinline__ int mla_len(const int* __restrict__ seqlens, int b, int cap) {
+  return min(max(__ldg(seqlens + b), 0), cap);
+}
+__device__ __forceinline__ bool mla_page_ok(int page, int num_pages) { return (unsigned)page < (unsigned)num_pages; }
+inline int mla_len_cap(int64_t max_pages_per_seq, int64_t num_pages, int64_t page_size) {
+  const int64_t cap = (max_pages_per_seq < num_pages ? max_pages_per_seq : num_pages) * page_size;
+  return (int)(cap < 0x7fffffc0ll ? cap : 0x7fffffc0ll);
+}
+
 // Launches the persistent, work-balanced decode (mla_persistent.cu).  `workspace` must hold
 // mla_persistent_workspace_bytes(batch) bytes.  Returns 0 or a TL_B200_E code.
 int64_t mla_persistent_workspace_bytes(int64_t batch);

@@ -38,6 +38,7 @@ struct MlaParams {
   const int* order;            // [batch] sequence ids, longest first
   void* out;                   // [batch, heads, 512]
   int batch, heads, page_size, max_pages;
+  int len_cap, num_pages;      // bounds for the lengths and page ids read on the device
   float scale_log2;
   int* status;
 };
@@ -83,7 +84,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int b = p.order[blockIdx.x >> 1];
   const int half = blockIdx.x & 1;
-  const int seqlen = max(p.seqlens[b], 0);
+  const int seqlen = mla_len(p.seqlens, b, p.len_cap);
   const int n_tiles = (seqlen + kMlaBN - 1) / kMlaBN;
   const int* table = p.block_table + (int64_t)b * p.max_pages;
 
@@ -129,7 +130,8 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
         if (j == 1 && !(ok = mbar_wait(bar_qready, 0, abort_flag))) break;   // stages 1-2 park Q's residual until then
         const int tok = j * kMlaBN;
         const int page = __ldg(table + tok / p.page_size);
-        const int row = page * p.page_size + tok % p.page_size;      // row of the flattened cache
+        // row of the flattened cache; a page id outside the cache reads row 0 and the softmax masks the tile
+        const int row = mla_page_ok(page, p.num_pages) ? page * p.page_size + tok % p.page_size : 0;
         const uint32_t full = bar_kvfull + 8 * st;
         mbar_expect_tx(full, kMlaStageBytes);
 #pragma unroll
@@ -290,6 +292,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
 #pragma unroll 4
     for (int t = st_id * 4; t < tok_end; t += kMlaSoftmaxThreads * 4) {
       const int page = __ldg(table + t / p.page_size);
+      if (!mla_page_ok(page, p.num_pages)) continue;           // masked tile
       const float4 v = __ldg(reinterpret_cast<const float4*>(p.kv_scale + (int64_t)page * p.page_size + t % p.page_size));
       max_ts = fmaxf(max_ts, v.x);                              // slots past the end hold arbitrary bytes
       if (t + 1 < tok_end) max_ts = fmaxf(max_ts, v.y);
@@ -315,6 +318,7 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
     const uint32_t t_o = tmem_base + kMlaColO + wg * 128 + lane_off;
     for (int j = 0; j < n_tiles && ok; ++j) {
       const uint32_t t_s = tmem_base + kMlaColS + (j & 1) * kMlaBN + lane_off;
+      const int tile_page = __ldg(table + j * kMlaBN / p.page_size);                 // on its way during the wait
       ok = mbar_wait(bar_sfull + 8 * (j & 1), (j >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -323,7 +327,8 @@ mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams
       tmem_ld_32x32(t_s + wg * 32, sv);
       tmem_ld_wait();
       const float4* ts4 = reinterpret_cast<const float4*>(base_ptr + (stage_addr(j % kMlaStages) - base) + kMlaTile) + wg * 8;
-      const int valid = seqlen - j * kMlaBN - wg * 32;      // tokens of this half tile that exist
+      // tokens of this half tile that exist; none if the tile's page id is outside the cache
+      const int valid = mla_page_ok(tile_page, p.num_pages) ? seqlen - j * kMlaBN - wg * 32 : 0;
       // sp = acc * token_scale (packed pairs); the per-head factor s_scale > 0 is applied inside the
       // exponent, so the row maximum can be taken on sp
       float2 sp[16];
@@ -483,6 +488,7 @@ struct MlaRowParams {
   const int *block_table, *seqlens;
   void* out;
   int batch, heads, d, dv, page_size, max_pages;
+  int len_cap, num_pages;
   float scale;
 };
 
@@ -494,13 +500,15 @@ mla_rows_kernel(const MlaRowParams p) {
   const int b = idx / p.heads;
   const TQ* q = (const TQ*)p.q + (int64_t)idx * p.d;
   const int* table = p.block_table + (int64_t)b * p.max_pages;
-  const int seqlen = p.seqlens[b];
+  const int seqlen = mla_len(p.seqlens, b, p.len_cap);
   float acc[MAXDV];
 #pragma unroll
   for (int i = 0; i < MAXDV; ++i) acc[i] = 0.f;
   float m = -INFINITY, l = 0.f;
   for (int t = 0; t < seqlen; ++t) {
-    const int64_t row = (int64_t)table[t / p.page_size] * p.page_size + t % p.page_size;
+    const int page = table[t / p.page_size];
+    if (!mla_page_ok(page, p.num_pages)) continue;             // a page id outside the cache: its tokens are masked
+    const int64_t row = (int64_t)page * p.page_size + t % p.page_size;
     const TC* kr = (const TC*)p.cache + row * p.d;
     const float ts = p.kv_scale ? p.kv_scale[row] : 1.f;
     float s = 0.f;
@@ -596,6 +604,7 @@ extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, con
     MlaParams p;
     p.q = q; p.kv_scale = kv_scale; p.block_table = block_table; p.seqlens = cache_seqlens; p.order = order; p.out = out;
     p.batch = (int)batch; p.heads = (int)heads; p.page_size = (int)page_size; p.max_pages = (int)max_pages_per_seq;
+    p.len_cap = mla_len_cap(max_pages_per_seq, num_pages, page_size); p.num_pages = (int)num_pages;
     p.scale_log2 = softmax_scale * 1.4426950408889634f;
     p.status = device_status_word();
     const unsigned grid = (unsigned)(2 * batch);
@@ -616,6 +625,7 @@ extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, con
   rp.q = q; rp.cache = kv_cache; rp.kv_scale = kv_scale; rp.block_table = block_table; rp.seqlens = cache_seqlens;
   rp.out = out; rp.batch = (int)batch; rp.heads = (int)heads; rp.d = (int)d; rp.dv = (int)dv;
   rp.page_size = (int)page_size; rp.max_pages = (int)max_pages_per_seq; rp.scale = softmax_scale;
+  rp.len_cap = mla_len_cap(max_pages_per_seq, num_pages, page_size); rp.num_pages = (int)num_pages;
   if (q_dtype == TL_BF16) return launch_mla_rows_cache<__nv_bfloat16>(rp, cache_dtype, s);
   return launch_mla_rows_cache<__half>(rp, cache_dtype, s);
 }
@@ -637,7 +647,7 @@ static __device__ __align__(256) int g_mla_order_scratch[kMlaNoAllocMaxBatch];
 // In host code the array's name is only a handle for the runtime, not a device address, so the
 // address is looked up once per device (with that device current) and cached.
 constexpr int kMaxDevices = 64;
-static int* g_mla_order_ptr[kMaxDevices] = {};
+static std::atomic<int*> g_mla_order_ptr[kMaxDevices] = {};     // host threads may make their first calls together
 }  // namespace tl
 
 extern "C" int tl_b200_mla_decode_paged_noalloc(const void* q, const void* kv_cache, const float* kv_scale,
@@ -662,12 +672,11 @@ extern "C" int tl_b200_mla_decode_paged_noalloc(const void* q, const void* kv_ca
   int dev = 0;
   TL_CUDA(cudaGetDevice(&dev));
   TL_REQUIRE(dev >= 0 && dev < kMaxDevices, "mla_decode_paged_noalloc: device index %d out of range", dev);
-  if (g_mla_order_ptr[dev] == nullptr) {
-    int* ptr = nullptr;
-    TL_CUDA(cudaGetSymbolAddress((void**)&ptr, g_mla_order_scratch));
-    g_mla_order_ptr[dev] = ptr;
+  int* order = g_mla_order_ptr[dev].load(std::memory_order_acquire);
+  if (order == nullptr) {
+    TL_CUDA(cudaGetSymbolAddress((void**)&order, g_mla_order_scratch));
+    g_mla_order_ptr[dev].store(order, std::memory_order_release);       // every thread looks up the same address
   }
-  int* order = g_mla_order_ptr[dev];
   cudaStream_t s = (cudaStream_t)stream;
   CUtensorMap tm;
   uint64_t dims[2] = {(uint64_t)kMlaD, (uint64_t)(num_pages * page_size)};
@@ -682,8 +691,11 @@ extern "C" int tl_b200_mla_decode_paged_noalloc(const void* q, const void* kv_ca
   MlaParams p;
   p.q = q; p.kv_scale = kv_scale; p.block_table = block_table; p.seqlens = cache_seqlens; p.order = order; p.out = out;
   p.batch = (int)batch; p.heads = (int)heads; p.page_size = (int)page_size; p.max_pages = (int)max_pages_per_seq;
+  p.len_cap = mla_len_cap(max_pages_per_seq, num_pages, page_size); p.num_pages = (int)num_pages;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
-  p.status = nullptr;      // the host-visible status word is allocated on demand; this path allocates nothing
+  // The host-visible status word is created by tl_b200_init (or by an earlier call of another entry
+  // point); this path allocates nothing, so without it a kernel that gives up a wait cannot say so.
+  p.status = device_status_word_if_created();
   if (q_dtype == TL_BF16) {
     auto kernel = mla_decode_fp8_kernel<__nv_bfloat16>;
     TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlaSmem));

@@ -39,6 +39,7 @@ struct MlaPrepParams {
   int4* sched;                 // [workers] begin sequence, begin tile, end sequence, end tile (exclusive)
   int2* seq_info;              // [batch] partial slot of the first piece, number of pieces
   int batch, heads, page_size, max_pages, workers;
+  int len_cap, num_pages;      // bounds for the lengths and page ids read on the device
 };
 
 // Block 0: the schedule (one thread walks the sequences, so it starts first).  Blocks [1, batch]:
@@ -61,7 +62,7 @@ mla_prepare_kernel(const MlaPrepParams p) {
     const int b0 = threadIdx.x * per;
     int local = 0;
     for (int i = 0; i < per; ++i)
-      if (b0 + i < p.batch) local += (max(p.seqlens[b0 + i], 0) + kMlaBN - 1) / kMlaBN + kMlaSegOverhead;
+      if (b0 + i < p.batch) local += (mla_len(p.seqlens, b0 + i, p.len_cap) + kMlaBN - 1) / kMlaBN + kMlaSegOverhead;
     int incl = local;                                      // inclusive scan over the block
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -75,7 +76,7 @@ mla_prepare_kernel(const MlaPrepParams p) {
     for (int i = 0; i < per; ++i)
       if (b0 + i < p.batch) {
         C[b0 + i] = before;
-        before += (max(p.seqlens[b0 + i], 0) + kMlaBN - 1) / kMlaBN + kMlaSegOverhead;
+        before += (mla_len(p.seqlens, b0 + i, p.len_cap) + kMlaBN - 1) / kMlaBN + kMlaSegOverhead;
       }
     if (threadIdx.x == 255) C[p.batch] = before;           // the last thread's running sum is the total
     __syncthreads();
@@ -108,7 +109,7 @@ mla_prepare_kernel(const MlaPrepParams p) {
     // ---------------------------------------------------------------- largest token scale of a sequence
     // (P is multiplied by 32 * scale[t] / this before it is cut to e4m3)
     const int b = blockIdx.x - 1;
-    const int seqlen = max(p.seqlens[b], 0);
+    const int seqlen = mla_len(p.seqlens, b, p.len_cap);
     const int* table = p.block_table + (int64_t)b * p.max_pages;
     float m = 0.f;
     for (int t0 = 0; t0 < seqlen; t0 += 4 * 1024) {
@@ -119,7 +120,8 @@ mla_prepare_kernel(const MlaPrepParams p) {
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (t < seqlen) {
           const int page = __ldg(table + t / p.page_size);
-          v[i] = __ldg(reinterpret_cast<const float4*>(p.kv_scale + (int64_t)page * p.page_size + t % p.page_size));
+          if (mla_page_ok(page, p.num_pages))       // the tokens of a page id outside the cache are masked
+            v[i] = __ldg(reinterpret_cast<const float4*>(p.kv_scale + (int64_t)page * p.page_size + t % p.page_size));
         }
       }
 #pragma unroll
@@ -231,6 +233,7 @@ struct MlaSchedParams {
   float* part_o;               // [2 * workers][128][512] normalised partial outputs
   float* part_lse;             // [2 * workers][128] their log2-sum-exp
   int batch, heads, page_size, max_pages;
+  int len_cap, num_pages;
   float scale_log2;
   int* status;
 };
@@ -244,10 +247,10 @@ struct MlaPiece {
 
 // The pieces of a range are its sequences in order; the first starts at the range's begin tile, the
 // last (if the end tile is not zero) stops at the end tile.  An empty sequence is a piece of zero tiles.
-__device__ __forceinline__ MlaPiece mla_piece(const int4 sc, int seq, const int* __restrict__ seqlens, int batch) {
+__device__ __forceinline__ MlaPiece mla_piece(const int4 sc, int seq, const int* __restrict__ seqlens, int batch, int len_cap) {
   MlaPiece pc{seq, 0, 0, false, false};
   if (seq >= batch || seq > sc.z || (seq == sc.z && sc.w == 0)) return pc;
-  const int n_seq = (max(__ldg(seqlens + seq), 0) + kMlaBN - 1) / kMlaBN;
+  const int n_seq = (mla_len(seqlens, seq, len_cap) + kMlaBN - 1) / kMlaBN;
   pc.t0 = (seq == sc.x) ? sc.y : 0;
   const int t1 = (seq == sc.z) ? sc.w : n_seq;
   pc.n = max(t1 - pc.t0, 0);
@@ -328,11 +331,11 @@ mla_decode_persistent_kernel(const __grid_constant__ CUtensorMap tm_kv, const __
     if (elect_one()) {
       bool ok = true;
       int g = 0, a = 0;                            // tiles and non-empty pieces so far
-      MlaPiece nxt = mla_piece(sc, sc.x, p.seqlens, p.batch);
+      MlaPiece nxt = mla_piece(sc, sc.x, p.seqlens, p.batch, p.len_cap);
       while (nxt.valid && ok) {
         const MlaPiece pc = nxt;
         const int seq = pc.seq;
-        nxt = mla_piece(sc, seq + 1, p.seqlens, p.batch);        // its length is on the way while this piece runs
+        nxt = mla_piece(sc, seq + 1, p.seqlens, p.batch, p.len_cap);        // its length is on the way while this piece runs
         if (pc.n == 0) continue;
         if (a > 0 && !(ok = mbar_wait(bar_qfree, (a - 1) & 1, abort_flag))) break;
         mbar_expect_tx(bar_qfull, kMlaQBytes);
@@ -345,7 +348,8 @@ mla_decode_persistent_kernel(const __grid_constant__ CUtensorMap tm_kv, const __
           if (!(ok = mbar_wait(bar_kvempty + 8 * st, ((g / kMlaStages) & 1) ^ 1, abort_flag))) break;
           const int tok = (pc.t0 + j) * kMlaBN;
           const int page = __ldg(table + tok / p.page_size);
-          const int row = page * p.page_size + tok % p.page_size;      // row of the flattened cache
+          // row of the flattened cache; a page id outside the cache reads row 0 and the softmax masks the tile
+          const int row = mla_page_ok(page, p.num_pages) ? page * p.page_size + tok % p.page_size : 0;
           const uint32_t full = bar_kvfull + 8 * st;
           mbar_expect_tx(full, kMlaStageBytes);
 #pragma unroll
@@ -367,10 +371,10 @@ mla_decode_persistent_kernel(const __grid_constant__ CUtensorMap tm_kv, const __
       const uint64_t v_desc = smem_desc_sw128(sm_kv, kMlaBN * 128, 1024);
       bool ok = true;
       int g0 = 0, a = 0;                           // first tile counter of the piece, non-empty pieces so far
-      MlaPiece nxt = mla_piece(sc, sc.x, p.seqlens, p.batch);
+      MlaPiece nxt = mla_piece(sc, sc.x, p.seqlens, p.batch, p.len_cap);
       while (nxt.valid && ok) {
         const MlaPiece pc = nxt;
-        nxt = mla_piece(sc, pc.seq + 1, p.seqlens, p.batch);
+        nxt = mla_piece(sc, pc.seq + 1, p.seqlens, p.batch, p.len_cap);
         if (pc.n == 0) continue;
         auto issue_s = [&](int j) {
           const int g = g0 + j, st = g % kMlaStages;
@@ -441,7 +445,7 @@ mla_decode_persistent_kernel(const __grid_constant__ CUtensorMap tm_kv, const __
     // goes to tensor memory: each warpgroup moves its share of the columns, 16-byte loads that are
     // contiguous across a warp, all in flight together, then stores of 32 words.
     auto stage_qlo = [&](MlaPiece pc) {
-      while (pc.valid && pc.n == 0) pc = mla_piece(sc, pc.seq + 1, p.seqlens, p.batch);
+      while (pc.valid && pc.n == 0) pc = mla_piece(sc, pc.seq + 1, p.seqlens, p.batch, p.len_cap);
       if (!pc.valid) return;
       constexpr int UN = 32 / kWG;                // 16-byte units per thread
       const uint4* src = reinterpret_cast<const uint4*>(p.qlo) + ((int64_t)pc.seq * 32 + wg * UN) * kMlaHeads + h;
@@ -463,13 +467,13 @@ mla_decode_persistent_kernel(const __grid_constant__ CUtensorMap tm_kv, const __
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_qlo);
     };
-    MlaPiece nxt = mla_piece(sc, sc.x, p.seqlens, p.batch);
+    MlaPiece nxt = mla_piece(sc, sc.x, p.seqlens, p.batch, p.len_cap);
     stage_qlo(nxt);
     int g0 = 0, a = 0;
     while (nxt.valid && ok) {
       const MlaPiece pc = nxt;
       const int seq = pc.seq;
-      nxt = mla_piece(sc, seq + 1, p.seqlens, p.batch);          // its length is on the way while this piece runs
+      nxt = mla_piece(sc, seq + 1, p.seqlens, p.batch, p.len_cap);          // its length is on the way while this piece runs
       if (pc.n == 0) {
         TQ* out = reinterpret_cast<TQ*>(p.out) + ((int64_t)seq * p.heads + h) * kMlaDV + half * 256 + wg * OC;
         if (pc.whole && h < p.heads)              // an empty sequence: zeros
@@ -480,12 +484,14 @@ mla_decode_persistent_kernel(const __grid_constant__ CUtensorMap tm_kv, const __
       const float max_ts = __ldg(p.seq_max_ts + seq);
       const float ts_norm = max_ts > 0.f ? kPScale / max_ts : kPScale;
       const float s_scale = q_scale * p.scale_log2;
-      const int seqlen = max(__ldg(p.seqlens + seq), 0);
+      const int seqlen = mla_len(p.seqlens, seq, p.len_cap);
+      const int* table = p.block_table + (int64_t)seq * p.max_pages;
       // online softmax: a row is shared by one thread of each warpgroup
       float m_used = -INFINITY, row_sum = 0.f;
       for (int j = 0; j < pc.n && ok; ++j) {
         const int g = g0 + j;
         const uint32_t t_s = tmem_base + kMlaColS + (g & 1) * kMlaBN + lane_off;
+        const int tile_page = __ldg(table + (pc.t0 + j) * kMlaBN / p.page_size);     // on its way during the wait
         ok = mbar_wait(bar_sfull + 8 * (g & 1), (g >> 1) & 1, abort_flag);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
@@ -495,7 +501,8 @@ mla_decode_persistent_kernel(const __grid_constant__ CUtensorMap tm_kv, const __
         tmem_ld_32x32(t_s + wg * TOK, sv);
         tmem_ld_wait();
         const float4* ts4 = reinterpret_cast<const float4*>(base_ptr + (stage_addr(g % kMlaStages) - base) + kMlaTile) + wg * NV;
-        const int valid = seqlen - (pc.t0 + j) * kMlaBN - wg * TOK;      // tokens of this share that exist
+        // tokens of this share that exist; none if the tile's page id is outside the cache
+        const int valid = mla_page_ok(tile_page, p.num_pages) ? seqlen - (pc.t0 + j) * kMlaBN - wg * TOK : 0;
         // sp = acc * token_scale (packed pairs); the per-head factor s_scale > 0 is applied inside the
         // exponent, so the row maximum can be taken on sp
         float2 sp[TOK / 2];
@@ -834,11 +841,13 @@ int mla_persistent_launch(const void* q, const void* kv_cache, const float* kv_s
   pp.sched = reinterpret_cast<int4*>(ws + w.sched); pp.seq_info = reinterpret_cast<int2*>(ws + w.seq_info);
   pp.batch = (int)batch; pp.heads = (int)heads; pp.page_size = (int)page_size; pp.max_pages = (int)max_pages_per_seq;
   pp.workers = workers;
+  pp.len_cap = mla_len_cap(max_pages_per_seq, num_pages, page_size); pp.num_pages = (int)num_pages;
   MlaSchedParams sp;
   sp.qlo = pp.qlo; sp.q_scale = pp.q_scale; sp.seq_max_ts = pp.seq_max_ts; sp.kv_scale = kv_scale;
   sp.block_table = block_table; sp.seqlens = cache_seqlens; sp.sched = pp.sched; sp.out = out;
   sp.part_o = reinterpret_cast<float*>(ws + w.part_o); sp.part_lse = reinterpret_cast<float*>(ws + w.part_lse);
   sp.batch = (int)batch; sp.heads = (int)heads; sp.page_size = (int)page_size; sp.max_pages = (int)max_pages_per_seq;
+  sp.len_cap = pp.len_cap; sp.num_pages = pp.num_pages;
   sp.scale_log2 = softmax_scale * 1.4426950408889634f;
   sp.status = device_status_word();
   if (q_dtype == TL_BF16) return mla_persistent_launch_t<__nv_bfloat16>(tm_kv, tm_q, pp, sp, pp.seq_info, stream);

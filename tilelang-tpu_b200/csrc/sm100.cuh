@@ -327,6 +327,7 @@ int make_tensor_map(CUtensorMap* map, CUtensorMapDataType type, int rank, const 
 
 // Library-owned status word (host-mapped, one per process) that kernels write on an aborted wait.
 int* device_status_word();
+int* device_status_word_if_created();
 int take_device_status();
 
 }  // namespace tl

@@ -104,6 +104,12 @@ def _match_matmul(func: PrimFunc):
     bn = b_tile.shape[0] if trans_b else b_tile.shape[1]
     _check_tiling(func, "matmul", [(M, bm), (N, bn), (K, bk)])
     _require(const_value(ops[1].args[1]) == K // bk, "matmul: the K loop must cover K")
+    if trans_b and K // bk > 1:
+        # `C = A B^T` carries no accumulate flag in the reference's generated code
+        # (src/target/codegen_ppl.cc:1276-1279): every K iteration overwrites C, so the program
+        # does not compute the full product.  The tile-op executor reproduces that; the fused GEMM
+        # (which sums over all of K) is bound only where the two agree.
+        return None
     _require(sorted(_grid(func)) == sorted([N // bn, M // bm]), "matmul: the grid must cover C")
     ia, ib, ic = A.param_index, B.param_index, C.param_index
     from .. import ops as native
