@@ -1,13 +1,15 @@
 #!/usr/bin/env python
 """Benchmark of the operator path on B200.
 
-One step = one pass of the Llama-3-8B memory-bound operators over a batch of 8192 tokens, bf16:
+One step = one pass of the Llama-3-8B memory-bound operators over ONE batch of 8192 tokens, bf16:
 RMSNorm over hidden 4096 (weight, eps 1e-6), RoPE on Q[8192,32,128] and K[8192,8,128]
-(theta 500000) and SwiGLU on [8192,14336] — four kernel launches through the C ABI.
-`value` is algorithmic GB/s (inputs read once + outputs written once) with inputs resident in
-HBM; `e2e` is the same metric through the host-tensor call path with pinned host buffers and the
-host<->device copies inside the timed region.  With N ranks every rank owns its own batch
-(data-parallel, no collective on the data path): weak scaling.
+(theta 500000) and SwiGLU on [8192,14336] - four kernels of the library per step.
+With N ranks the rows (tokens) of that one batch are split over the GPUs, 8192/N each (strong
+scaling); no collective is on the data path, and the all-gather of the four outputs is timed
+separately (`ms_with_output_gather`).  `value` is algorithmic GB/s of the whole batch (inputs read
+once + outputs written once) with inputs resident in HBM, device time, max over ranks; `e2e` is the
+same metric through `tilelang.compile(...)` programs called with pinned HOST tensors, the
+host<->device copies inside the timed region.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -42,6 +44,7 @@ SWIGLU_DRAM_BYTES_PER_TOKEN = 301.8e6 / 4096
 METRIC = "GEMM/attn TFLOP/s and norm/RoPE GB/s vs B200 roofline at 1/2/4/8 GPUs"
 WORKLOAD = ("llama3-8b memory-bound ops, bf16, 8192 tokens: rmsnorm[8192x4096] + "
             "rope(Q[8192,32,128],K[8192,8,128]) + swiglu[8192x14336]")
+TOKENS = 8192
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -126,6 +129,19 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------
+def config_for(world: int, tokens: int = TOKENS) -> dict:
+    """The `config` object, identical in both arms."""
+    return {"workload": WORKLOAD, "tokens": tokens, "sharding": f"rows (tokens) split over {world} GPU(s), {tokens // world} each",
+            "l2": "every rank rotates over input sets that together exceed 1.0 GB (> 126 MB L2); no flush"}
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def cpu_pass(w, O):
     """One pass of the workload through the CPU restatement; returns nothing (timing only)."""
     O.rmsnorm(w["x"], w["weight"], eps=w["eps"])
@@ -146,16 +162,21 @@ def time_cpu(w, total_bytes, reps=3):
 
 
 def run_reference(args, rank):
-    """Reference arm: the reference's CPU path for this workload on the host cores."""
+    """Reference arm: the reference's CPU path for this workload on the host cores (rank 0 only)."""
     if rank != 0:
         return
+    # torchrun exports OMP_NUM_THREADS=1 to its workers; the reference arm uses every host core it may run on
+    threads = host_threads()
+    torch.set_num_threads(threads)
     from tilelang import workloads
-    w = workloads.llama8b_memory_ops()
-    total = sum(workloads.llama8b_algorithmic_bytes().values())
+    w = workloads.llama8b_memory_ops(tokens=args.tokens)
+    total = sum(workloads.llama8b_algorithmic_bytes(tokens=args.tokens).values())
     import oracle.ops as O
-    for _ in range(max(1, min(args.warmup, 1))):
+    cap_w, cap_s = 3, 30                 # a pass is ~0.2 s on 32 cores: 30 passes keep the arm under a minute
+    warmup = max(1, min(args.warmup, cap_w))
+    steps = max(1, min(args.steps, cap_s))
+    for _ in range(warmup):
         cpu_pass(w, O)
-    steps = max(1, min(args.steps, 5))
     t = time.perf_counter()
     for _ in range(steps):
         cpu_pass(w, O)
@@ -163,29 +184,65 @@ def run_reference(args, rank):
     gbs = total / dt / 1e9
     line = {
         "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus,
-        "steps": steps, "warmup": 1, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "tokens": 8192},
-        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": f"{steps} full passes of the 8192-token workload "
-                                   "(torch-CPU restatement of the demos' check functions; the "
-                                   "reference's cmodel emulator is not installable)"},
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": config_for(max(args.gpus, 1), args.tokens),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"{steps} full passes of the {args.tokens}-token workload on {threads} threads "
+                                   "(torch-CPU restatement of the demos' check functions; the reference's "
+                                   "cmodel emulator is not installable); steps above "
+                                   f"{cap_s} and warm-up above {cap_w} are capped to bound the run"},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
 # ------------------------------------------------------------------------------------------
+class Step:
+    """The four launches of one step over this rank's rows, for one input set."""
+
+    def __init__(self, ops, d, outs, eps):
+        self.ops, self.d, self.o, self.eps = ops, d, outs, eps
+
+    def head(self):
+        d, o = self.d, self.o
+        self.ops.rmsnorm(d["x"], o["y"], d["weight"], eps=self.eps)
+        self.ops.rope(d["q"], d["cos"], d["sin"], o["qo"])
+        self.ops.rope(d["k"], d["cos"], d["sin"], o["ko"])
+
+    def tail(self):
+        self.ops.swiglu(self.d["gate"], self.d["up"], self.o["so"])
+
+    def full(self):
+        self.head()
+        self.tail()
+
+
+def capture(fn):
+    """CUDA graph of the launches `fn` makes (None if this driver/runtime cannot capture them)."""
+    try:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return g
+    except Exception as exc:      # plain launches still measure the kernels; the line says which mode ran
+        print(f"bench: graph capture unavailable ({type(exc).__name__}: {exc}); plain launches", file=sys.stderr)
+        torch.cuda.synchronize()
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--tokens", type=int, default=8192, help="tokens per GPU (default: the named config)")
+    ap.add_argument("--tokens", type=int, default=TOKENS,
+                    help="tokens of the batch (default: the named configuration; smaller values are for profiler captures)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="plain launches instead of CUDA graphs")
     ap.add_argument("--no-kernels", action="store_true",
-                    help="skip the per-kernel section (GEMM bf16/FP8, FlashAttention, MLA decode)")
+                    help="skip the per-kernel section (GEMM bf16/FP8, fused MLP, FlashAttention, MLA decode)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -197,7 +254,9 @@ def main():
         return
 
     import torch.distributed as dist
-    from tilelang import ops, workloads
+    import tilelang
+    from tilelang import ops, parallel, workloads
+    from tilelang import programs as P
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the operator path has no CPU fallback")
@@ -209,34 +268,58 @@ def main():
     warmup = max(args.warmup, 3)
     steps = max(args.steps, 1)
 
+    # ---- ONE 8192-token problem (seed 1, generated on the CPU so a checker sees the same bits); this rank's rows
     tokens = args.tokens
-    w = workloads.llama8b_memory_ops(tokens=tokens, seed=1 + rank)   # each rank owns its own batch
+    w = workloads.llama8b_memory_ops(tokens=tokens, seed=1)
     alg = workloads.llama8b_algorithmic_bytes(tokens=tokens)
     bytes_per_step = sum(alg.values())
+    lo, hi = parallel.partition(tokens, world, rank)
+    rows = hi - lo
+    row_keys = ("x", "q", "k", "cos", "sin", "gate", "up")
+    mine = {k: w[k][lo:hi].contiguous() for k in row_keys}
+    mine["weight"] = w["weight"]
 
-    d = {k: (v.to(dev) if isinstance(v, torch.Tensor) else v) for k, v in w.items()}
-    y = torch.empty_like(d["x"])
-    qo = torch.empty_like(d["q"])
-    ko = torch.empty_like(d["k"])
-    so = torch.empty_like(d["gate"])
-
-    def step(ev=None):
-        ops.rmsnorm(d["x"], y, d["weight"], eps=w["eps"])
-        ops.rope(d["q"], d["cos"], d["sin"], qo)
-        ops.rope(d["k"], d["cos"], d["sin"], ko)
-        if ev is not None:
-            ev[0].record()
-        ops.swiglu(d["gate"], d["up"], so)
-        if ev is not None:
-            ev[1].record()
+    # Input sets: set 0 is the problem itself; sets 1.. are the same rows rotated by a few positions (distinct
+    # buffers, same values), so that consecutive steps never find their inputs in the 126 MB L2.
+    n_sets = max(1, world)
+    base = {k: v.to(dev) for k, v in mine.items()}
+    sets = [base] + [{k: (torch.roll(v, 7 * s, 0).contiguous() if k in row_keys and k not in ("cos", "sin") else v)
+                      for k, v in base.items()} for s in range(1, n_sets)]
+    shapes = {"y": (tokens, 4096), "qo": (tokens, 32, 128), "ko": (tokens, 8, 128), "so": (tokens, 14336)}
+    gathers = [{k: parallel.ShardedOutput(shp, 0, torch.bfloat16, dev) for k, shp in shapes.items()} for _ in range(n_sets)]
+    steps_of = [Step(ops, sets[s], {k: so.local for k, so in gathers[s].items()}, w["eps"]) for s in range(n_sets)]
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(warmup):
-        step()
+    for st in steps_of:                      # warm-up of every set with plain launches (also initialises the library)
+        st.full()
+    barrier()
+    graphs = None
+    if not args.no_graph:
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            gs = [(capture(st.full), capture(st.head), capture(st.tail)) for st in steps_of]
+        torch.cuda.current_stream().wait_stream(side)
+        if all(g is not None for trio in gs for g in trio):
+            graphs = gs
+    mode = "CUDA graph replay (4 kernel nodes per step)" if graphs else "plain launches through the C ABI"
+
+    def run_step(i, ev=None):
+        s = i % n_sets
+        if ev is None:
+            graphs[s][0].replay() if graphs else steps_of[s].full()
+            return
+        graphs[s][1].replay() if graphs else steps_of[s].head()
+        ev[0].record()
+        graphs[s][2].replay() if graphs else steps_of[s].tail()
+        ev[1].record()
+
+    for i in range(warmup):
+        run_step(i)
     barrier()
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
@@ -245,7 +328,7 @@ def main():
         time.sleep(0.25)
 
     # events bracket the dominant kernel (SwiGLU, 70% of the bytes) inside the timed region
-    n_ev = min(steps, 512)
+    n_ev = min(steps, 256)
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(n_ev)]
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -254,86 +337,94 @@ def main():
         sampler.mark_begin()
     start.record()
     for i in range(steps):
-        step(evs[i] if i < n_ev else None)
+        run_step(i, evs[i] if i < n_ev else None)
     end.record()
     barrier()
     if sampler:
         sampler.mark_end()
-    launches = ops.launch_count() - launches0
+    launches = 4 * steps if graphs else ops.launch_count() - launches0
     ms_total = start.elapsed_time(end)
     swiglu_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
     clocks = sampler.stop() if sampler else None
 
-    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    def max_over_ranks(v):
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_per_step = max_over_ranks(ms_total) / steps
+    swiglu_ms = max_over_ranks(swiglu_ms)
+    value = bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # ---- the same steps followed by the all-gather of the four outputs (in place, one NCCL call per output)
+    ms_gather = None
+    gathered_bytes = sum(2 * int(torch.tensor(shp).prod()) for shp in shapes.values())
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_total = float(t.item())
-    ms_per_step = ms_total / steps
-    value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
+        g_steps = max(3, min(steps, 50))
 
-    # ---- end to end: pinned host tensors in, results back on the host, every step ----------
-    hin = {k: w[k].pin_memory() for k in ("x", "weight", "q", "k", "cos", "sin", "gate", "up")}
-    hout = {"y": torch.empty_like(w["x"]).pin_memory(), "qo": torch.empty_like(w["q"]).pin_memory(),
-            "ko": torch.empty_like(w["k"]).pin_memory(), "so": torch.empty_like(w["gate"]).pin_memory()}
-    h2d = sum(v.numel() * v.element_size() for v in hin.values())
-    d2h = sum(v.numel() * v.element_size() for v in hout.values())
+        def step_and_gather(i):
+            run_step(i)
+            for so in gathers[i % n_sets].values():
+                so.gather()
 
-    # Three streams and two sets of device buffers: the host->device copy of step i+1 and the
-    # device->host copy of step i-1 run while step i computes (PCIe is full duplex).  Every step's copies
-    # are inside the timed region; nothing is reused from one step to the next.
-    s_in, s_cmp, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-    din = [{k: torch.empty_like(v, device=dev) for k, v in hin.items()} for _ in range(2)]
-    dout = [{"y": torch.empty_like(y), "qo": torch.empty_like(qo), "ko": torch.empty_like(ko), "so": torch.empty_like(so)}
-            for _ in range(2)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_cmp = [torch.cuda.Event() for _ in range(2)]
-    ev_out = [torch.cuda.Event() for _ in range(2)]
+        for i in range(3):
+            step_and_gather(i)
+        barrier()
+        s1, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s1.record()
+        for i in range(g_steps):
+            step_and_gather(i)
+        e1.record()
+        barrier()
+        ms_gather = max_over_ranks(s1.elapsed_time(e1)) / g_steps
+        # the gathered set-0 outputs are the full tensors, in place (rows are the leading dimension)
+        assert all(so.full_view() is not None for so in gathers[0].values())
 
-    def e2e_steps_run(n):
-        for i in range(n):
-            b = i & 1
-            with torch.cuda.stream(s_in):
-                if i >= 2:
-                    s_in.wait_event(ev_cmp[b])            # the step that last read these inputs has computed
-                for k, v in hin.items():
-                    din[b][k].copy_(v, non_blocking=True)
-                ev_in[b].record(s_in)
-            with torch.cuda.stream(s_cmp):
-                s_cmp.wait_event(ev_in[b])
-                if i >= 2:
-                    s_cmp.wait_event(ev_out[b])           # its previous results are on the host
-                dd, oo = din[b], dout[b]
-                ops.rmsnorm(dd["x"], oo["y"], dd["weight"], eps=w["eps"])
-                ops.rope(dd["q"], dd["cos"], dd["sin"], oo["qo"])
-                ops.rope(dd["k"], dd["cos"], dd["sin"], oo["ko"])
-                ops.swiglu(dd["gate"], dd["up"], oo["so"])
-                ev_cmp[b].record(s_cmp)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(ev_cmp[b])
-                for k in ("y", "qo", "ko", "so"):
-                    hout[k].copy_(dout[b][k], non_blocking=True)
-                ev_out[b].record(s_out)
-        for st in (s_in, s_cmp, s_out):
-            torch.cuda.current_stream().wait_stream(st)
+    # ---- end to end: the C2 programs compiled with tilelang.compile, called with pinned host tensors every step
+    del sets, steps_of, graphs, base
+    gathers = None
+    torch.cuda.empty_cache()
+    kernels_e2e = {
+        "rmsnorm": tilelang.compile(P.rmsnorm(rows, 4096, eps=w["eps"]), out_idx=-1, target="b200"),
+        "rope_q": tilelang.compile(P.rope(rows, 32, 128), out_idx=-1, target="b200"),
+        "rope_k": tilelang.compile(P.rope(rows, 8, 128), out_idx=-1, target="b200"),
+        "swiglu": tilelang.compile(P.swiglu(rows, 14336), out_idx=-1, target="b200"),
+    }
+    hin = {k: v.pin_memory() for k, v in mine.items()}
+    hin["weight"] = hin["weight"].view(1, -1)
+    hout = {k: torch.empty((rows,) + shp[1:], dtype=torch.bfloat16).pin_memory() for k, shp in shapes.items()}
+    calls = [("rmsnorm", (hin["x"], hin["weight"], hout["y"])), ("rope_q", (hin["q"], hin["cos"], hin["sin"], hout["qo"])),
+             ("rope_k", (hin["k"], hin["cos"], hin["sin"], hout["ko"])), ("swiglu", (hin["gate"], hin["up"], hout["so"]))]
+    nbytes = lambda t: t.numel() * t.element_size()      # noqa: E731
+    h2d = sum(nbytes(t) for _, a in calls for t in a[:-1])
+    d2h = sum(nbytes(a[-1]) for _, a in calls)
+
+    def e2e_run(n):
+        for _ in range(n):
+            for name, a in calls:
+                kernels_e2e[name](*a)
+        for k in kernels_e2e.values():
+            k.adapter.join()
 
     e2e_steps = max(2, min(steps, 20))
-    e2e_steps_run(2)
+    e2e_run(3)
     barrier()
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
-    for st in (s_in, s_cmp, s_out):
-        st.wait_event(s2)
-    e2e_steps_run(e2e_steps)
+    e2e_run(e2e_steps)
     e2.record()
     barrier()
-    t2 = torch.tensor([s2.elapsed_time(e2)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t2.item()) / e2e_steps
-    e2e_value = world * bytes_per_step / (e2e_ms * 1e-3) / 1e9
+    e2e_ms = max_over_ranks(s2.elapsed_time(e2)) / e2e_steps
+    e2e_value = bytes_per_step / (e2e_ms * 1e-3) / 1e9
+    h2d_all, d2h_all = max_over_ranks(float(h2d)) * world, max_over_ranks(float(d2h)) * world
+    e2e_ok = True
+    if rank == 0:                         # what came back is what the device-resident path wrote for the same rows
+        import oracle.ops as O
+        ref = O.swiglu(mine["gate"][:64], mine["up"][:64])
+        e2e_ok = bool(torch.allclose(hout["so"][:64].float(), ref.float(), atol=2e-2, rtol=2e-2))
 
-    # hand the big buffers back before the per-kernel section allocates its own
-    del hin, hout, din, dout, d, y, qo, ko, so
+    del hin, hout, calls, kernels_e2e
     torch.cuda.empty_cache()
     peaks = measured_peaks()
     kernels = None
@@ -343,33 +434,44 @@ def main():
 
     if rank == 0:
         peak, peak_kind = peaks["hbm_gbs"], peaks["note"].replace("of ", "")
-        achieved = alg["swiglu"] / (swiglu_ms * 1e-3) / 1e9
+        swiglu_bytes = alg["swiglu"] / world                     # bytes one launch moves on one GPU
+        achieved = swiglu_bytes / (swiglu_ms * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
-            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "tokens_per_gpu": tokens, "parallelism": f"dp{world}",
-                       "l2": "per-step working set 1.0 GB > 126 MB L2 (inputs larger than L2, no flush)",
-                       "bytes_per_step_per_gpu": bytes_per_step},
+            "config": config_for(world, tokens),
+            "launch_mode": mode, "bytes_per_step": bytes_per_step, "rows_per_gpu": rows, "input_sets_per_gpu": n_sets,
             "roofline": {"bound": "hbm", "kernel": "swiglu_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": f"of {peak_kind}",
-                         "traffic": SWIGLU_DRAM_BYTES_PER_TOKEN * tokens,
-                         "traffic_source": "dram__bytes of one ncu capture at 4096 tokens, scaled by the token count",
-                         "avg_launch_ms": swiglu_ms},
-            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+                         "traffic": SWIGLU_DRAM_BYTES_PER_TOKEN * rows,
+                         "traffic_source": "dram__bytes of one ncu capture at 4096 tokens, scaled by the rows of a launch",
+                         "avg_launch_ms": swiglu_ms, "bytes_per_launch": swiglu_bytes,
+                         "timing": f"CUDA events around the SwiGLU launch in the first {n_ev} steps of the timed region"},
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": int(h2d_all), "d2h_bytes_per_step": int(d2h_all),
+                    "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "path": "tilelang.compile(program, target='b200') JITKernel called with pinned host tensors; "
+                            "staging streams and buffers owned by the adapter", "results_checked": e2e_ok},
             "gpu_launches": int(launches),
             "clocks": clocks,
         }
+        if ms_gather is not None:
+            line["ms_with_output_gather"] = ms_gather
+            line["output_gather"] = {"bytes_gathered_per_step": gathered_bytes, "collective": "4 x ncclAllGather, in place",
+                                     "ms": ms_gather - ms_per_step,
+                                     "gbs_per_gpu_received": gathered_bytes * (world - 1) / world / max((ms_gather - ms_per_step) * 1e-3, 1e-9) / 1e9}
         if kernels is not None:
             line["kernels"] = kernels
-        if world == 1 and not args.no_cpu_baseline:
-            cpu_gbs, cpu_s = time_cpu(w, bytes_per_step)
+        if not args.no_cpu_baseline:
+            threads = host_threads()
+            torch.set_num_threads(threads)
+            cpu_gbs, cpu_s = time_cpu(w, bytes_per_step, reps=2 if world > 1 else 3)
             line["cpu_baseline"] = {
-                "value": cpu_gbs, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-                "sample": f"best of 3 full passes of the same 8192-token workload ({cpu_s:.2f} s per pass)"}
+                "value": cpu_gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                "sample": f"best of {2 if world > 1 else 3} full passes of the same {tokens}-token workload ({cpu_s:.2f} s per pass)"}
         print(json.dumps(line), flush=True)
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

@@ -114,7 +114,8 @@ int tl_b200_fill(void* dst, int64_t rows, int64_t cols, int64_t ld, float value,
  * codegen_ppl.cc:891-913,1280-1287), 4 max (the running maximum that ppl_reduce_max keeps with
  * clear=False, customize.py:519-560).  b_mode 0: b has the shape of a; 1: b is (rows,1)
  * and broadcasts across columns (:868-889); 2: b is ignored and `scalar` is used
- * (ppl_mul_C / ppl_add_C, :917-957).  fp32 arithmetic, rounded to `dtype`.          */
+ * (ppl_mul_C / ppl_add_C, :917-957); 3: b is (1,cols) and broadcasts down the rows (no reference
+ * form: the per-column weight of the Llama RMSNorm).  fp32 arithmetic, rounded to `dtype`.     */
 int tl_b200_binary(const void* a, const void* b, void* out, int64_t rows, int64_t cols, int op,
                    int b_mode, float scalar, int dtype, void* stream);
 
@@ -241,6 +242,35 @@ int tl_b200_mla_decode_paged_noalloc(const void* q, const void* kv_cache, const 
                                      void* out, int64_t batch, int64_t heads, int64_t page_size,
                                      int64_t max_pages_per_seq, int64_t num_pages, float softmax_scale,
                                      int q_dtype, void* stream);
+
+/* ---- generic entry point ---------------------------------------------------------
+ * One symbol with the shape of the reference's generated
+ *     extern "C" int tilelang_tpu_run(void** args)
+ * (src/tl_templates/tpu/main_template.cpp:39; ctypes prototype argtypes=[POINTER(c_void_p)],
+ * restype=c_int at tilelang/jit/adapter/cython/adapter.py:215-216), for bindings that want to keep
+ * a single prototype.  `args` holds the POINTER arguments of the typed entry point `kernel_id`
+ * names, in declaration order (a workspace pointer, where there is one, comes last); `meta` holds
+ * its non-pointer arguments in declaration order (the workspace size, where there is one, comes
+ * last), integers as they are and every float as its IEEE-754 bit pattern in the low 32 bits.
+ * The generated symbol has its program's sizes baked in; a pre-built library cannot, hence `meta`. */
+#define TL_B200_K_RMSNORM 1
+#define TL_B200_K_ROPE 2
+#define TL_B200_K_SWIGLU 3
+#define TL_B200_K_REDUCE_ROWS 4
+#define TL_B200_K_UNARY 5
+#define TL_B200_K_BINARY 6
+#define TL_B200_K_ROPE_ADD 7
+#define TL_B200_K_COPY2D 8
+#define TL_B200_K_FILL 9
+#define TL_B200_K_GATHER_ROWS 10
+#define TL_B200_K_TOPK 11
+#define TL_B200_K_GEMM 12
+#define TL_B200_K_MLP_GATE_UP 13
+#define TL_B200_K_GEMM_FP8_BLOCKSCALE 14
+#define TL_B200_K_FLASH_ATTN_FWD 15
+#define TL_B200_K_MLA_DECODE_DENSE 16
+#define TL_B200_K_MLA_DECODE_PAGED 17
+int tl_b200_run(int kernel_id, void** args, const int64_t* meta, void* stream);
 
 #ifdef __cplusplus
 }

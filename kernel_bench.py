@@ -1,6 +1,9 @@
 """Per-kernel throughput of the tensor-core programs at the benchmark shapes, sharded over the
-ranks of one node the way `parallel.py` describes (GEMM by N columns, attention by heads, MLA
-decode by sequences) with one all-gather of the outputs timed separately.
+ranks of one node the way `tilelang/parallel.py` describes (GEMM by N columns, attention by heads, MLA
+decode by sequences).  Every kernel writes its block straight into its slot of a rank-major receive
+buffer (`parallel.ShardedOutput`), and the ONE in-place all-gather of the outputs is timed separately
+(`ms_with_output_gather`); the gathered result is consumed through a zero-copy split view (columns,
+heads) or put in order by one row-gather launch (MLA decode, whose sequences are dealt out by length).
 
 Inputs are synthetic and generated on the device (these runs measure speed; parity lives in
 tests/).  Work formulas are the reference's own: GEMM 2*M*N*K
@@ -56,9 +59,10 @@ def gemm_bf16(dev, rank, world, peaks, m=8192, n=28672, k=8192):
     g = torch.Generator(device=dev).manual_seed(2)
     a = (torch.randn(m, k, generator=g, device=dev) * 0.05).bfloat16()
     b = (torch.randn(k, hi - lo, generator=g, device=dev) * 0.05).bfloat16()
-    c = torch.empty(m, hi - lo, dtype=torch.bfloat16, device=dev)
+    so = parallel.ShardedOutput((m, n), 1, torch.bfloat16, dev, multiple=256)
+    c = so.local
     ms = _time(lambda: ops.gemm(a, b, c), world)
-    ms_g = _time(lambda: (ops.gemm(a, b, c), parallel.all_gather_cat(c, 1)), world, reps=2, warmup=1) if world > 1 else ms
+    ms_g = _time(lambda: (ops.gemm(a, b, c), so.gather()), world, reps=3, warmup=2) if world > 1 else ms
     return _entry("gemm_tcgen05_kernel", f"bf16 M{m} K{k} N{n}, B row-major [K,N]", 2.0 * m * n * k, 1e12, "TFLOP/s",
                   ms, ms_g, peaks["bf16_tflops"], peaks["note"], f"N columns / {world}", 1)
 
@@ -71,10 +75,11 @@ def gemm_fp8(dev, rank, world, peaks, m=8192, n=28672, k=8192):
     b8 = torch.randn(nl, k, generator=g, device=dev).to(torch.float8_e4m3fn)
     sa = torch.rand(m, k // 128, generator=g, device=dev) * 1e-3 + 1e-4
     sb = torch.rand(-(-nl // 128), k // 128, generator=g, device=dev) * 1e-3 + 1e-4
-    c = torch.empty(m, nl, dtype=torch.bfloat16, device=dev)
+    so = parallel.ShardedOutput((m, n), 1, torch.bfloat16, dev, multiple=128)
+    c = so.local
     ms = _time(lambda: ops.gemm_fp8_blockscale(a8, b8, sa, sb, c), world)
-    ms_g = _time(lambda: (ops.gemm_fp8_blockscale(a8, b8, sa, sb, c), parallel.all_gather_cat(c, 1)), world,
-                 reps=2, warmup=1) if world > 1 else ms
+    ms_g = _time(lambda: (ops.gemm_fp8_blockscale(a8, b8, sa, sb, c), so.gather()), world,
+                 reps=3, warmup=2) if world > 1 else ms
     return _entry("gemm_fp8_blockscale_kernel", f"e4m3 M{m} K{k} N{n}, fp32 scales per 1x128 (A) and 128x128 (B)",
                   2.0 * m * n * k, 1e12, "TFLOP/s", ms, ms_g, 2 * peaks["bf16_tflops"],
                   "2 x " + peaks["note"] + " (no FP8 peak was measured)", f"N columns / {world}", 1)
@@ -89,7 +94,8 @@ def mlp_gate_up(dev, rank, world, peaks, m=8192, n=14336, k=4096):
     x = torch.randn(m, k, generator=g, device=dev).bfloat16()
     wg = (torch.randn(nl, k, generator=g, device=dev) * k ** -0.5).bfloat16()
     wu = (torch.randn(nl, k, generator=g, device=dev) * k ** -0.5).bfloat16()
-    out = torch.empty(m, nl, dtype=torch.bfloat16, device=dev)
+    so = parallel.ShardedOutput((m, n), 1, torch.bfloat16, dev, multiple=128)
+    out = so.local
     gate, up = torch.empty_like(out), torch.empty_like(out)
     ms = _time(lambda: ops.mlp_gate_up(x, wg, wu, out), world)
 
@@ -99,7 +105,7 @@ def mlp_gate_up(dev, rank, world, peaks, m=8192, n=14336, k=4096):
         ops.swiglu(gate, up, out)
 
     ms_u = _time(unfused, world)
-    ms_g = _time(lambda: (ops.mlp_gate_up(x, wg, wu, out), parallel.all_gather_cat(out, 1)), world, reps=2, warmup=1) \
+    ms_g = _time(lambda: (ops.mlp_gate_up(x, wg, wu, out), so.gather()), world, reps=3, warmup=2) \
         if world > 1 else ms
     e = _entry("mlp_gate_up_tcgen05_kernel", f"bf16 M{m} K{k} N{n}: silu(x Wg^T) * (x Wu^T), weights [N,K]",
                4.0 * m * n * k, 1e12, "TFLOP/s", ms, ms_g, peaks["bf16_tflops"], peaks["note"], f"N columns / {world}", 1)
@@ -112,10 +118,11 @@ def flash_attn(dev, rank, world, peaks, b=4, s=4096, h=32, d=128):
     hl = hi - lo
     g = torch.Generator(device=dev).manual_seed(4)
     q, k, v = (torch.randn(b, s, hl, d, generator=g, device=dev).bfloat16() for _ in range(3))
-    o = torch.empty_like(q)
+    so = parallel.ShardedOutput((b, s, h, d), 2, torch.bfloat16, dev)
+    o = so.local
     ms = _time(lambda: ops.flash_attn_fwd(q, k, v, o, causal=True), world)
-    ms_g = _time(lambda: (ops.flash_attn_fwd(q, k, v, o, causal=True), parallel.all_gather_cat(o, 2)), world,
-                 reps=2, warmup=1) if world > 1 else ms
+    ms_g = _time(lambda: (ops.flash_attn_fwd(q, k, v, o, causal=True), so.gather()), world,
+                 reps=3, warmup=2) if world > 1 else ms
     return _entry("flash_attn_tcgen05_kernel", f"bf16 causal B{b} H{h} S{s} D{d} (bshd)", 4.0 * b * h * s * s * d * 0.5,
                   1e12, "TFLOP/s", ms, ms_g, peaks["bf16_tflops"], peaks["note"], f"heads / {world}", 1)
 
@@ -146,12 +153,14 @@ def mla_decode(dev, rank, world, peaks, batch=128, heads=128, d=576, dv=512, pag
         cache[p0:p1] = (x / sc).to(torch.float8_e4m3fn)
         scale[p0:p1] = sc.squeeze(-1)
     q = torch.randn(nb, heads, d, generator=g, device=dev).bfloat16()
-    out = torch.empty(nb, heads, dv, dtype=torch.bfloat16, device=dev)
+    lists = parallel.balance_by_length(lens_all.tolist(), world)
+    so = parallel.ShardedOutput((batch, heads, dv), 0, torch.bfloat16, dev, index_lists=lists)
+    out = so.local
+    ordered = torch.empty(batch, heads, dv, dtype=torch.bfloat16, device=dev)
     table, lens_d = table.to(dev), lens.to(dev)
     fn = lambda: ops.mla_decode_paged(q, cache, scale, table, lens_d, out, softmax_scale=d ** -0.5)   # noqa: E731
     ms = _time(fn, world)
-    lists = parallel.balance_by_length(lens_all.tolist(), world)
-    ms_g = _time(lambda: (fn(), parallel.all_gather_rows_by_index(out, lists)), world, reps=2, warmup=1) if world > 1 else ms
+    ms_g = _time(lambda: (fn(), so.gather(), so.assemble(ordered)), world, reps=3, warmup=2) if world > 1 else ms
     tokens = int(lens_all.sum())
     flops = 2.0 * tokens * heads * (d + dv)
     nbytes = tokens * (d + 4) + batch * heads * (d + dv) * 2

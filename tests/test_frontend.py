@@ -288,7 +288,7 @@ def generic_program(M=64, N=96, bm=32, bn=32, dtype="bfloat16"):
 
 
 def test_float32_program_forms_bind_to_the_fused_kernels():
-    assert bind(rms_norm_program_f32(64, 128, 32, eps=1e-6)).facts == dict(rows=64, cols=128, eps=1e-6, dtype="float32")
+    assert bind(rms_norm_program_f32(64, 128, 32, eps=1e-6)).facts == dict(rows=64, cols=128, eps=1e-6, dtype="float32", weight=False)
     assert bind(swiglu_program_f32(64, 128, 32, 64)).program == "swiglu"
 
 
@@ -422,3 +422,68 @@ def test_reference_mla_decode_program_binds():
     b = bind(build(4, 8, 1, 512, 32, 4, 4, 4))
     assert b.program == "mla_decode" and b.facts["pe_dim"] == 4 and b.facts["seqlen_kv"] == 512
     assert b.facts["scale"] == pytest.approx(36 ** -0.5)
+
+
+# ------------------------------------------------------------------ programs of the benchmark configurations
+def test_benchmark_programs_bind_to_the_fused_kernels():
+    from tilelang import programs as P
+    b = bind(P.rmsnorm(8192, 4096, eps=1e-6))
+    assert b.program == "rmsnorm" and b.facts["weight"] is True and b.facts["eps"] == pytest.approx(1e-6)
+    assert bind(P.rmsnorm(128, 128, weight=False)).facts["weight"] is False
+    b = bind(P.rope(8192, 32, 128))
+    assert b.program == "rope" and b.facts["shape"] == [8192, 32, 128] and b.facts["table"] == [8192, 128]
+    assert bind(P.swiglu(8192, 14336)).program == "swiglu"
+    assert bind(P.gemm_fp8_blockscale(256, 384, 512)).entry_point == "tl_b200_gemm_fp8_blockscale"
+    k = tilelang.compile(P.mla_decode_paged(4, 128, 576, 512, 40, 64, 11), out_idx=-1, target="b200")
+    assert [list(p.shape) for p in k.params][-1] == [4, 1, 128, 512] and k.adapter.result_idx == [5]
+    assert k.params[1].dtype == torch.float8_e4m3fn
+
+
+def test_weighted_rmsnorm_with_other_dataflow_is_not_bound_to_the_fused_kernel():
+    """Same op order as the weighted RMSNorm, but the weight multiplies the SQUARES: not RMSNorm."""
+    M, N, bm = 64, 128, 32
+
+    @T.prim_func
+    def not_rmsnorm(A: T.Tensor((M, N), "bfloat16"), W: T.Tensor((1, N), "bfloat16"), B: T.Tensor((M, N), "bfloat16")):
+        with T.Kernel(M // bm, is_cpu=True) as (bx,):
+            a16 = T.alloc_shared((bm, N), "bfloat16")
+            a32 = T.alloc_shared((bm, N), "float32")
+            sq = T.alloc_shared((bm, N), "float32")
+            acc = T.alloc_shared((bm, 1), "float32")
+            w16 = T.alloc_shared((1, N), "bfloat16")
+            w32 = T.alloc_shared((1, N), "float32")
+            T.ppl_copy(A[bx * bm, 0], a16)
+            T.ppl_copy(a16, a32)
+            T.ppl_mul(sq, a32, a32)
+            T.ppl_copy(W[0, 0], w16)
+            T.ppl_copy(w16, w32)
+            T.ppl_mul(sq, sq, w32)
+            T.ppl_reduce_sum(sq, acc, dim=1)
+            T.ppl_mul_C(acc, acc, T.float32(1.0 / N))
+            T.ppl_add_C(acc, acc, T.float32(1e-6))
+            T.ppl_rsqrt(acc, acc)
+            T.ppl_mul(a32, a32, acc)
+            T.ppl_copy(a32, a16)
+            T.ppl_copy(a16, B[bx * bm, 0])
+    assert bind(not_rmsnorm).program == "generic"
+
+
+def test_rope_program_with_mismatched_token_blocks_is_rejected():
+    tokens, heads, width, bt = 128, 4, 64, 32
+
+    @T.prim_func
+    def shifted(X: T.Tensor((tokens, heads, width), "bfloat16"), Cos: T.Tensor((tokens, width), "bfloat16"),
+                Sin: T.Tensor((tokens, width), "bfloat16"), Out: T.Tensor((tokens, heads, width), "bfloat16")):
+        with T.Kernel(tokens // bt, heads, is_cpu=True) as (bx, by):
+            x, c, s, xc, xs, nx, nxs, o = (T.alloc_shared((bt, width), "bfloat16") for _ in range(8))
+            T.ppl_copy(X[bx * bt:(bx + 1) * bt, by, 0:width], x)
+            T.ppl_copy(Cos[0, 0], c)                      # always the first token block: not the per-token table
+            T.ppl_copy(Sin[bx * bt, 0], s)
+            T.ppl_mul(xc, x, c)
+            T.ppl_mul(xs, x, s)
+            T.ppl_mul_C(nx, x, -1.0)
+            T.ppl_mul(nxs, nx, s)
+            T.ppl_rope_add(o, xc, nxs, xc, xs)
+            T.ppl_copy(o, Out[bx * bt:(bx + 1) * bt, by, 0:width])
+    with pytest.raises(UnsupportedProgram, match="same token block"):
+        bind(shifted)

@@ -127,3 +127,78 @@ def test_float32_program_forms(cuda_device):
     out = torch.zeros(64, 128)
     assert tilelang.compile(swiglu_program_f32(64, 128, 32, 64), out_idx=0, target="b200")(out, gate, up) == 0
     assert torch.allclose(out, O.swiglu(gate, up), atol=1e-5, rtol=1e-5)
+
+
+# ------------------------------------------------------------------ benchmark programs through the plug-in call
+def test_llama_programs_through_the_adapter_equal_the_operator_calls(cuda_device):
+    """The programs the end-to-end benchmark compiles (weighted RMSNorm, RoPE with per-token tables shared by
+    the heads, SwiGLU), called with pinned host tensors: same bits as `tilelang.ops` on device tensors."""
+    from tilelang import ops, programs as P, workloads
+    w = workloads.llama8b_memory_ops(tokens=256, seed=11)
+    dev = cuda_device
+    k_norm = tilelang.compile(P.rmsnorm(256, 4096, eps=w["eps"]), out_idx=-1, target="b200")
+    k_rq = tilelang.compile(P.rope(256, 32, 128), out_idx=-1, target="b200")
+    k_rk = tilelang.compile(P.rope(256, 8, 128), out_idx=-1, target="b200")
+    k_sw = tilelang.compile(P.swiglu(256, 14336), out_idx=-1, target="b200")
+    assert [k.adapter.bound.program for k in (k_norm, k_rq, k_rk, k_sw)] == ["rmsnorm", "rope", "rope", "swiglu"]
+    pin = lambda t: t.contiguous().pin_memory()                                       # noqa: E731
+    hy, hq, hk, hs = (pin(torch.full_like(w[n], float("nan"))) for n in ("x", "q", "k", "gate"))
+    for _ in range(3):                    # three calls in flight exercise both buffer sets of every adapter
+        assert k_norm(pin(w["x"]), pin(w["weight"].view(1, -1)), hy) == 0
+        assert k_rq(pin(w["q"]), pin(w["cos"]), pin(w["sin"]), hq) == 0
+        assert k_rk(pin(w["k"]), pin(w["cos"]), pin(w["sin"]), hk) == 0
+        assert k_sw(pin(w["gate"]), pin(w["up"]), hs) == 0
+    for k in (k_norm, k_rq, k_rk, k_sw):
+        k.adapter.synchronize()
+    d = {n: v.to(dev) for n, v in w.items() if isinstance(v, torch.Tensor)}
+    y, qo, ko, so = (torch.empty_like(d[n]) for n in ("x", "q", "k", "gate"))
+    ops.rmsnorm(d["x"], y, d["weight"], eps=w["eps"])
+    ops.rope(d["q"], d["cos"], d["sin"], qo)
+    ops.rope(d["k"], d["cos"], d["sin"], ko)
+    ops.swiglu(d["gate"], d["up"], so)
+    for host, devt in ((hy, y), (hq, qo), (hk, ko), (hs, so)):
+        assert torch.equal(host.view(torch.int16), devt.cpu().view(torch.int16))
+    assert torch.allclose(hy.float(), O.rmsnorm(w["x"], w["weight"], eps=w["eps"]).float(), atol=2e-2, rtol=2e-2)
+    assert torch.equal(hq.view(torch.int16), O.rope(w["q"], w["cos"], w["sin"]).view(torch.int16))
+
+
+def test_a_call_that_reads_what_an_earlier_call_still_writes_waits_for_it(cuda_device):
+    """Asynchronous (pinned) calls chained through a host tensor: the second program's upload of `mid` is ordered
+    after the first program's download into it, across two adapters."""
+    k1 = tilelang.compile(rms_norm_program(256, 512, 32, eps=1e-6), out_idx=-1, target="b200")
+    k2 = tilelang.compile(rms_norm_program(256, 512, 32, eps=1e-6), out_idx=-1, target="b200")
+    assert k1 is not k2
+    a = torch.randn(256, 512, generator=gen(12)).bfloat16().pin_memory()
+    mid = torch.zeros(256, 512, dtype=torch.bfloat16).pin_memory()
+    out = torch.zeros(256, 512, dtype=torch.bfloat16).pin_memory()
+    assert k1(a, mid) == 0 and k2(mid, out) == 0
+    k2.adapter.synchronize()
+    ref = O.rmsnorm(O.rmsnorm(a, eps=1e-6), eps=1e-6)
+    assert torch.allclose(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_library_programs_fp8_gemm_and_paged_mla(cuda_device):
+    """The two benchmark operators without a `ppl_*` form go through the same compile / call convention."""
+    from tilelang import ops, programs as P, workloads
+    dev = cuda_device
+    g = gen(13)
+    m, n, k = 256, 384, 512
+    a8, sa = O.per_token_cast_to_fp8(torch.randn(m, k, generator=g) * 0.05)
+    b8, sb = O.per_block_cast_to_fp8(torch.randn(n, k, generator=g) * 0.05)
+    c = torch.zeros(m, n, dtype=torch.bfloat16)
+    kern = tilelang.compile(P.gemm_fp8_blockscale(m, n, k), out_idx=-1, target="b200")
+    assert kern(a8, b8, sa, sb, c) == 0
+    cd = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+    ops.gemm_fp8_blockscale(a8.to(dev), b8.to(dev), sa.to(dev), sb.to(dev), cd)
+    assert torch.equal(c.view(torch.int16), cd.cpu().view(torch.int16))
+    assert torch.allclose(c.float(), O.gemm_fp8_blockscale(a8, b8, sa, sb).float(), atol=2e-2, rtol=2e-2)
+
+    cfg = workloads.mla_fp8_paged(batch=4, heads=128, min_len=100, max_len=700, seed=14)
+    pages, page = cfg["kv_cache"].shape[0], cfg["kv_cache"].shape[1]
+    prog = P.mla_decode_paged(4, 128, 576, 512, pages, page, cfg["block_table"].shape[1])
+    kern = tilelang.compile(prog, out_idx=-1, target="b200")
+    out = torch.zeros(4, 1, 128, 512, dtype=torch.bfloat16)
+    assert kern(cfg["q"], cfg["kv_cache"].view(pages, page, 1, 576), cfg["kv_scale"], cfg["block_table"],
+                cfg["cache_seqlens"], out) == 0
+    ref = O.mla_decode_paged(cfg["q"][:, 0], cfg["kv_cache"], cfg["kv_scale"], cfg["block_table"], cfg["cache_seqlens"], 512)
+    assert torch.allclose(out[:, 0].float(), ref.float(), atol=2e-2, rtol=2e-2)

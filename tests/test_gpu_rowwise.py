@@ -267,3 +267,26 @@ def test_swiglu_over_a_wide_gate_range(cuda_device, dtype):
     ref = O.swiglu(g, u).float()
     assert torch.allclose(out.cpu().float(), ref, atol=5e-3, rtol=1e-2)
     assert (out.cpu().float()[g.float() < -17.5] == 0).all()
+
+
+# ------------------------------------------------------------------ the generic void** entry point
+def test_generic_entry_point_runs_programs(cuda_device):
+    """`tl_b200_run(kernel_id, void** args, meta, stream)`: the pointer list in the shape of the reference's
+    generated `tilelang_tpu_run(void** args)`, sizes in `meta`; same bits as the typed entry points."""
+    from tilelang import _native as N
+    g = gen(77)
+    x = torch.randn(64, 512, generator=g).to(BF).to(cuda_device)
+    w = (1 + 0.02 * torch.randn(512, generator=g)).to(BF).to(cuda_device)
+    y_typed, y_run = torch.zeros_like(x), torch.zeros_like(x)
+    assert ops.rmsnorm(x, y_typed, w, eps=1e-6) == 0
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = N.run("rmsnorm", [x.data_ptr(), w.data_ptr(), y_run.data_ptr()], [64, 512, N.float_bits(1e-6), N.TL_BF16], stream)
+    assert rc == 0 and torch.equal(y_typed.view(torch.int16), y_run.view(torch.int16))
+    a = torch.randn(128, 64, generator=g).to(HF).to(cuda_device)
+    b = torch.randn(64, 96, generator=g).to(HF).to(cuda_device)
+    c_typed, c_run = (torch.zeros(128, 96, dtype=HF, device=cuda_device) for _ in range(2))
+    assert ops.gemm(a, b, c_typed) == 0
+    rc = N.run("gemm", [a.data_ptr(), b.data_ptr(), c_run.data_ptr()], [128, 96, 64, 0, N.TL_F16, N.TL_F16], stream)
+    assert rc == 0 and torch.equal(c_typed.view(torch.int16), c_run.view(torch.int16))
+    rc = N.run("swiglu", [0, 0, 0], [16, N.TL_BF16], stream)
+    assert rc == -1 and "null" in N.last_error()

@@ -54,3 +54,20 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setenv("TL_B200_LIB", str(tmp_path / "nope.so"))
     with pytest.raises(_native.NativeLibraryError):
         _native.load()
+
+
+def test_generic_entry_point_dispatches_and_validates_without_gpu():
+    """`tl_b200_run(kernel_id, void** args, meta, stream)` keeps the `void**` shape of the reference's
+    generated symbol; argument validation of the typed entry point behind it runs before any CUDA call."""
+    from tilelang import _native
+    import re as _re
+    header = (ROOT / "include" / "tl_b200.h").read_text()
+    ids = {m.group(1).lower(): int(m.group(2)) for m in _re.finditer(r"#define TL_B200_K_([A-Z0-9_]+) (\d+)", header)}
+    assert ids == _native.KERNEL_IDS
+    rc = _native.run("rmsnorm", [0, 0, 0], [4, 4, _native.float_bits(1e-6), _native.TL_BF16], None)
+    assert rc == -1 and "null" in _native.last_error()
+    rc = _native.run("rope", [0, 0, 0, 0], [4, 3, 1, _native.TL_BF16], None)
+    assert rc == -1 and "even" in _native.last_error()
+    lib = _native.load()
+    rc = lib.tl_b200_run(99, (ctypes.c_void_p * 1)(), (ctypes.c_int64 * 1)(), None)
+    assert rc == -1 and "unknown kernel id" in _native.last_error()

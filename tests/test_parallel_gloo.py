@@ -24,6 +24,7 @@ def _worker(rank, world, port, results):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         g = torch.Generator().manual_seed(0)                    # same data on every rank
+        q0, k0, v0 = (torch.randn(1, 16, 6, 8, generator=g).bfloat16() for _ in range(3))
         # rows: RMSNorm
         x = torch.randn(37, 64, generator=g).bfloat16()
         y = parallel.all_gather_cat(O.rmsnorm(parallel.shard(x, 0, world, rank), eps=1e-6), 0)
@@ -31,8 +32,25 @@ def _worker(rank, world, port, results):
         # columns: GEMM, B split by N in multiples of 16
         a = torch.randn(24, 32, generator=g).bfloat16()
         b = torch.randn(32, 80, generator=g).bfloat16()
-        c = parallel.all_gather_cat(O.matmul(a, parallel.shard(b, 1, world, rank, multiple=16)), 1)
+        c = parallel.all_gather_cat(O.matmul(a, parallel.shard(b, 1, world, rank, multiple=16)), 1, multiple=16, total=80)
         ok = ok and torch.equal(c.view(torch.int16), O.matmul(a, b).view(torch.int16))
+        # the hot-path form: the receive buffer is built once, the producer writes its block into
+        # `.local`, ONE all-gather, and the result is a view (rows) or a split view (heads)
+        so = parallel.ShardedOutput((64, 16), 0, torch.bfloat16, "cpu")
+        xs = torch.randn(64, 16, generator=g).bfloat16()
+        lo, hi = parallel.partition(64, world, rank)
+        so.local.copy_(O.rmsnorm(xs[lo:hi], eps=1e-6))
+        so.gather()
+        ok = ok and so.full_view() is not None and so.full_view().data_ptr() == so.recv.data_ptr()
+        ok = ok and torch.equal(so.full_view().view(torch.int16), O.rmsnorm(xs, eps=1e-6).view(torch.int16))
+        so_h = parallel.ShardedOutput((1, 16, 6, 8), 2, torch.bfloat16, "cpu")
+        lo, hi = parallel.partition(6, world, rank)
+        so_h.local.copy_(O.flash_attn_fwd(*(t[:, :, lo:hi].contiguous() for t in (q0, k0, v0)), causal=True))
+        so_h.gather()
+        ref_o = O.flash_attn_fwd(q0, k0, v0, causal=True)
+        ok = ok and so_h.full_view() is None
+        ok = ok and torch.allclose(so_h.split_view().reshape(1, 16, 6, 8).float(), ref_o.float(), atol=1e-2)
+        ok = ok and torch.allclose(so_h.assemble().float(), ref_o.float(), atol=1e-2)
         # heads: attention on bshd
         q, k, v = (torch.randn(1, 16, 6, 8, generator=g).bfloat16() for _ in range(3))
         o = parallel.all_gather_cat(O.flash_attn_fwd(*(parallel.shard(t, 2, world, rank) for t in (q, k, v)),

@@ -534,6 +534,7 @@ binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ 
     float bv;
     if constexpr (BMODE == 0) bv = to_f32(b[i]);
     else if constexpr (BMODE == 1) bv = to_f32(b[i / cols]);
+    else if constexpr (BMODE == 3) bv = to_f32(b[i % cols]);
     else bv = to_f32(from_f32<T>(scalar));  // scalar is first cast to the tile dtype
     float r;
     if constexpr (OP == 0) r = av + bv;
@@ -638,6 +639,7 @@ static int binary_mode(const void* a, const void* b, void* o, int64_t n, int64_t
     case 0: binary_kernel<T, OP, 0><<<grid, kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)o, n, cols, sc); break;
     case 1: binary_kernel<T, OP, 1><<<grid, kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)o, n, cols, sc); break;
     case 2: binary_kernel<T, OP, 2><<<grid, kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)o, n, cols, sc); break;
+    case 3: binary_kernel<T, OP, 3><<<grid, kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)o, n, cols, sc); break;
     default: return fail(TL_B200_EINVAL, "binary: unknown b_mode %d", b_mode);
   }
   TL_LAUNCH_CHECK("binary_kernel");

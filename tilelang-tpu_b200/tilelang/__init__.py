@@ -10,6 +10,7 @@ __version__ = "0.1.0"
 from . import _native  # noqa: F401
 from . import ops  # noqa: F401
 from . import language  # noqa: F401,E402
+from . import programs  # noqa: F401,E402
 from .engine import lower  # noqa: F401,E402
 from .jit import JITKernel, compile, jit  # noqa: F401,E402
 from .cache import cached, clear_cache  # noqa: F401,E402

@@ -50,7 +50,26 @@ PROTOTYPES = {
     "tl_b200_fill": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_float, c_int, c_void_p]),
     "tl_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
     "tl_b200_mlp_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "tl_b200_run": (c_int, [c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64), c_void_p]),
 }
+
+# kernel ids of tl_b200_run (values of the TL_B200_K_* macros)
+KERNEL_IDS = {name: i + 1 for i, name in enumerate(
+    ["rmsnorm", "rope", "swiglu", "reduce_rows", "unary", "binary", "rope_add", "copy2d", "fill", "gather_rows", "topk",
+     "gemm", "mlp_gate_up", "gemm_fp8_blockscale", "flash_attn_fwd", "mla_decode_dense", "mla_decode_paged"])}
+
+
+def float_bits(v: float) -> int:
+    """A float argument of tl_b200_run: its IEEE-754 single-precision bit pattern."""
+    import struct
+    return struct.unpack("<I", struct.pack("<f", float(v)))[0]
+
+
+def run(kernel: str, pointers, meta, stream) -> int:
+    """Call `tl_b200_run`: the pointer arguments and the non-pointer arguments of the typed entry point."""
+    args = (c_void_p * len(pointers))(*[c_void_p(p) for p in pointers])
+    m = (c_int64 * len(meta))(*[int(x) for x in meta])
+    return load().tl_b200_run(KERNEL_IDS[kernel], args, m, stream)
 
 
 class NativeLibraryError(RuntimeError):

@@ -73,8 +73,8 @@ def validate(func: PrimFunc) -> None:
         if op.name in _BINARY_OPS:
             out, x, y = op.args
             _need(out.shape == x.shape and out.dtype == x.dtype == y.dtype, f"{op.name}: out and in1 must agree in shape and dtype")
-            _need(y.shape == x.shape or (len(x.shape) == 2 and tuple(y.shape) == (x.shape[0], 1)),
-                  f"{op.name}: in2 must be shaped like in1 or (M, 1)")
+            _need(y.shape == x.shape or (len(x.shape) == 2 and tuple(y.shape) in ((x.shape[0], 1), (1, x.shape[1]))),
+                  f"{op.name}: in2 must be shaped like in1, (M, 1) or (1, N)")
         if op.name == "ppl.rope_add":
             _need(all(len(t.shape) == 2 and t.shape == op.args[0].shape and t.dtype == op.args[0].dtype for t in op.args)
                   and op.args[0].shape[1] % 2 == 0, "ppl.rope_add: five 2-D tiles of one shape and dtype, even width")

@@ -29,6 +29,7 @@ class BoundKernel:
     entry_point: str               # C-ABI symbol(s) it calls
     run: Callable[..., int]
     facts: dict
+    full_outputs: bool = True      # every element of every output is written (the adapter need not upload outputs)
 
     def describe(self) -> str:
         return f"{self.program} -> {self.entry_point} {self.facts}"
@@ -52,6 +53,21 @@ def _buf(x) -> Buffer:
 
 def _close(a: float, b: float, rel=1e-6) -> bool:
     return abs(a - b) <= rel * max(abs(a), abs(b), 1e-30)
+
+
+def _same_expr(a, b) -> bool:
+    """Two index expressions denote the same value (compared as affine forms over the block and loop variables)."""
+    ca, cb = const_value(a), const_value(b)
+    if ca is not None or cb is not None:
+        return ca is not None and cb is not None and ca == cb
+    fa, fb = a.affine(), b.affine()
+    if fa is None or fb is None:
+        return a is b
+    return fa[1] == fb[1] and {id(v): c for v, c in fa[0].items()} == {id(v): c for v, c in fb[0].items()}
+
+
+def _extents(r: Region):
+    return tuple(1 if e is None else int(e) for e in r.extents)
 
 
 def _require(cond, msg):
@@ -134,20 +150,72 @@ _RMS_SPLITK_F32 = ["ppl.fill", "loop.begin", "ppl.copy", "ppl.mul", "ppl.reduce_
                    "ppl.add_C", "ppl.rsqrt", "loop.begin", "ppl.copy", "ppl.mul", "ppl.copy", "loop.end"]
 
 
+def _strip_weight(func: PrimFunc):
+    """Splits off the per-column weight of the Llama form of RMSNorm, if the program has one:
+    a third parameter of shape (1, N) that is loaded into a (1, N) tile (cast to fp32 for 16-bit
+    tensors) and multiplied into the normalised tile with a row-broadcast `ppl_mul`.  The reference's
+    `ppl_mul` only broadcasts an (M, 1) column (src/target/codegen_ppl.cc:868-889); the (1, N) row is
+    an extension of this library for the benchmark's weighted RMSNorm.  Returns (ops without the
+    weight ops, weight buffer or None, the weight mul or None)."""
+    if len(func.params) != 3:
+        return list(func.ops), None, None
+    ops = list(func.ops)
+    w_tiles, drop, W = set(), set(), None
+    for i, o in enumerate(ops):
+        if o.name != "ppl.copy":
+            continue
+        src, dst = _buf(o.args[0]), _buf(o.args[1])
+        if _is_param(src, func) and len(src.shape) == 2 and src.shape[0] == 1 and dst.scope != "global" \
+                and tuple(dst.shape) == tuple(src.shape):
+            if W is not None and src is not W:
+                return list(func.ops), None, None
+            W = src
+            w_tiles.add(id(dst))
+            drop.add(i)
+        elif id(src) in w_tiles and dst.scope != "global" and tuple(dst.shape) == tuple(src.shape):
+            w_tiles.add(id(dst))                      # the cast copy of the weight tile
+            drop.add(i)
+    if W is None:
+        return list(func.ops), None, None
+    muls = [i for i, o in enumerate(ops) if o.name == "ppl.mul" and id(o.args[2]) in w_tiles]
+    if len(muls) != 1:
+        return list(func.ops), None, None
+    wmul = ops[muls[0]]
+    drop.add(muls[0])
+    return [o for i, o in enumerate(ops) if i not in drop], W, wmul
+
+
 def _match_rmsnorm(func: PrimFunc):
-    n = _names(func.ops)
-    if n not in (_RMS_BODY, _RMS_SPLITK, _RMS_BODY_F32, _RMS_SPLITK_F32) or len(func.params) != 2:
+    ops, W, wmul = _strip_weight(func)
+    n = _names(ops)
+    if n not in (_RMS_BODY, _RMS_SPLITK, _RMS_BODY_F32, _RMS_SPLITK_F32) or len(func.params) != (3 if W is not None else 2):
         return None
-    ops = func.ops
     split = n in (_RMS_SPLITK, _RMS_SPLITK_F32)
+    if split and W is not None:
+        return None
     copies = [o for o in ops if o.name == "ppl.copy"]
     load = next((o for o in copies if _is_param(o.args[0], func)), None)          # first load of the input
     store = next((o for o in reversed(copies) if _is_param(o.args[1], func)), None)
     if load is None or store is None:
         return None
+    muls = [o for o in ops if o.name == "ppl.mul"]
+    red = next(o for o in ops if o.name == "ppl.reduce_sum")
     mul_c = next(o for o in ops if o.name == "ppl.mul_C")
     add_c = next(o for o in ops if o.name == "ppl.add_C")
-    if not (_is_param(load.args[0], func) and _is_param(store.args[1], func)):
+    rsq = next(o for o in ops if o.name == "ppl.rsqrt")
+    sq, norm = muls[0], muls[-1]
+    # dataflow: x * x -> row sum -> * 1/N -> + eps -> rsqrt -> x * r (a program with the same op order
+    # but other operands is not RMSNorm and goes to the tile-op executor)
+    acc = rsq.args[0]
+    flow = (sq.args[1] is sq.args[2] and red.args[0] is sq.args[0]
+            and mul_c.args[0] is mul_c.args[1] and add_c.args[0] is add_c.args[1] and add_c.args[1] is mul_c.args[0]
+            and rsq.args[1] is add_c.args[0] and norm.args[2] is acc and tuple(acc.shape) == (sq.args[1].shape[0], 1))
+    if not split:
+        flow = flow and mul_c.args[1] is red.args[1] and norm.args[1] is sq.args[1] and norm.args[0] is sq.args[1]
+    if not flow:
+        return None
+    if wmul is not None and not (wmul.args[0] is norm.args[0] and wmul.args[1] is norm.args[0]
+                                 and func.ops.index(wmul) > func.ops.index(norm)):
         return None
     X, Y = _buf(load.args[0]), _buf(store.args[1])
     _require(len(X.shape) == 2 and X.shape == Y.shape and X.dtype == Y.dtype, "rmsnorm: A and B must be equal 2-D")
@@ -156,15 +224,18 @@ def _match_rmsnorm(func: PrimFunc):
     tile = _buf(load.args[1])
     _check_tiling(func, "rmsnorm", [(M, tile.shape[0]), (N, tile.shape[1])])
     _require(split or tile.shape[1] == N, "rmsnorm: the row tile must span N")
+    if W is not None:
+        _require(tuple(W.shape) == (1, N) and W.dtype == X.dtype, "rmsnorm: the weight must be a (1, N) row of the input dtype")
     eps = float(add_c.args[2])
     ix, iy = X.param_index, Y.param_index
+    iw = W.param_index if W is not None else None
     from .. import ops as native
 
     def run(*t):
-        return native.rmsnorm(t[ix], t[iy], None, eps)
+        return native.rmsnorm(t[ix], t[iy], None if iw is None else t[iw].view(-1), eps)
 
     return BoundKernel("rmsnorm_splitk" if split else "rmsnorm", "tl_b200_rmsnorm", run,
-                       dict(rows=M, cols=N, eps=eps, dtype=X.dtype))
+                       dict(rows=M, cols=N, eps=eps, dtype=X.dtype, weight=W is not None))
 
 
 _ROPE = ["ppl.copy", "ppl.copy", "ppl.copy", "ppl.mul", "ppl.mul", "ppl.mul_C", "ppl.mul", "ppl.rope_add", "ppl.copy"]
@@ -185,18 +256,35 @@ def _match_rope(func: PrimFunc):
     if not ok:
         return None
     X, Cs, Sn, Out = _buf(ld_x.args[0]), _buf(ld_c.args[0]), _buf(ld_s.args[0]), _buf(store.args[1])
-    _require(X.shape == Cs.shape == Sn.shape == Out.shape and len(X.shape) == 2, "rope: x/cos/sin/out must be "
-             "equal 2-D tensors")
     _require(X.dtype == Cs.dtype == Sn.dtype == Out.dtype, "rope: one dtype for x/cos/sin/out")
-    _check_tiling(func, "rope", [(X.shape[0], x_t.shape[0]), (X.shape[1], x_t.shape[1])])
     _require(x_t.shape[1] % 2 == 0, "rope: tile width must be even")
+    if len(X.shape) == 3:
+        # x and out are (tokens, heads, W); cos/sin are (tokens, W) tables shared by the heads of a
+        # token: a block loads rows [t0, t0 + bt) of ONE head and the same rows of the tables
+        T_, H_, W_ = X.shape
+        _require(Out.shape == X.shape and tuple(Cs.shape) == (T_, W_) and Sn.shape == Cs.shape,
+                 "rope: x/out (tokens, heads, W) need cos/sin tables of shape (tokens, W)")
+        xr, cr, sr, orr = ld_x.args[0], ld_c.args[0], ld_s.args[0], store.args[1]
+        bt = x_t.shape[0]
+        _require(_extents(xr) == (bt, 1, W_) and _extents(orr) == (bt, 1, W_) and _extents(cr) == (bt, W_)
+                 and _extents(sr) == (bt, W_) and tuple(x_t.shape) == (bt, W_),
+                 "rope: a block must cover bt tokens of one head and the full width")
+        _require(_same_expr(xr.starts[0], cr.starts[0]) and _same_expr(xr.starts[0], sr.starts[0])
+                 and _same_expr(xr.starts[0], orr.starts[0]) and _same_expr(xr.starts[1], orr.starts[1]),
+                 "rope: x, cos, sin and out must be addressed by the same token block (and x, out by the same head)")
+        _check_tiling(func, "rope", [(T_, bt)])
+        _require(sorted(_grid(func)) == sorted([T_ // bt, H_]), "rope: the grid must cover tokens x heads")
+    else:
+        _require(X.shape == Cs.shape == Sn.shape == Out.shape and len(X.shape) == 2, "rope: x/cos/sin/out must be "
+                 "equal 2-D tensors")
+        _check_tiling(func, "rope", [(X.shape[0], x_t.shape[0]), (X.shape[1], x_t.shape[1])])
     idx = [b.param_index for b in (X, Cs, Sn, Out)]
     from .. import ops as native
 
     def run(*t):
         return native.rope(t[idx[0]], t[idx[1]], t[idx[2]], t[idx[3]])
 
-    return BoundKernel("rope", "tl_b200_rope", run, dict(rows=X.shape[0], width=X.shape[1], dtype=X.dtype))
+    return BoundKernel("rope", "tl_b200_rope", run, dict(shape=list(X.shape), table=list(Cs.shape), dtype=X.dtype))
 
 
 _SWIGLU = ["ppl.fill", "ppl.copy", "ppl.copy", "ppl.copy", "ppl.copy", "ppl.mul_C", "ppl.exp", "ppl.add", "ppl.div",
@@ -332,7 +420,8 @@ def _match_topk(func: PrimFunc):
     def run(*t):
         return native.topk(t[i_s], t[i_d], t[i_i], k, bool(desc))
 
-    return BoundKernel("topk", "tl_b200_topk", run, dict(length=length, K=k, descended=bool(desc), dtype=src.dtype))
+    return BoundKernel("topk", "tl_b200_topk", run, dict(length=length, K=k, descended=bool(desc), dtype=src.dtype),
+                       full_outputs=False)       # only the first K entries of the two outputs are written
 
 
 def _match_gather(func: PrimFunc):
@@ -467,7 +556,29 @@ def _match_mla_decode(func: PrimFunc):
                        dict(batch=b, heads=h, seqlen_kv=s, dim=dim, pe_dim=pe, scale=scale, dtype=Q.dtype))
 
 
-_MATCHERS = [_match_matmul, _match_rmsnorm, _match_rope, _match_swiglu, _match_mlp, _match_reduce, _match_topk, _match_gather,
+def _match_library_program(func: PrimFunc):
+    """Programs of `tilelang.programs` that name the library kernel implementing them."""
+    kernel = func.attrs.get("library_kernel")
+    if kernel is None:
+        return None
+    facts = dict(func.attrs.get("facts", {}))
+    from .. import ops as native
+    if kernel == "gemm_fp8_blockscale":
+        return BoundKernel("gemm_fp8_blockscale", "tl_b200_gemm_fp8_blockscale",
+                           lambda a8, b8, sa, sb, c: native.gemm_fp8_blockscale(a8, b8, sa, sb, c), facts)
+    if kernel == "mla_decode_paged":
+        scale, dv = facts["softmax_scale"], facts["dv"]
+        if facts["scaled"]:
+            def run(q, kv, kvs, table, lens, out):
+                return native.mla_decode_paged(q, kv, kvs, table, lens, out, dv=dv, softmax_scale=scale)
+        else:
+            def run(q, kv, table, lens, out):
+                return native.mla_decode_paged(q, kv, None, table, lens, out, dv=dv, softmax_scale=scale)
+        return BoundKernel("mla_decode_paged", "tl_b200_mla_decode_paged", run, facts)
+    raise UnsupportedProgram(f"unknown library kernel {kernel!r}")
+
+
+_MATCHERS = [_match_library_program, _match_matmul, _match_rmsnorm, _match_rope, _match_swiglu, _match_mlp, _match_reduce, _match_topk, _match_gather,
              _match_elementwise, _match_flash_attention, _match_mla_decode]
 
 
@@ -485,7 +596,7 @@ def bind(func: PrimFunc) -> BoundKernel:
         reason = str(why)
     else:
         return BoundKernel("generic", "tile-op executor (one tl_b200_* launch per op)", run,
-                           dict(ops=len(func.ops), grid=[int(const_value(g)) for g in func.grid]))
+                           dict(ops=len(func.ops), grid=[int(const_value(g)) for g in func.grid]), full_outputs=False)
     raise UnsupportedProgram(
         f"the generic tile-op executor cannot run it either ({reason}); "
         "this ppl_* program does not match any kernel of the b200 library (matmul, rmsnorm, "

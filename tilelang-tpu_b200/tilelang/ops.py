@@ -123,7 +123,7 @@ def unary(x: torch.Tensor, y: torch.Tensor, op: str) -> int:
 
 
 def binary(a: torch.Tensor, b, out: torch.Tensor, op: str) -> int:
-    """out = a (op) b; b is a tensor shaped like a, a (rows, 1) column, or a Python scalar."""
+    """out = a (op) b; b is a tensor shaped like a, a (rows, 1) column, a (1, cols) row, or a Python scalar."""
     if a.dim() != 2 or out.shape != a.shape or out.dtype != a.dtype:
         raise ValueError("binary: a and out must be 2-D with equal shape and dtype")
     rows, cols = a.shape
@@ -133,10 +133,12 @@ def binary(a: torch.Tensor, b, out: torch.Tensor, op: str) -> int:
             raise ValueError("binary: dtype mismatch")
         if b.shape == a.shape:
             mode = 0
-        elif b.numel() == rows:
+        elif b.numel() == rows and (b.dim() < 2 or b.shape[-1] == 1 or cols == 1):
             mode = 1
+        elif b.numel() == cols and b.dim() == 2 and b.shape[0] == 1:
+            mode = 3
         else:
-            raise ValueError("binary: b must match a or be a (rows, 1) column")
+            raise ValueError("binary: b must match a, be a (rows, 1) column or a (1, cols) row")
         s = _prepare(a, b, out)
         bp = _ptr(b)
     else:
@@ -334,11 +336,15 @@ _workspaces: dict = {}
 
 
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
-    """Scratch owned by this module, one growing buffer per device (the library never allocates)."""
-    buf = _workspaces.get(device)
+    """Scratch owned by this module (the library never allocates): one growing buffer per
+    (device, stream).  Calls on different streams may overlap on the GPU and must not share the
+    partial results kept there; on one stream they are ordered, and a buffer that is replaced by a
+    larger one goes back to torch's allocator, which reuses it only in stream order."""
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes:
         buf = torch.empty(max(nbytes, 4096), dtype=torch.uint8, device=device)
-        _workspaces[device] = buf
+        _workspaces[key] = buf
     return buf
 
 
