@@ -212,17 +212,19 @@ def topk(src: torch.Tensor, k: int, descending: bool = True):
 
 # ---------------------------------------------------------------------------- attention
 def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: bool,
-                   head_chunk: int = 4) -> torch.Tensor:
+                   head_chunk: int = 4, q_offset: int = 0) -> torch.Tensor:
     """softmax(Q K^T / sqrt(d) [+ tril mask]) V on bshd tensors, fp32, cast to q.dtype.
 
     Follows `ref_program` of tpu_demo/flashattn/tpu_test_flashattn_bf16.py:171-182 (identical to
     examples/flash_attention/example_mha_fwd_bshd.py:173-184); evaluated a few heads at a time
-    so the score matrix of long sequences stays small.
+    so the score matrix of long sequences stays small.  `q_offset` lets a test check a block of query
+    rows of a long sequence: row i of `q` then stands at position q_offset + i of the sequence (the
+    mask of the full problem restricted to those rows; 0 is the reference function itself).
     """
     b, sq, h, d = q.shape
     sk = k.shape[1]
     out = torch.empty(b, sq, h, d, dtype=q.dtype)
-    mask = torch.tril(torch.ones(sq, sk)) == 0 if causal else None
+    mask = torch.tril(torch.ones(sq, sk), diagonal=q_offset) == 0 if causal else None
     for h0 in range(0, h, head_chunk):
         hs = slice(h0, min(h, h0 + head_chunk))
         scores = torch.einsum("bqhd,bkhd->bhqk", q[:, :, hs].float(), k[:, :, hs].float())

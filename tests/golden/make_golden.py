@@ -23,10 +23,12 @@ import torch
 import torch.nn.functional as F
 
 import os
-if len(sys.argv) < 2 and "TILELANG_TPU_REFERENCE" not in os.environ:
+_args = [a for a in sys.argv[1:] if not a.startswith("--")]
+if not _args and "TILELANG_TPU_REFERENCE" not in os.environ:
     raise SystemExit("usage: make_golden.py /path/to/reference   (or set TILELANG_TPU_REFERENCE)")
-REF = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["TILELANG_TPU_REFERENCE"])
-OUT = Path(__file__).resolve().parent
+REF = Path(_args[0] if _args else os.environ["TILELANG_TPU_REFERENCE"])
+OUT_OVERRIDE = os.environ.get("TILELANG_TPU_GOLDEN_OUT")
+OUT = Path(OUT_OVERRIDE) if OUT_OVERRIDE else Path(__file__).resolve().parent
 
 
 def lift(path: str, funcs=(), assigns=(), env=None):
@@ -179,7 +181,31 @@ def main():
     a8, sa = env["per_token_cast_to_fp8"](xa)
     b8, sb = env["per_block_cast_to_fp8"](xb)
     save("fp8_quant", xa=xa, xb=xb, a8=a8, sa=sa, b8=b8, sb=sb)
+    fp8_gemm_reference(env)
+
+
+def fp8_gemm_reference(env=None):
+    """`ref_deepgemm_fp8` (example_deepgemm_fp8_2xAcc.py:115-139) calls torch._scaled_mm with row-wise
+    scales on "cuda", which torch's CPU backend does not implement: this fixture is written only when
+    the script runs on a machine with a CUDA device (`--only-fp8-gemm` skips everything else)."""
+    if not torch.cuda.is_available():
+        print("fp8_gemm_ref.npz not refreshed: ref_deepgemm_fp8 needs torch._scaled_mm on a CUDA device")
+        return
+    env = lift("examples/deepseek_deepgemm/example_deepgemm_fp8_2xAcc.py",
+               funcs=("ceildiv", "per_token_cast_to_fp8", "per_block_cast_to_fp8", "ref_deepgemm_fp8"))
+    g = gen(113)
+    m, n, k = 256, 384, 1024
+    xa = (torch.randn(m, k, generator=g) * 0.05).cuda()
+    xb = (torch.randn(n, k, generator=g) * 0.05).cuda()
+    a8, sa = env["per_token_cast_to_fp8"](xa)
+    b8, sb = env["per_block_cast_to_fp8"](xb)
+    ref = env["ref_deepgemm_fp8"](a8, b8, sa, sb, torch.bfloat16)
+    save("fp8_gemm_ref", a8=a8.cpu(), sa=sa.cpu(), b8=b8.cpu(), sb=sb.cpu(), ref=ref.cpu())
 
 
 if __name__ == "__main__":
-    main()
+    if "--only-fp8-gemm" in sys.argv:
+        sys.argv.remove("--only-fp8-gemm")
+        fp8_gemm_reference()
+    else:
+        main()

@@ -115,9 +115,17 @@ def test_benchmark_config_properties(cuda_device):
     vmax = v.float().cummax(dim=1).values
     vmin = v.float().cummin(dim=1).values
     assert (out.float() <= vmax + 2e-2).all() and (out.float() >= vmin - 2e-2).all()
-    hs = slice(5, 7)
-    ref = O.flash_attn_fwd(q[:1, :, hs], k[:1, :, hs], v[:1, :, hs], causal=True, head_chunk=1)
-    assert torch.allclose(out[:1, :, hs].float(), ref.float(), **TOL16)
+    # the oracle on one whole head of every batch entry ...
+    for bi, hi in enumerate((5, 0, 31, 18)):
+        sel = (slice(bi, bi + 1), slice(None), slice(hi, hi + 1))
+        ref = O.flash_attn_fwd(q[sel], k[sel], v[sel], causal=True, head_chunk=1)
+        assert torch.allclose(out[sel].float(), ref.float(), **TOL16), (bi, hi)
+    # ... and on the first and the last 256 query rows of EVERY (batch, head): the shortest and the
+    # longest rows of work of each one (first CTA scheduled last, last CTA scheduled first)
+    ref = O.flash_attn_fwd(q[:, :256], k[:, :256], v[:, :256], causal=True)
+    assert torch.allclose(out[:, :256].float(), ref.float(), **TOL16)
+    ref = O.flash_attn_fwd(q[:, s - 256:], k, v, causal=True, q_offset=s - 256)
+    assert torch.allclose(out[:, s - 256:].float(), ref.float(), **TOL16)
 
 
 def test_run_to_run_determinism(cuda_device):

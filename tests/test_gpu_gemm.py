@@ -52,6 +52,7 @@ def test_gemm_tensor_core_shapes(cuda_device, dtype, transpose_b, m, n, k):
     b = (torch.randn(n, k, generator=g) if transpose_b else torch.randn(k, n, generator=g)).to(dtype)
     ref32 = O.matmul(a, b, F32, transpose_b)
     c = run(a, b, dtype, transpose_b, cuda_device)
+    assert torch.allclose(c.float(), ref32.to(dtype).float(), **TOL16)          # the stated tolerance
     check(c, ref32, k ** 0.5)
     # identity structure: exact integers survive fp32 accumulation bit-exactly
     c32 = run(a, b, F32, transpose_b, cuda_device)
@@ -92,8 +93,26 @@ def test_gemm_anchor_config(cuda_device):
     b = torch.randn(1024, 1024, generator=g).half()
     ref = O.matmul(a, b)
     c = run(a, b, HF, False, cuda_device)
+    assert torch.allclose(c.float(), ref.float(), **TOL16)                       # the stated tolerance: atol = rtol = 2e-2
     check(c, ref.float(), 32.0)
-    assert torch.allclose(c.float(), ref.float(), atol=2e-2 * 32, rtol=2e-2)
+
+
+def test_gemm_llama70b_ffn_config(cuda_device):
+    """bf16 M8192 K8192 N28672, A and B = 0.05 N(0,1) from seed 2: the oracle on 64 rows spread over every
+    128-row tile band, all 28672 columns (so every column shard of every sharding), at the stated tolerance."""
+    g = gen(2)
+    m, k, n = 8192, 8192, 28672
+    a = (torch.randn(m, k, generator=g) * 0.05).to(BF)
+    b = (torch.randn(k, n, generator=g) * 0.05).to(BF)
+    c = torch.full((m, n), float("nan"), dtype=BF, device=cuda_device)
+    assert ops.gemm(a.to(cuda_device), b.to(cuda_device), c) == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    rows = torch.arange(64) * 128 + torch.randint(0, 128, (64,), generator=g)      # one row in each of the 64 row tiles
+    ref = O.matmul(a[rows], b, BF)
+    got = c[rows.to(cuda_device)].cpu()
+    assert torch.allclose(got.float(), ref.float(), **TOL16)
+    assert torch.isfinite(c.float()).all()
 
 
 def test_gemm_linearity_at_large_size(cuda_device):

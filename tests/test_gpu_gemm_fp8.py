@@ -85,3 +85,45 @@ def test_argument_errors(cuda_device):
         ops.gemm_fp8_blockscale(a8.to(cuda_device)[:, :64].contiguous(), b8.to(cuda_device)[:, :64].contiguous(),
                                 sa.to(cuda_device), sb.to(cuda_device),
                                 torch.zeros(128, 128, dtype=torch.bfloat16, device=cuda_device))
+
+
+def calc_diff(x, y):
+    """1 - cosine-style similarity: the measure the block-scaled GEMM example asserts on
+    (examples/deepseek_deepgemm/example_deepgemm_fp8_2xAcc.py:142-146, `diff < 1e-3`)."""
+    x, y = x.double(), y.double()
+    return float(1 - 2 * (x * y).sum() / (x * x + y * y).sum())
+
+
+def test_against_the_reference_functions_own_result(cuda_device):
+    """tests/golden/fp8_gemm_ref.npz holds the output of the reference's `ref_deepgemm_fp8` (:115-139, per-block
+    torch._scaled_mm on a CUDA device, every 128-wide partial rounded to bf16 before the fp32 sum) on operands cut
+    by its own quantisers: oracle and kernel must meet it within the example's own criterion."""
+    from conftest import GOLDEN
+    if not (GOLDEN / "fp8_gemm_ref.npz").exists():
+        pytest.skip("fixture not generated (needs a CUDA device and the reference tree)")
+    g = load_golden("fp8_gemm_ref", dict(a8=F8, b8=F8, ref=torch.bfloat16))
+    out = run(g["a8"], g["b8"], g["sa"].contiguous(), g["sb"].contiguous(), torch.bfloat16, cuda_device)
+    assert calc_diff(out, g["ref"]) < 1e-3
+    assert torch.allclose(out.float(), g["ref"].float(), atol=2e-2, rtol=2e-2)
+
+
+def test_llama70b_ffn_config(cuda_device):
+    """e4m3 M8192 K8192 N28672 (0.05 N(0,1), seed 2) cut by the example's quantisers: the oracle on 64 rows
+    spread over every 128-row tile band and all columns, at the stated tolerance."""
+    g = gen(2)
+    m, k, n = 8192, 8192, 28672
+    a8, sa = O.per_token_cast_to_fp8(torch.randn(m, k, generator=g) * 0.05)
+    b = torch.randn(k, n, generator=g) * 0.05                    # drawn as [K, N] like the bf16 configuration
+    b8, sb = O.per_block_cast_to_fp8(b.t().contiguous())
+    del b
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    assert ops.gemm_fp8_blockscale(a8.to(cuda_device), b8.to(cuda_device), sa.contiguous().to(cuda_device),
+                                   sb.contiguous().to(cuda_device), out) == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    rows = torch.arange(64) * 128 + torch.randint(0, 128, (64,), generator=g)
+    ref = O.gemm_fp8_blockscale(a8[rows], b8, sa[rows], sb, torch.float32)
+    got = out[rows.to(cuda_device)].cpu().float()
+    assert torch.allclose(got, ref, atol=2e-2, rtol=2e-2)
+    assert calc_diff(got, ref) < 1e-3
+    assert torch.isfinite(out.float()).all()
