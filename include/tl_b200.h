@@ -43,6 +43,7 @@ extern "C" {
 #define TL_E4M3 3
 #define TL_I32 4
 #define TL_U32 5
+#define TL_I16 6   /* integer row sums only */
 
 /* ---- library management ---------------------------------------------------
  * Replaces init()/post() of the generated host (main_template.cpp:14-37).    */
@@ -56,6 +57,12 @@ int64_t tl_b200_launch_count(void);
  * Meaningful after the stream has been synchronised.  (The generated TPU host reports launch
  * failures through its return value, main_template.cpp:64-67.)                               */
 int tl_b200_device_status(void);
+/* Self-test of that path: launches one warp that waits, with the library's bounded wait and a budget
+ * of budget_us microseconds (1 .. 100000), on a barrier nothing arrives at.  The wait expires, the
+ * kernel writes the status word and returns; after a stream synchronise tl_b200_device_status()
+ * reports it and the context stays usable.  (No counterpart in the reference, whose launches block
+ * inside the vendor runtime.)                                                                    */
+int tl_b200_selftest_bounded_wait(int64_t budget_us, void* stream);
 
 /* ---- RMSNorm program ------------------------------------------------------
  * y[r,:] = x[r,:] * rsqrt(mean(x[r,:]^2) + eps) (* weight[:] if weight != NULL),
@@ -85,7 +92,8 @@ int tl_b200_swiglu(const void* gate, const void* up, void* out, int64_t n_elems,
  * y[r] = sum or max over x[r, 0:cols];  op 0 = sum (ppl_reduce_sum,
  * codegen_ppl.cc:1554-1792), op 1 = max (ppl_reduce_max, :1352-1553).
  * Accumulation in fp32; output in `dtype`.  Programs: tpu_demo/tpu_test_reduce_sum.py,
- * tpu_demo/tpu_test_reduce_max.py.                                                 */
+ * tpu_demo/tpu_test_reduce_max.py.  The sum also takes TL_I32 / TL_U32 / TL_I16 tiles
+ * (codegen_ppl.cc:1570-1592): exact sums modulo 2^32, TL_I16 cut to 16 bits.         */
 int tl_b200_reduce_rows(const void* x, void* y, int64_t rows, int64_t cols, int op, int dtype,
                         void* stream);
 
@@ -145,7 +153,9 @@ int tl_b200_topk(const void* src, void* out_vals, int32_t* out_idx, int64_t rows
  * (`transpose_B=True` of ppl_gemm, customize.py:101-133, codegen_ppl.cc:1244-1279).
  * in_dtype TL_F16 / TL_BF16 run on tcgen05 tensor cores when A, B are 16-byte aligned,
  * k % 8 == 0 and (trans_b or n % 8 == 0); other shapes and TL_F32 use an FMA kernel.
- * out_dtype is in_dtype or TL_F32.                                                   */
+ * out_dtype is in_dtype or TL_F32.  in_dtype TL_E4M3 is the plain (un-scaled) FP8 operand form
+ * of ppl_gemm (codegen_ppl.cc:775-790): tensor cores only (16-byte aligned tensors, k % 16 == 0,
+ * trans_b or n % 16 == 0), out_dtype TL_F32, TL_BF16 or TL_F16.                        */
 int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
                  int in_dtype, int out_dtype, void* stream);
 

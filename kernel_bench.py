@@ -67,6 +67,22 @@ def gemm_bf16(dev, rank, world, peaks, m=8192, n=28672, k=8192):
                   ms, ms_g, peaks["bf16_tflops"], peaks["note"], f"N columns / {world}", 1)
 
 
+def gemm_fp8_plain(dev, rank, world, peaks, m=8192, n=28672, k=8192):
+    """Un-scaled e4m3 GEMM (the FP8 operand form of ppl_gemm) at the C4 shape: what the FP8 tensor path of this
+    library delivers without the per-128-K promotion; the block-scaled entry is read against it."""
+    lo, hi = parallel.partition(n, world, rank, 256)
+    g = torch.Generator(device=dev).manual_seed(2)
+    a8 = torch.randn(m, k, generator=g, device=dev).to(torch.float8_e4m3fn)
+    b8 = torch.randn(hi - lo, k, generator=g, device=dev).to(torch.float8_e4m3fn)
+    so = parallel.ShardedOutput((m, n), 1, torch.bfloat16, dev, multiple=256)
+    c = so.local
+    ms = _time(lambda: ops.gemm(a8, b8, c, True), world)
+    ms_g = _time(lambda: (ops.gemm(a8, b8, c, True), so.gather()), world, reps=3, warmup=2) if world > 1 else ms
+    return _entry("gemm_tcgen05_kernel (e4m3 operands)", f"e4m3 M{m} K{k} N{n}, B [N,K], no scales, bf16 out", 2.0 * m * n * k,
+                  1e12, "TFLOP/s", ms, ms_g, 2 * peaks["bf16_tflops"], "2 x " + peaks["note"] + " (no FP8 peak was measured)",
+                  f"N columns / {world}", 1)
+
+
 def gemm_fp8(dev, rank, world, peaks, m=8192, n=28672, k=8192):
     lo, hi = parallel.partition(n, world, rank, 128)
     nl = hi - lo
@@ -211,9 +227,14 @@ def small_ops(dev, rank, world, peaks, rows=8192, cols=4096):
 
 def run_all(dev, rank, world, peaks):
     out = []
-    for fn in (gemm_bf16, gemm_fp8, mlp_gate_up, flash_attn, mla_decode):
+    plain_fp8 = None
+    for fn in (gemm_bf16, gemm_fp8_plain, gemm_fp8, mlp_gate_up, flash_attn, mla_decode):
         try:
             e = fn(dev, rank, world, peaks)
+            if fn is gemm_fp8_plain:
+                plain_fp8 = e["value"]
+            if fn is gemm_fp8 and plain_fp8:
+                e["frac_of_plain_e4m3_gemm"] = e["value"] / plain_fp8
             if world > 1 and e.get("peak"):       # `value` is the whole job: compare with the peak of all GPUs
                 e["peak"] *= world
                 e["frac_of_peak"] = e["value"] / e["peak"]
@@ -231,6 +252,7 @@ def run_all(dev, rank, world, peaks):
 SMALL = {      # reduced shapes for profiler captures: inputs above the 126 MB L2, a few hundred MB on the device
     "gemm_bf16": dict(m=4096, n=8192, k=4096),
     "gemm_fp8": dict(m=4096, n=8192, k=4096),
+    "gemm_fp8_plain": dict(m=4096, n=8192, k=4096),
     "mlp_gate_up": dict(m=4096, n=4096, k=4096),
     "flash_attn": dict(b=2, s=4096, h=16, d=128),
     "mla_decode": dict(batch=32),

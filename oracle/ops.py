@@ -172,7 +172,16 @@ def mlp(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch
 
 # ---------------------------------------------------------------------------- reductions / elementwise
 def reduce_sum(x: torch.Tensor) -> torch.Tensor:
-    """tpu_demo/tpu_test_reduce_sum.py:36 — row sum, keepdim; fp32 accumulate, cast back."""
+    """tpu_demo/tpu_test_reduce_sum.py:36 — row sum, keepdim; fp32 accumulate, cast back.  Integer tiles
+    (int32 / uint32 / int16, accepted by the code generator at src/target/codegen_ppl.cc:1570-1592): the exact
+    sum cut to the tile's width (two's complement wrap-around)."""
+    if x.dtype in (torch.int32, torch.uint32, torch.int16):
+        signed = x.view(torch.int32) if x.dtype == torch.uint32 else x
+        total = signed.to(torch.int64).sum(dim=1, keepdim=True)
+        if x.dtype == torch.int16:
+            return ((total + 2 ** 15) % 2 ** 16 - 2 ** 15).to(torch.int16)
+        wrapped = ((total + 2 ** 31) % 2 ** 32 - 2 ** 31).to(torch.int32)
+        return wrapped.view(torch.uint32) if x.dtype == torch.uint32 else wrapped
     return x.float().sum(dim=1, keepdim=True).to(x.dtype)
 
 

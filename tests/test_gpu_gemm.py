@@ -143,3 +143,24 @@ def test_gemm_argument_errors(cuda_device):
         ops.gemm(a, torch.zeros(8, 8, dtype=BF, device=cuda_device), torch.zeros(8, 8, dtype=BF, device=cuda_device))
     with pytest.raises(ValueError):
         ops.gemm(a, torch.zeros(16, 8, dtype=HF, device=cuda_device), torch.zeros(8, 8, dtype=BF, device=cuda_device))
+
+
+@pytest.mark.parametrize("transpose_b", [False, True])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 512, 384), (200, 144, 80), (1, 16, 16), (1024, 1024, 1024),
+                                   (384, 1296, 528)])
+def test_gemm_e4m3_operands(cuda_device, transpose_b, m, n, k):
+    """The plain FP8 operand form of ppl_gemm (src/target/codegen_ppl.cc:775-790): e4m3 A and B, fp32 accumulate.
+    Products of e4m3 values are exact in fp32, so only the summation order separates kernel and oracle."""
+    F8 = torch.float8_e4m3fn
+    g = gen(m + 5 * n + 11 * k)
+    a = torch.randn(m, k, generator=g).to(F8)
+    b = (torch.randn(n, k, generator=g) if transpose_b else torch.randn(k, n, generator=g)).to(F8)
+    ref = O.matmul(a.float(), b.float(), F32, transpose_b)
+    c = run(a, b, F32, transpose_b, cuda_device)
+    assert ((c.double() - ref.double()).abs() <= 1e-4 * k ** 0.5 + 1e-5 * ref.double().abs()).all()
+    c16 = run(a, b, BF, transpose_b, cuda_device)
+    assert torch.allclose(c16.float(), ref.to(BF).float(), **TOL16)
+    # small integers: every partial sum is exact, the result must be bit-identical
+    ai = torch.randint(-3, 4, (m, k), generator=g).float().to(F8)
+    bi = torch.randint(-3, 4, (n, k) if transpose_b else (k, n), generator=g).float().to(F8)
+    assert torch.equal(run(ai, bi, F32, transpose_b, cuda_device), O.matmul(ai.float(), bi.float(), F32, transpose_b))

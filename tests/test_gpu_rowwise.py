@@ -174,6 +174,26 @@ def test_reduce_shapes(cuda_device, dtype, rows, cols):
     assert ((y.cpu().double() - ref).abs() <= tol).all()
 
 
+@pytest.mark.parametrize("dtype", [torch.int32, torch.uint32, torch.int16])
+@pytest.mark.parametrize("rows,cols", [(64, 64), (7, 1), (33, 1000), (3, 70001)])
+def test_reduce_sum_integer_tiles_bit_exact(cuda_device, dtype, rows, cols):
+    """ppl_reduce_sum on integer tiles (codegen_ppl.cc:1570-1592): exact, wrap-around included."""
+    g = gen(rows * 3 + cols)
+    if dtype == torch.int16:
+        x = torch.randint(-2 ** 15, 2 ** 15, (rows, cols), generator=g, dtype=torch.int32).to(torch.int16)
+    else:
+        x = torch.randint(-2 ** 31, 2 ** 31 - 1, (rows, cols), generator=g, dtype=torch.int64).to(torch.int32)
+        if dtype == torch.uint32:
+            x = x.view(torch.uint32)
+    y = torch.zeros(rows, 1, dtype=dtype, device=cuda_device)
+    assert ops.reduce_rows(x.to(cuda_device), y, "sum") == 0
+    ref = O.reduce_sum(x)
+    bits = torch.int16 if dtype == torch.int16 else torch.int32
+    assert torch.equal(y.cpu().view(bits), ref.view(bits))
+    with pytest.raises(RuntimeError, match="sum only"):
+        ops.reduce_rows(x.to(cuda_device), y, "max")
+
+
 def test_sigmoid_golden_and_tile_ops(cuda_device):
     g = load_golden("sigmoid_fp32")
     y = torch.zeros_like(g["a"], device=cuda_device)
@@ -290,3 +310,24 @@ def test_generic_entry_point_runs_programs(cuda_device):
     assert rc == 0 and torch.equal(c_typed.view(torch.int16), c_run.view(torch.int16))
     rc = N.run("swiglu", [0, 0, 0], [16, N.TL_BF16], stream)
     assert rc == -1 and "null" in N.last_error()
+
+
+# ------------------------------------------------------------------ a bounded wait that runs out
+def test_expired_bounded_wait_reaches_the_host_and_leaves_the_context_usable(cuda_device):
+    """Every barrier wait of the tensor-core kernels is bounded; when one gives up the kernel raises its abort
+    flag, returns and writes a host-visible status word.  The self-test kernel makes exactly that happen (one
+    warp, a barrier nothing arrives at, a 2 ms budget - no copy or MMA in flight, nothing faults or hangs)."""
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert ops.selftest_bounded_wait(2000) == 0
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="TL_B200_EDEVICE"):
+        ops.check_device_status()
+    assert ops.device_status() == 0                              # reading clears it
+    x = torch.randn(8, 64, generator=gen(3)).to(BF).to(cuda_device)
+    y = torch.zeros_like(x)
+    assert ops.rmsnorm(x, y, eps=1e-6) == 0                      # the context is still good
+    torch.cuda.synchronize()
+    assert torch.allclose(y.cpu().float(), O.rmsnorm(x.cpu(), eps=1e-6).float(), **TOL16)
+    with pytest.raises(RuntimeError, match="budget"):
+        ops.selftest_bounded_wait(10 ** 7)

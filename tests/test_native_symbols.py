@@ -71,3 +71,24 @@ def test_generic_entry_point_dispatches_and_validates_without_gpu():
     lib = _native.load()
     rc = lib.tl_b200_run(99, (ctypes.c_void_p * 1)(), (ctypes.c_int64 * 1)(), None)
     assert rc == -1 and "unknown kernel id" in _native.last_error()
+
+
+def test_device_status_error_path_on_the_host(monkeypatch):
+    """`ops.check_device_status()` turns a non-zero status word into TL_B200_EDEVICE (-4); the word itself is
+    faked here, the GPU test makes a real bounded wait run out."""
+    from tilelang import _native, ops
+
+    class FakeLib:
+        def tl_b200_device_status(self):
+            return 1
+
+        def tl_b200_last_error(self):
+            return b"a kernel gave up a bounded wait (device status 1)"
+
+    monkeypatch.setattr(_native, "_lib", FakeLib())
+    with pytest.raises(RuntimeError, match="TL_B200_EDEVICE.*bounded wait"):
+        ops.check_device_status()
+    monkeypatch.setattr(_native, "_lib", None)
+    lib = _native.load()
+    assert lib.tl_b200_device_status() == 0                      # no status word exists without a device
+    assert lib.tl_b200_selftest_bounded_wait(0, None) == -1 and "budget" in _native.last_error()

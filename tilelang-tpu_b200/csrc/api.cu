@@ -108,9 +108,36 @@ int take_device_status() {
   return v;
 }
 
+// One warp waits, with the library's bounded wait, on a barrier that nothing ever arrives at: the wait
+// runs out of its (short) budget, the abort flag is raised and the status word is written exactly as the
+// tensor-core kernels do when one of their waits gives up.  No copy or MMA is in flight, nothing hangs.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long budget_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    sm100::mbar_init(sm100::smem_u32(&bar), 1);
+    sm100::mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = sm100::mbar_wait_budget(sm100::smem_u32(&bar), 0, &abort_flag, budget_ns);
+    if (!ok && status) *status = abort_flag;
+  }
+}
+
 }  // namespace tl
 
 extern "C" {
+
+int tl_b200_selftest_bounded_wait(int64_t budget_us, void* stream) {
+  TL_REQUIRE(budget_us >= 1 && budget_us <= 100000, "selftest_bounded_wait: budget must be 1 us .. 100 ms");
+  int* status = tl::device_status_word();
+  TL_REQUIRE(status != nullptr, "selftest_bounded_wait: the host-mapped status word could not be created");
+  tl::bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (unsigned long long)budget_us * 1000ull);
+  TL_LAUNCH_CHECK("bounded_wait_selftest_kernel");
+  return TL_B200_OK;
+}
 
 int tl_b200_init(int device) {
   int n = 0;

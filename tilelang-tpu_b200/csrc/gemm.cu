@@ -6,6 +6,8 @@
 // drain the other accumulator (tcgen05.ld -> round -> global stores) while the next tile's main
 // loop already runs.  B may be [K,N] row-major (MN-major operand, the layout of the reference
 // matmul program) or [N,K] row-major (K-major, `transpose_B=True` of ppl_gemm).
+// e4m3 operands (the plain, un-scaled FP8 form of ppl_gemm, src/target/codegen_ppl.cc:775-790) run the same
+// kernel with `kind::f8f6f4`: every byte offset is the same, a stage simply holds twice the K elements.
 // fp32 inputs and shapes TMA cannot describe use a plain shared-memory-tiled FMA kernel.
 #include "sm100.cuh"
 
@@ -18,14 +20,14 @@ using namespace sm100;
 // tcgen05 kernel
 // =================================================================================
 constexpr int kBM = 128;        // rows of C per tile = TMEM lanes
-constexpr int kBK = 64;         // K per stage: 64 x 2 bytes = one 128-byte swizzle row
-constexpr int kUmmaK = 16;      // K of one tcgen05.mma for 16-bit operands
+constexpr int kRowBytes = 128;   // K bytes per stage row: one 128-byte swizzle row (64 16-bit or 128 8-bit elements)
+constexpr int kUmmaBytes = 32;  // K bytes of one tcgen05.mma (16 16-bit or 32 8-bit elements)
 constexpr int kGemmThreads = 256;
 constexpr int kEpiWarp0 = 4;    // warps 4..7 form the epilogue (warp%4 selects the TMEM lane quarter)
 
 template <int BN> struct GemmCfg {
-  static constexpr int kStageA = kBM * kBK * 2;
-  static constexpr int kStageB = BN * kBK * 2;
+  static constexpr int kStageA = kBM * kRowBytes;
+  static constexpr int kStageB = BN * kRowBytes;
   static constexpr int kStages = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
   static constexpr int kTmemCols = 2 * BN;                      // two accumulators
   static constexpr int kSmemBytes = kStages * (kStageA + kStageB) + 1024 /*alignment*/ + 256 /*barriers*/;
@@ -37,7 +39,7 @@ struct GemmParams {
   int m, n, k;
   int tiles_m, tiles_n;
   int c_is_f32;       // output element: 0 = same 16-bit type as the inputs, 1 = fp32
-  int in_fmt;         // kFmtF16 / kFmtBF16
+  int in_fmt;         // kFmtF16 / kFmtBF16 (16-bit operands), kFmtE4M3 (8-bit)
   int* status;
 };
 
@@ -83,12 +85,15 @@ __device__ __forceinline__ void store_row_chunk(TOut* dst, const uint32_t (&acc)
   }
 }
 
-template <int BN, bool B_MN_MAJOR, typename TOut>
+template <int BN, bool B_MN_MAJOR, typename TOut, int EB>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const GemmParams p) {
   using Cfg = GemmCfg<BN>;
   constexpr int STAGES = Cfg::kStages;
+  constexpr int kBK = kRowBytes / EB;          // K elements per stage (EB = bytes per operand element)
+  constexpr int kSlabCols = kRowBytes / EB;    // MN-major B: columns per 128-byte slab
+  constexpr int kSlabBytes = kBK * kRowBytes;  // ... and the bytes of one slab (kBK k-rows)
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;          // swizzle atoms need 1024-byte alignment
@@ -147,10 +152,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           mbar_expect_tx(full, Cfg::kStageA + Cfg::kStageB);
           tma_load_2d(smem_a + stage * Cfg::kStageA, &tm_a, full, kb * kBK, tm * kBM);
           if constexpr (B_MN_MAJOR) {
-            // B is [K,N]: 64-column slabs of 64 k-rows, 8 KB each
+            // B is [K,N]: slabs of 128 bytes of columns x kBK k-rows (8 KB for 16-bit, 16 KB for 8-bit operands)
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(smem_b + stage * Cfg::kStageB + j * (64 * kBK * 2), &tm_b, full, tn * BN + j * 64,
+            for (int j = 0; j < BN / kSlabCols; ++j)
+              tma_load_2d(smem_b + stage * Cfg::kStageB + j * kSlabBytes, &tm_b, full, tn * BN + j * kSlabCols,
                           kb * kBK);
           } else {
             tma_load_2d(smem_b + stage * Cfg::kStageB, &tm_b, full, kb * kBK, tn * BN);
@@ -179,17 +184,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const uint32_t a_addr = smem_a + stage * Cfg::kStageA;
           const uint32_t b_addr = smem_b + stage * Cfg::kStageB;
 #pragma unroll
-          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
-            // A, K-major: 8-row groups are 1024 B apart; a K step of 16 elements is 32 B.
-            const uint64_t a_desc = smem_desc_sw128(a_addr + kk * (kUmmaK * 2), 16, 1024);
+          for (int kk = 0; kk < kRowBytes / kUmmaBytes; ++kk) {
+            // A, K-major: 8-row groups are 1024 B apart; a K step is 32 B.
+            const uint64_t a_desc = smem_desc_sw128(a_addr + kk * kUmmaBytes, 16, 1024);
             uint64_t b_desc;
             if constexpr (B_MN_MAJOR)
-              // MN-major: 64-column slabs 8 KB apart (leading), 8-k-row groups 1 KB apart (stride);
-              // a K step of 16 rows is 2 KB.
-              b_desc = smem_desc_sw128(b_addr + kk * (kUmmaK * 128), 64 * kBK * 2, 1024);
+              // MN-major: slabs one slab apart (leading), 8-k-row groups 1 KB apart (stride);
+              // a K step is 32 / EB k-rows of 128 B.
+              b_desc = smem_desc_sw128(b_addr + kk * (kUmmaBytes / EB * kRowBytes), kSlabBytes, 1024);
             else
-              b_desc = smem_desc_sw128(b_addr + kk * (kUmmaK * 2), 16, 1024);
-            mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+              b_desc = smem_desc_sw128(b_addr + kk * kUmmaBytes, 16, 1024);
+            if constexpr (EB == 2) mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            else mma_f8_ss(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
           mma_commit(bar_empty + 8 * stage);          // stage is free once these MMAs retire
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -304,9 +310,9 @@ static int launch_simt(const void* a, const void* b, void* c, int m, int n, int 
   return TL_B200_OK;
 }
 
-template <int BN, bool B_MN, typename TOut>
+template <int BN, bool B_MN, typename TOut, int EB = 2>
 static int launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t s) {
-  auto kernel = gemm_tcgen05_kernel<BN, B_MN, TOut>;
+  auto kernel = gemm_tcgen05_kernel<BN, B_MN, TOut, EB>;
   TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN>::kSmemBytes));
   const int tiles = p.tiles_m * p.tiles_n;
   const int grid = tiles < sm_count() ? tiles : sm_count();
@@ -323,11 +329,27 @@ static int launch_tc_out(const CUtensorMap& ta, const CUtensorMap& tb, const Gem
   return b_mn ? launch_tc<BN, true, T16>(ta, tb, p, s) : launch_tc<BN, false, T16>(ta, tb, p, s);
 }
 
+// e4m3 operands: out_kind 0 = fp32, 1 = bf16, 2 = fp16
+template <int BN>
+static int launch_tc_f8(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bool b_mn, int out_kind,
+                        cudaStream_t s) {
+  if (out_kind == 0)
+    return b_mn ? launch_tc<BN, true, float, 1>(ta, tb, p, s) : launch_tc<BN, false, float, 1>(ta, tb, p, s);
+  if (out_kind == 1)
+    return b_mn ? launch_tc<BN, true, __nv_bfloat16, 1>(ta, tb, p, s) : launch_tc<BN, false, __nv_bfloat16, 1>(ta, tb, p, s);
+  return b_mn ? launch_tc<BN, true, __half, 1>(ta, tb, p, s) : launch_tc<BN, false, __half, 1>(ta, tb, p, s);
+}
+
+// T16 = uint8_t selects the e4m3 form (out_kind as above); otherwise the 16-bit operand type
 template <typename T16>
 static int gemm_tc(const void* a, const void* b, void* c, int m, int n, int k, bool trans_b, bool c_f32,
-                   cudaStream_t s) {
+                   cudaStream_t s, int out_kind = 0) {
+  constexpr bool is_f8 = std::is_same<T16, uint8_t>::value;
+  constexpr int EB = is_f8 ? 1 : 2;
+  constexpr int kBK = kRowBytes / EB;
   const bool is_bf16 = std::is_same<T16, __nv_bfloat16>::value;
-  const CUtensorMapDataType dt = is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = is_f8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                       : (is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
   // Tile width: the widest that still gives every SM a tile.
   int bn = 256;
   const int tiles_m = (m + kBM - 1) / kBM;
@@ -338,21 +360,21 @@ static int gemm_tc(const void* a, const void* b, void* c, int m, int n, int k, b
   CUtensorMap ta, tb;
   {
     uint64_t dims[2] = {(uint64_t)k, (uint64_t)m};
-    uint64_t strides[1] = {(uint64_t)k * 2};
+    uint64_t strides[1] = {(uint64_t)k * EB};
     uint32_t box[2] = {(uint32_t)kBK, (uint32_t)kBM};
     int rc = make_tensor_map(&ta, dt, 2, a, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
   if (trans_b) {   // B is [N,K]: K-major
     uint64_t dims[2] = {(uint64_t)k, (uint64_t)n};
-    uint64_t strides[1] = {(uint64_t)k * 2};
+    uint64_t strides[1] = {(uint64_t)k * EB};
     uint32_t box[2] = {(uint32_t)kBK, (uint32_t)bn};
     int rc = make_tensor_map(&tb, dt, 2, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-  } else {         // B is [K,N]: MN-major, loaded as 64-column slabs
+  } else {         // B is [K,N]: MN-major, loaded as slabs of 128 bytes of columns
     uint64_t dims[2] = {(uint64_t)n, (uint64_t)k};
-    uint64_t strides[1] = {(uint64_t)n * 2};
-    uint32_t box[2] = {64u, (uint32_t)kBK};
+    uint64_t strides[1] = {(uint64_t)n * EB};
+    uint32_t box[2] = {(uint32_t)(kRowBytes / EB), (uint32_t)kBK};
     int rc = make_tensor_map(&tb, dt, 2, b, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
   }
@@ -363,13 +385,23 @@ static int gemm_tc(const void* a, const void* b, void* c, int m, int n, int k, b
   p.tiles_m = tiles_m;
   p.tiles_n = (n + bn - 1) / bn;
   p.c_is_f32 = c_f32 ? 1 : 0;
-  p.in_fmt = is_bf16 ? kFmtBF16 : kFmtF16;
+  p.in_fmt = is_f8 ? kFmtE4M3 : (is_bf16 ? kFmtBF16 : kFmtF16);
   p.status = device_status_word();
   const bool b_mn = !trans_b;
-  switch (bn) {
-    case 256: return launch_tc_out<256, T16>(ta, tb, p, b_mn, s);
-    case 128: return launch_tc_out<128, T16>(ta, tb, p, b_mn, s);
-    default: return launch_tc_out<64, T16>(ta, tb, p, b_mn, s);
+  if constexpr (is_f8) {
+    if (bn < 128 && b_mn) bn = 128;       // an MN-major slab of 8-bit columns is 128 columns wide
+    p.tiles_n = (n + bn - 1) / bn;
+    switch (bn) {
+      case 256: return launch_tc_f8<256>(ta, tb, p, b_mn, out_kind, s);
+      case 128: return launch_tc_f8<128>(ta, tb, p, b_mn, out_kind, s);
+      default: return launch_tc_f8<64>(ta, tb, p, b_mn, out_kind, s);
+    }
+  } else {
+    switch (bn) {
+      case 256: return launch_tc_out<256, T16>(ta, tb, p, b_mn, s);
+      case 128: return launch_tc_out<128, T16>(ta, tb, p, b_mn, s);
+      default: return launch_tc_out<64, T16>(ta, tb, p, b_mn, s);
+    }
   }
 }
 
@@ -384,11 +416,21 @@ extern "C" int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, in
   if (m == 0 || n == 0) return TL_B200_OK;
   TL_REQUIRE(a && b && c, "gemm: null tensor pointer");
   TL_REQUIRE(k > 0, "gemm: K must be positive");
-  TL_REQUIRE(out_dtype == in_dtype || out_dtype == TL_F32, "gemm: output must be the input type or float32");
+  TL_REQUIRE(out_dtype == in_dtype || out_dtype == TL_F32 ||
+                 (in_dtype == TL_E4M3 && (out_dtype == TL_BF16 || out_dtype == TL_F16)),
+             "gemm: output must be the input type or float32 (e4m3 operands: float32, bfloat16 or float16)");
+  TL_REQUIRE(!(in_dtype == TL_E4M3 && out_dtype == TL_E4M3), "gemm: e4m3 operands need a float32, bfloat16 or float16 output");
   cudaStream_t s = (cudaStream_t)stream;
   const bool tb = trans_b != 0;
   const int M = (int)m, N = (int)n, K = (int)k;
   if (in_dtype == TL_F32) return launch_simt<float, float>(a, b, c, M, N, K, tb, s);
+  if (in_dtype == TL_E4M3) {
+    // plain (un-scaled) FP8 product: tensor cores only; TMA needs 16-byte aligned bases and row strides
+    TL_REQUIRE(aligned16(a) && aligned16(b) && K % 16 == 0 && (tb || N % 16 == 0),
+               "gemm: e4m3 operands need 16-byte aligned tensors, K %% 16 == 0 and (transposed B or N %% 16 == 0)");
+    const int out_kind = out_dtype == TL_F32 ? 0 : (out_dtype == TL_BF16 ? 1 : 2);
+    return gemm_tc<uint8_t>(a, b, c, M, N, K, tb, out_dtype == TL_F32, s, out_kind);
+  }
   TL_REQUIRE(in_dtype == TL_F16 || in_dtype == TL_BF16, "gemm: unsupported input dtype %d", in_dtype);
   // TMA needs 16-byte aligned bases and row strides
   const bool tma_ok = aligned16(a) && aligned16(b) && K % 8 == 0 && (tb || N % 8 == 0);

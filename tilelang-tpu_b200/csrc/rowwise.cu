@@ -499,6 +499,31 @@ static int reduce_dispatch(const void* x, void* y, int64_t rows, int64_t cols, c
   return TL_B200_OK;
 }
 
+// Integer row sums (ppl_reduce_sum accepts int32 / uint32 / int16 tiles, src/target/codegen_ppl.cc:1570-1592):
+// a warp per row, sums modulo 2^32 (int16: the 32-bit sum cut to 16 bits), so signed and unsigned share the bits.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+reduce_sum_int_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int64_t cols) {
+  const int lane = threadIdx.x % 32;
+  const int64_t row = (int64_t)blockIdx.x * (kThreads / 32) + threadIdx.x / 32;
+  if (row >= rows) return;
+  const T* xr = x + row * cols;
+  uint32_t acc = 0;
+  for (int64_t c = lane; c < cols; c += 32) acc += (uint32_t)(int32_t)xr[c];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) y[row] = (T)acc;
+}
+
+template <typename T>
+static int reduce_sum_int(const void* x, void* y, int64_t rows, int64_t cols, cudaStream_t s) {
+  const int64_t grid = (rows + kThreads / 32 - 1) / (kThreads / 32);
+  TL_REQUIRE(grid < (1ll << 31), "reduce_rows: too many rows (%lld)", (long long)rows);
+  reduce_sum_int_kernel<T><<<(unsigned)grid, kThreads, 0, s>>>((const T*)x, (T*)y, rows, cols);
+  TL_LAUNCH_CHECK("reduce_sum_int_kernel");
+  return TL_B200_OK;
+}
+
 // =================================================================================
 // Elementwise tile ops (scalar indexing; these back the generic per-op path, not a
 // bandwidth headline).
@@ -707,6 +732,11 @@ int tl_b200_reduce_rows(const void* x, void* y, int64_t rows, int64_t cols, int 
   if (rows == 0) return TL_B200_OK;
   TL_REQUIRE(x && y, "reduce_rows: null tensor pointer");
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TL_I32 || dtype == TL_U32 || dtype == TL_I16) {
+    TL_REQUIRE(op == 0, "reduce_rows: integer tiles support the sum only (as ppl_reduce_sum does)");
+    if (dtype == TL_I16) return reduce_sum_int<int16_t>(x, y, rows, cols, s);
+    return reduce_sum_int<uint32_t>(x, y, rows, cols, s);
+  }
   if (op == 0) { TL_FLOAT_DISPATCH(dtype, (reduce_dispatch<T, false>(x, y, rows, cols, s))); }
   TL_FLOAT_DISPATCH(dtype, (reduce_dispatch<T, true>(x, y, rows, cols, s)));
 }

@@ -67,7 +67,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded wait.  Returns false if the CTA is aborting (either this wait ran out of budget or
 // another role raised the flag).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                 unsigned long long budget_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   uint32_t spins = 0;
@@ -75,12 +76,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63u) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitBudgetNs) {
+      if (global_timer_ns() - t0 > budget_ns) {
         *abort_flag = kStatusWaitTimeout;
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_budget(bar, parity, abort_flag, kWaitBudgetNs);
 }
 
 // ---- TMA ------------------------------------------------------------------------------------------

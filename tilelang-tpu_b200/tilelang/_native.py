@@ -15,7 +15,7 @@ from pathlib import Path
 _PKG_ROOT = Path(__file__).resolve().parent.parent
 DEFAULT_LIB = _PKG_ROOT / "lib" / "libtl_b200.so"
 
-TL_F32, TL_F16, TL_BF16, TL_E4M3, TL_I32, TL_U32 = range(6)
+TL_F32, TL_F16, TL_BF16, TL_E4M3, TL_I32, TL_U32, TL_I16 = range(7)
 
 # name -> (restype, argtypes).  Kept in declaration order of include/tl_b200.h.
 PROTOTYPES = {
@@ -24,6 +24,7 @@ PROTOTYPES = {
     "tl_b200_last_error": (c_char_p, []),
     "tl_b200_launch_count": (c_int64, []),
     "tl_b200_device_status": (c_int, []),
+    "tl_b200_selftest_bounded_wait": (c_int, [c_int64, c_void_p]),
     "tl_b200_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_float, c_int, c_void_p]),
     "tl_b200_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
     "tl_b200_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),

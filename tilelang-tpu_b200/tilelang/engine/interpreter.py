@@ -65,9 +65,10 @@ def validate(func: PrimFunc) -> None:
         if op.name == "ppl.gemm":
             a, b, c = op.args
             _need(not op.attrs["transpose_A"], "ppl.gemm: transpose_A is not supported (the reference's code generator ignores it)")
-            _need(a.dtype == b.dtype and a.dtype in _FLOATS, "ppl.gemm: A and B must share a float dtype")
+            _need(a.dtype == b.dtype and a.dtype in _FLOATS + ("float8_e4m3", "e4m3_float8"),
+                  "ppl.gemm: A and B must share a float dtype (fp32, fp16, bf16 or e4m3)")
             if op.attrs["transpose_B"]:
-                _need(c.dtype in (a.dtype, "float32"), "ppl.gemm: C must have the input dtype or float32")
+                _need(c.dtype in (a.dtype, "float32") and c.dtype in _FLOATS, "ppl.gemm: C must have the input dtype or float32")
             else:
                 _need(c.dtype == "float32", "ppl.gemm without transpose_B accumulates: C must be float32")
         if op.name in _BINARY_OPS:

@@ -16,6 +16,7 @@ _DTYPES = {
     torch.bfloat16: N.TL_BF16,
     torch.int32: N.TL_I32,
     torch.uint32: N.TL_U32,
+    torch.int16: N.TL_I16,
 }
 if hasattr(torch, "float8_e4m3fn"):
     _DTYPES[torch.float8_e4m3fn] = N.TL_E4M3
@@ -226,8 +227,28 @@ def device_status() -> int:
     return int(N.load().tl_b200_device_status())
 
 
+def check_device_status() -> None:
+    """Raise if a kernel gave up a bounded wait since the last check (status TL_B200_EDEVICE); call after the
+    stream has been synchronised.  The adapter of the reference raises on a non-zero native status in the same
+    way (cython_wrapper.pyx:160-163)."""
+    code = device_status()
+    if code:
+        raise RuntimeError(f"device status {code} (TL_B200_EDEVICE): {N.last_error()}")
+
+
+def selftest_bounded_wait(budget_us: int = 1000) -> int:
+    """Launch the one-warp kernel whose bounded wait is made to run out (nothing arrives at its barrier)."""
+    index = torch.cuda.current_device()
+    if index not in _initialised_devices:
+        N.check(N.load().tl_b200_init(index), "tl_b200_init")
+        _initialised_devices.add(index)
+    return N.check(N.load().tl_b200_selftest_bounded_wait(int(budget_us), torch.cuda.current_stream().cuda_stream),
+                   "tl_b200_selftest_bounded_wait")
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, transpose_b: bool = False) -> int:
-    """c = a @ b (b is (K, N)) or a @ b.T (b is (N, K), transpose_b=True); fp32 accumulation."""
+    """c = a @ b (b is (K, N)) or a @ b.T (b is (N, K), transpose_b=True); fp32 accumulation.
+    fp16 / bf16 / fp32 operands, or e4m3 (the plain, un-scaled FP8 form of ppl_gemm)."""
     if a.dim() != 2 or b.dim() != 2 or c.dim() != 2:
         raise ValueError("gemm: a, b, c must be 2-D")
     m, k = a.shape
@@ -236,9 +257,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, transpose_b: bool = 
         raise ValueError("gemm K shape check failed")          # message of ppl_gemm's assert
     if tuple(c.shape) != (m, n):
         raise ValueError(f"gemm: c must be ({m}, {n})")
-    if a.dtype != b.dtype or c.dtype not in (a.dtype, torch.float32):
+    f8 = getattr(torch, "float8_e4m3fn", None)
+    if a.dtype != b.dtype:
+        raise ValueError("gemm: a and b must share a dtype")
+    if a.dtype == f8:
+        if c.dtype not in (torch.float32, torch.bfloat16, torch.float16):
+            raise ValueError("gemm: e4m3 operands take a float32, bfloat16 or float16 output")
+    elif c.dtype not in (a.dtype, torch.float32):
         raise ValueError("gemm: a and b must share a dtype; c has that dtype or float32")
-    if a.dtype not in (torch.float16, torch.bfloat16, torch.float32):
+    if a.dtype not in (torch.float16, torch.bfloat16, torch.float32, f8):
         raise ValueError(f"gemm: unsupported dtype {a.dtype}")
     s = _prepare(a, b, c)
     return N.check(N.load().tl_b200_gemm(_ptr(a), _ptr(b), _ptr(c), m, n, k, 1 if transpose_b else 0,
