@@ -158,6 +158,12 @@ int tl_b200_topk(const void* src, void* out_vals, int32_t* out_idx, int64_t rows
  * trans_b or n % 16 == 0), out_dtype TL_F32, TL_BF16 or TL_F16.                        */
 int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
                  int in_dtype, int out_dtype, void* stream);
+/* The same with the width of the C tile chosen by the caller: tile_n 64, 128 or 256 columns (0 = the
+ * library's own rule, the widest tile that still gives every SM one).  For a shape -> tile table kept by
+ * the host (role of the reference's tuner, tilelang/autotuner/__init__.py:90-345).  Results do not depend
+ * on the choice.                                                                                        */
+int tl_b200_gemm_tiled(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
+                       int in_dtype, int out_dtype, int tile_n, void* stream);
 
 /* ---- gated MLP, front half -----------------------------------------------------
  * out[m,n] = silu(x Wg^T) * (x Wu^T) with x [m,k] and w_gate, w_up [n,k] row-major, all of

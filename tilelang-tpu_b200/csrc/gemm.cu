@@ -343,7 +343,7 @@ static int launch_tc_f8(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
 // T16 = uint8_t selects the e4m3 form (out_kind as above); otherwise the 16-bit operand type
 template <typename T16>
 static int gemm_tc(const void* a, const void* b, void* c, int m, int n, int k, bool trans_b, bool c_f32,
-                   cudaStream_t s, int out_kind = 0) {
+                   cudaStream_t s, int out_kind = 0, int tile_n = 0) {
   constexpr bool is_f8 = std::is_same<T16, uint8_t>::value;
   constexpr int EB = is_f8 ? 1 : 2;
   constexpr int kBK = kRowBytes / EB;
@@ -356,6 +356,7 @@ static int gemm_tc(const void* a, const void* b, void* c, int m, int n, int k, b
   auto tiles_for = [&](int w) { return (int64_t)tiles_m * ((n + w - 1) / w); };
   if (tiles_for(256) < sm_count()) bn = 128;
   if (bn == 128 && tiles_for(128) < sm_count()) bn = 64;
+  if (tile_n == 64 || tile_n == 128 || tile_n == 256) bn = tile_n;     // the caller's choice (a tuned table)
 
   CUtensorMap ta, tb;
   {
@@ -411,6 +412,12 @@ using namespace tl;
 
 extern "C" int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
                             int in_dtype, int out_dtype, void* stream) {
+  return tl_b200_gemm_tiled(a, b, c, m, n, k, trans_b, in_dtype, out_dtype, 0, stream);
+}
+
+extern "C" int tl_b200_gemm_tiled(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
+                                  int in_dtype, int out_dtype, int tile_n, void* stream) {
+  TL_REQUIRE(tile_n == 0 || tile_n == 64 || tile_n == 128 || tile_n == 256, "gemm: tile_n must be 0, 64, 128 or 256");
   TL_REQUIRE(m >= 0 && n >= 0 && k >= 0, "gemm: negative size");
   TL_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), "gemm: dimension exceeds 2^31");
   if (m == 0 || n == 0) return TL_B200_OK;
@@ -429,14 +436,14 @@ extern "C" int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, in
     TL_REQUIRE(aligned16(a) && aligned16(b) && K % 16 == 0 && (tb || N % 16 == 0),
                "gemm: e4m3 operands need 16-byte aligned tensors, K %% 16 == 0 and (transposed B or N %% 16 == 0)");
     const int out_kind = out_dtype == TL_F32 ? 0 : (out_dtype == TL_BF16 ? 1 : 2);
-    return gemm_tc<uint8_t>(a, b, c, M, N, K, tb, out_dtype == TL_F32, s, out_kind);
+    return gemm_tc<uint8_t>(a, b, c, M, N, K, tb, out_dtype == TL_F32, s, out_kind, tile_n);
   }
   TL_REQUIRE(in_dtype == TL_F16 || in_dtype == TL_BF16, "gemm: unsupported input dtype %d", in_dtype);
   // TMA needs 16-byte aligned bases and row strides
   const bool tma_ok = aligned16(a) && aligned16(b) && K % 8 == 0 && (tb || N % 8 == 0);
   if (tma_ok) {
-    if (in_dtype == TL_BF16) return gemm_tc<__nv_bfloat16>(a, b, c, M, N, K, tb, out_dtype == TL_F32, s);
-    return gemm_tc<__half>(a, b, c, M, N, K, tb, out_dtype == TL_F32, s);
+    if (in_dtype == TL_BF16) return gemm_tc<__nv_bfloat16>(a, b, c, M, N, K, tb, out_dtype == TL_F32, s, 0, tile_n);
+    return gemm_tc<__half>(a, b, c, M, N, K, tb, out_dtype == TL_F32, s, 0, tile_n);
   }
   if (in_dtype == TL_BF16) {
     if (out_dtype == TL_F32) return launch_simt<__nv_bfloat16, float>(a, b, c, M, N, K, tb, s);
