@@ -487,3 +487,46 @@ def test_rope_program_with_mismatched_token_blocks_is_rejected():
             T.ppl_copy(o, Out[bx * bt:(bx + 1) * bt, by, 0:width])
     with pytest.raises(UnsupportedProgram, match="same token block"):
         bind(shifted)
+
+
+# ------------------------------------------------------------------ kernel cache and tile table
+def test_cache_is_keyed_by_program_content_and_persists_its_record(tmp_path, monkeypatch):
+    from tilelang import cache
+    monkeypatch.setenv("TILELANG_B200_CACHE_DIR", str(tmp_path))
+    cache.clear_cache()
+    k1 = tilelang.compile(rms_norm_program(64, 128, 32, eps=1e-6), out_idx=-1, target="b200")
+    k2 = tilelang.compile(rms_norm_program(64, 128, 32, eps=1e-6), out_idx=-1, target="b200")     # a second, equal program object
+    assert k1 is k2
+    k3 = tilelang.compile(rms_norm_program(64, 128, 32, eps=1e-5), out_idx=-1, target="b200")
+    assert k3 is not k1 and k3.cache_key != k1.cache_key
+    rec = cache.load_record(k1.cache_key)
+    assert rec["program"] == "rmsnorm" and rec["entry_point"] == "tl_b200_rmsnorm" and rec["facts"]["eps"] == pytest.approx(1e-6)
+    # a record that disagrees with today's binding (e.g. written by an older library) is reported and replaced
+    (tmp_path / "programs" / f"{k1.cache_key}.json").write_text('{"program": "generic", "entry_point": "x", "facts": {}}')
+    cache.clear_cache()
+    with pytest.warns(UserWarning, match="bound to"):
+        tilelang.compile(rms_norm_program(64, 128, 32, eps=1e-6), out_idx=-1, target="b200")
+    assert cache.load_record(k1.cache_key)["program"] == "rmsnorm"
+    cache.clear_cache()
+
+
+def test_tile_table_round_trip(tmp_path, monkeypatch):
+    from tilelang import cache
+    monkeypatch.setenv("TILELANG_B200_CACHE_DIR", str(tmp_path))
+    cache.clear_cache(disk=True)
+    assert cache.tile_choice("gemm", m=128, n=256, k=64, dtype="torch.bfloat16", transpose_b=False) is None
+    cache.set_tile_choice("gemm", {"tile_n": 128, "ms": 0.5}, m=128, n=256, k=64, dtype="torch.bfloat16", transpose_b=False)
+    cache.clear_cache()
+    cache._tile_table = None                       # a new process reads the file
+    assert cache.tile_choice("gemm", m=128, n=256, k=64, dtype="torch.bfloat16", transpose_b=False)["tile_n"] == 128
+    cache.clear_cache(disk=True)
+
+
+def test_autotuner_interface_rejects_unrunnable_configs_on_cpu():
+    from tilelang.autotuner import AutoTuner, product_configs
+    cfgs = product_configs(blk_m=[32, 48])
+    assert cfgs == [{"blk_m": 32}, {"blk_m": 48}]
+    tuner = AutoTuner.from_kernel(lambda blk_m: rms_norm_program(64, 128, blk_m), cfgs).set_compile_args(out_idx=-1)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="no configuration"):     # timing needs the GPU: there is no CPU path
+            tuner.run(warmup=1, rep=1)

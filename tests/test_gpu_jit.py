@@ -202,3 +202,30 @@ def test_library_programs_fp8_gemm_and_paged_mla(cuda_device):
                 cfg["cache_seqlens"], out) == 0
     ref = O.mla_decode_paged(cfg["q"][:, 0], cfg["kv_cache"], cfg["kv_scale"], cfg["block_table"], cfg["cache_seqlens"], 512)
     assert torch.allclose(out[:, 0].float(), ref.float(), atol=2e-2, rtol=2e-2)
+
+
+def test_autotuner_and_tile_table(cuda_device, tmp_path, monkeypatch):
+    """The tuner times program configurations on the GPU; `tune_gemm` fills the shape -> tile table that
+    `ops.gemm` reads, and the result does not depend on the tile."""
+    from tilelang import cache, ops
+    from tilelang.autotuner import AutoTuner, product_configs, tune_gemm
+    monkeypatch.setenv("TILELANG_B200_CACHE_DIR", str(tmp_path))
+    cache.clear_cache(disk=True)
+    res = AutoTuner.from_kernel(lambda blk_m: rms_norm_program(256, 512, blk_m, eps=1e-6),
+                                product_configs(blk_m=[32, 64, 48])).set_compile_args(
+        out_idx=-1, ref_prog=lambda a: O.rmsnorm(a.cpu(), eps=1e-6), rtol=2e-2, atol=2e-2).run(warmup=2, rep=3)
+    assert res.config["blk_m"] in (32, 64) and res.latency > 0
+    assert [t for t in res.trials if "error" in t][0]["config"] == {"blk_m": 48}       # 48 does not divide 256
+    choice = tune_gemm(512, 1024, 256, torch.bfloat16, warmup=1, rep=2)
+    assert choice["tile_n"] in (64, 128, 256)
+    assert cache.tile_choice("gemm", m=512, n=1024, k=256, dtype="torch.bfloat16", transpose_b=False)["tile_n"] == choice["tile_n"]
+    g = gen(21)
+    a = torch.randn(512, 256, generator=g).bfloat16().to(cuda_device)
+    b = torch.randn(256, 1024, generator=g).bfloat16().to(cuda_device)
+    outs = []
+    for t in (0, 64, 128, 256, None):
+        c = torch.zeros(512, 1024, dtype=torch.bfloat16, device=cuda_device)
+        ops.gemm(a, b, c, tile_n=t)
+        outs.append(c)
+    assert all(torch.equal(outs[0].view(torch.int16), o.view(torch.int16)) for o in outs[1:])
+    cache.clear_cache(disk=True)

@@ -15,3 +15,4 @@ from .engine import lower  # noqa: F401,E402
 from .jit import JITKernel, compile, jit  # noqa: F401,E402
 from .cache import cached, clear_cache  # noqa: F401,E402
 from .profiler import Profiler  # noqa: F401,E402
+from . import autotuner  # noqa: F401,E402

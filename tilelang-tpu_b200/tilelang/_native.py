@@ -16,6 +16,7 @@ _PKG_ROOT = Path(__file__).resolve().parent.parent
 DEFAULT_LIB = _PKG_ROOT / "lib" / "libtl_b200.so"
 
 TL_F32, TL_F16, TL_BF16, TL_E4M3, TL_I32, TL_U32, TL_I16 = range(7)
+ABI_VERSION = 100          # TL_B200_VERSION of include/tl_b200.h
 
 # name -> (restype, argtypes).  Kept in declaration order of include/tl_b200.h.
 PROTOTYPES = {

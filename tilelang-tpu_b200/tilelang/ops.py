@@ -246,7 +246,7 @@ def selftest_bounded_wait(budget_us: int = 1000) -> int:
                    "tl_b200_selftest_bounded_wait")
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, transpose_b: bool = False) -> int:
+def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, transpose_b: bool = False, tile_n: int | None = None) -> int:
     """c = a @ b (b is (K, N)) or a @ b.T (b is (N, K), transpose_b=True); fp32 accumulation.
     fp16 / bf16 / fp32 operands, or e4m3 (the plain, un-scaled FP8 form of ppl_gemm)."""
     if a.dim() != 2 or b.dim() != 2 or c.dim() != 2:
@@ -268,8 +268,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, transpose_b: bool = 
     if a.dtype not in (torch.float16, torch.bfloat16, torch.float32, f8):
         raise ValueError(f"gemm: unsupported dtype {a.dtype}")
     s = _prepare(a, b, c)
-    return N.check(N.load().tl_b200_gemm(_ptr(a), _ptr(b), _ptr(c), m, n, k, 1 if transpose_b else 0,
-                                        dtype_code(a.dtype), dtype_code(c.dtype), s), "tl_b200_gemm")
+    if tile_n is None:                      # a choice the tuner stored for this shape, else the library's own rule
+        from .cache import tile_choice
+        tuned = tile_choice("gemm", m=m, n=n, k=k, dtype=str(a.dtype), transpose_b=bool(transpose_b))
+        tile_n = int(tuned["tile_n"]) if tuned else 0
+    return N.check(N.load().tl_b200_gemm_tiled(_ptr(a), _ptr(b), _ptr(c), m, n, k, 1 if transpose_b else 0,
+                                              dtype_code(a.dtype), dtype_code(c.dtype), int(tile_n), s), "tl_b200_gemm")
 
 
 def mlp_gate_up(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, out: torch.Tensor) -> int:

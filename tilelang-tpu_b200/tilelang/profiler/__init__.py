@@ -65,6 +65,20 @@ class Profiler:
         ins = self._inputs()
         return (func or self.adapter)(*ins)
 
+    def assert_allclose(self, reference_program: Callable, atol: float = 1e-2, rtol: float = 1e-2,
+                        max_mismatched_ratio: float = 0.01):
+        """Run the kernel and `reference_program(*inputs)` (the parameters that are not outputs, in order) and
+        compare every output (profiler/__init__.py:76-122)."""
+        ins = self._inputs()
+        self.adapter(*ins)
+        torch.cuda.synchronize()
+        ref = reference_program(*[t for i, t in enumerate(ins) if i not in self.result_idx])
+        ref = list(ref) if isinstance(ref, (tuple, list)) else [ref]
+        if len(ref) != len(self.result_idx):
+            raise ValueError(f"the reference returned {len(ref)} tensors for {len(self.result_idx)} outputs")
+        for i, r in zip(self.result_idx, ref):
+            assert_allclose(ins[i], r, rtol=rtol, atol=atol, max_mismatched_ratio=max_mismatched_ratio)
+
     def assert_consistent(self, repeat: int = 10):
         """Run-to-run determinism: outputs must be bit-identical (profiler/__init__.py:124-141)."""
         ins = self._inputs()
