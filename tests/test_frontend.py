@@ -530,3 +530,25 @@ def test_autotuner_interface_rejects_unrunnable_configs_on_cpu():
     if not torch.cuda.is_available():
         with pytest.raises(RuntimeError, match="no configuration"):     # timing needs the GPU: there is no CPU path
             tuner.run(warmup=1, rep=1)
+
+
+def test_matmul_with_other_addressing_goes_to_the_executor():
+    """Same op order as the matmul program, but every block reads the FIRST row block of A: not C = A B."""
+    M = N = K = 64
+
+    @T.prim_func
+    def not_matmul(A: T.Tensor((M, K), "float16"), B: T.Tensor((K, N), "float16"), C: T.Tensor((M, N), "float16")):
+        with T.Kernel(N // 32, M // 32, is_cpu=True) as (bx, by):
+            a_t = T.alloc_shared((32, 32), "float16")
+            b_t = T.alloc_shared((32, 32), "float16")
+            c_t = T.alloc_shared((32, 32), "float32")
+            c_o = T.alloc_shared((32, 32), "float16")
+            T.ppl_fill(c_t, T.float32(0))
+            for k in T.Pipelined(K // 32, num_stages=1):
+                T.ppl_copy(A[0, k * 32], a_t)
+                T.ppl_copy(B[k * 32, bx * 32], b_t)
+                T.ppl_gemm(a_t, b_t, c_t)
+            T.ppl_copy(c_t, c_o)
+            T.ppl_copy(c_o, C[by * 32, bx * 32])
+    assert bind(not_matmul).program == "generic"
+    assert bind(matmul_program(M, N, K, 32, 32, 32)).program == "matmul"

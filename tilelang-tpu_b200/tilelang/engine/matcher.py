@@ -127,6 +127,22 @@ def _match_matmul(func: PrimFunc):
         # (which sums over all of K) is bound only where the two agree.
         return None
     _require(sorted(_grid(func)) == sorted([N // bn, M // bm]), "matmul: the grid must cover C")
+    # addressing: A[row block, k tile], B[k tile, column block] (or B[column block, k tile]), C[row block, column block]
+    kvar = ops[1].args[0]
+    ar, br, cr = cp_a.args[0], cp_b.args[0], ops[-1].args[1]
+
+    def steps(e, var, size):
+        f = e.affine() if hasattr(e, "affine") else None
+        return f is not None and f[1] == 0 and {id(v): c for v, c in f[0].items()} == {id(var): size}
+
+    b_k, b_n = (br.starts[1], br.starts[0]) if trans_b else (br.starts[0], br.starts[1])
+    if not (steps(ar.starts[1], kvar, bk) and steps(b_k, kvar, bk) and _same_expr(ar.starts[0], cr.starts[0])
+            and _same_expr(b_n, cr.starts[1]) and const_value(ar.starts[0]) is None and const_value(b_n) is None):
+        return None                     # same op order, other addressing: the tile-op executor runs it as written
+    fa, fn_ = ar.starts[0].affine(), b_n.affine()
+    if fa is None or fn_ is None or list(fa[0].values()) != [bm] or list(fn_[0].values()) != [bn] or fa[1] or fn_[1] \
+            or next(iter(fa[0])) is next(iter(fn_[0])):
+        return None
     ia, ib, ic = A.param_index, B.param_index, C.param_index
     from .. import ops as native
 
@@ -499,7 +515,45 @@ def _match_flash_attention(func: PrimFunc):
     bm = _buf(ld_q.args[1]).shape[0]
     bn = _buf(ld_k.args[1]).shape[0]
     _check_tiling(func, "flash attention", [(seq_q, bm), (seq_k, bn)])
-    scale = float(mul_scale.args[2])
+    # dataflow of the loop body (a program with these op names but other operands is not attention and goes
+    # to the tile-op executor): S = Q K^T; m = rowmax(S); alpha = exp((m_prev - m) c); P = exp((S - m) c);
+    # l = l alpha + rowsum(P); O = O alpha + P V; after the loop O / l
+    q_t, k_t, s_t = qk.args
+    (cp_prev, fill_m, rmax, sub_a, mul_a, exp_a, sub_s, mul_s, exp_s, rsum, mul_l, add_l, cast_p) = body[3:16]
+    resc = body[16]
+    v_t, o_acc = pv.args[1], pv.args[2]
+    m_prev, m_cur = _buf(cp_prev.args[1]), _buf(cp_prev.args[0])
+    alpha, l_sum = sub_a.args[0], mul_l.args[0]
+    div, cast_o = ops[-3], ops[-2]
+    flow = (q_t is _buf(ld_q.args[1]) and k_t is _buf(ld_k.args[1]) and body[1].args[0] is s_t and body[1].args[1] == 0.0
+            and fill_m.args[0] is m_cur and fill_m.args[1] == -math.inf and rmax.args[0] is s_t and rmax.args[1] is m_cur
+            and sub_a.args[1] is m_prev and sub_a.args[2] is m_cur and mul_a.args[0] is alpha and mul_a.args[1] is alpha
+            and exp_a.args[0] is alpha
+            and sub_s.args[0] is s_t and sub_s.args[1] is s_t and sub_s.args[2] is m_cur
+            and mul_s.args[0] is s_t and mul_s.args[1] is s_t and exp_s.args[0] is s_t
+            and rsum.args[0] is s_t and mul_l.args[1] is l_sum and mul_l.args[2] is alpha
+            and add_l.args[0] is l_sum and add_l.args[1] is l_sum and add_l.args[2] is rsum.args[1]
+            and _buf(cast_p.args[0]) is s_t and pv.args[0] is _buf(cast_p.args[1])
+            and resc.args[0] is o_acc and resc.args[1] is o_acc and resc.args[2] is alpha
+            and v_t is _buf(ld_v.args[1])
+            and div.args[0] is o_acc and div.args[1] is o_acc and div.args[2] is l_sum
+            and _buf(cast_o.args[0]) is o_acc and _buf(store.args[0]) is _buf(cast_o.args[1]))
+    if not flow:
+        return None
+    _require(_close(float(mul_a.args[2]), float(mul_s.args[2])), "flash attention: one softmax scale for the row maxima and the scores")
+    scale = float(mul_s.args[2])
+    # tensor addressing: Q[bz, bx*bm : +bm, by, :], K/V[bz, k*bn : +bn, by, :], Output like Q
+    qr, kr, vr, orr = ld_q.args[0], ld_k.args[0], ld_v.args[0], store.args[1]
+    kvar = loop.args[0]
+    bx = qr.starts[1].affine()
+    _require(bx is not None and len(bx[0]) == 1 and bx[1] == 0 and list(bx[0].values()) == [bm],
+             "flash attention: the query block must start at bx * block_M")
+    bxv = next(iter(bx[0]))
+    ka = kr.starts[1].affine()
+    _require(ka is not None and ka[1] == 0 and {id(v): c for v, c in ka[0].items()} == {id(kvar): bn}
+             and _same_expr(kr.starts[1], vr.starts[1]), "flash attention: K and V tiles must start at k * block_N")
+    _require(all(_same_expr(qr.starts[i], r.starts[i]) for r in (kr, vr, orr) for i in (0, 2))
+             and _same_expr(qr.starts[1], orr.starts[1]), "flash attention: Q, K, V and Output must address the same batch entry and head")
     extent = loop.args[1]
     full = -(-seq_k // bn)
     if const_value(extent) is not None:
@@ -508,7 +562,17 @@ def _match_flash_attention(func: PrimFunc):
     else:
         # min(ceil(S/bn), ceil((bx+1)*bm / bn)): the reference's shortened causal loop; it does
         # NOT mask inside the last tile, so a query sees every key of that tile.
-        _require(isinstance(extent, Call) and extent.fn == "min", "flash attention: unrecognised KV loop extent")
+        _require(isinstance(extent, Call) and extent.fn == "min" and len(extent.args) == 2,
+                 "flash attention: unrecognised KV loop extent")
+        consts = [a for a in extent.args if const_value(a) is not None]
+        calls = [a for a in extent.args if isinstance(a, Call) and a.fn == "ceildiv"]
+        _require(len(consts) == 1 and const_value(consts[0]) == full and len(calls) == 1,
+                 "flash attention: the causal KV loop must be min(ceil(S / block_N), ceil((bx + 1) * block_M / block_N))")
+        num, den = calls[0].args
+        na = num.affine()
+        _require(const_value(den) == bn and na is not None and na[1] == bm
+                 and {id(v): c for v, c in na[0].items()} == {id(bxv): bm},
+                 "flash attention: the causal KV loop must be min(ceil(S / block_N), ceil((bx + 1) * block_M / block_N))")
         mode, diag = "block", 0
     idx = [b.param_index for b in (Q, K, V, O)]
     from .. import ops as native
@@ -539,6 +603,29 @@ def _match_mla_decode(func: PrimFunc):
     if not all(_is_param(b, func) for b in (Q, Qpe, KV, Kpe, Out)):
         return None
     _require(gemms[2].args[1] is gemms[0].args[1], "mla decode: V must be the latent KV tile")
+    # dataflow: S = Q KV^T + Q_pe K_pe^T (two products summed), P = exp(S c - m c) cast into the A operand of
+    # O += P KV, O rescaled by exp(m_prev c - m c), O / l at the end; everything else goes to the executor
+    body = ops[loop_i + 1:n.index("loop.end")]
+    bn_ = _names(body)
+    q_t, kv_t, s_t = gemms[0].args
+    qpe_t, kpe_t, s_pe = gemms[1].args
+    p_t, _, o_acc = gemms[2].args
+    adds = [o for o in body if o.name == "ppl.add"]
+    exps = [o for o in body if o.name == "ppl.exp"]
+    rmax = next((o for o in body if o.name == "ppl.reduce_max"), None)
+    rsum = next((o for o in body if o.name == "ppl.reduce_sum"), None)
+    casts = [o for o in body if o.name == "ppl.copy" and _buf(o.args[1]) is p_t]
+    div = ops[-3]
+    flow = (bn_.count("ppl.exp") == 2 and rmax is not None and rsum is not None and len(adds) == 2 and len(casts) == 1
+            and q_t is _buf(ops[0].args[1]) and qpe_t is _buf(ops[1].args[1])
+            and kv_t is _buf(ld_kv.args[1]) and kpe_t is _buf(ld_kpe.args[1])
+            and adds[0].args[0] is s_t and {id(adds[0].args[1]), id(adds[0].args[2])} == {id(s_t), id(s_pe)}
+            and rmax.args[0] is s_t and exps[1].args[0] is s_t and rsum.args[0] is s_t and _buf(casts[0].args[0]) is s_t
+            and adds[1].args[2] is rsum.args[1]
+            and div.args[0] is o_acc and div.args[1] is o_acc and div.args[2] is adds[1].args[0]
+            and any(o.name == "ppl.mul" and o.args[0] is o_acc and o.args[1] is o_acc and o.args[2] is exps[0].args[0] for o in body))
+    if not flow:
+        return None
     b, h, one, dim = Q.shape
     pe = Qpe.shape[-1]
     s = KV.shape[1]
