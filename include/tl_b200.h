@@ -259,6 +259,48 @@ int tl_b200_mla_decode_paged_noalloc(const void* q, const void* kv_cache, const 
                                      int64_t max_pages_per_seq, int64_t num_pages, float softmax_scale,
                                      int q_dtype, void* stream);
 
+/* ---- fused row-local tile programs ------------------------------------------------
+ * Runs a whole `ppl_*` program whose ops all work row by row - ppl_copy (load, store, cast), ppl_fill,
+ * ppl_add / subtract / mul / div with a full, (M,1) or (1,N) second operand, ppl_mul_C / add_C, ppl_exp2,
+ * ppl_sigmoid, ppl_rsqrt, ppl_reduce_sum / max, ppl_rope_add (customize.py:136-603) - in ONE launch: a row of
+ * every tile lives in registers, every global element is read once and written once.  The reference executes
+ * such a program as one runtime call per tile op (codegen_ppl.cc:879-1906).  The host lowers the program to
+ * instructions of a small accumulator machine: A is the accumulator row, T[0..n) are tile registers
+ * (n = tl_b200_tile_program_registers(max_width)), S[0..8) are per-row scalars ((M,1) tiles).  Results are
+ * rounded to `dtype` where an instruction names one (a tile's element type), as the reference's tile ops do.
+ *   LD_A / ST_A   A <-> param[base + coef . block + row * row_stride + col], col < width, cast from/to dtype
+ *                 (vec != 0 promises 16-byte alignment of every chunk of 8 elements)
+ *   LD_S / ST_S   S[r0] <-> param[base + coef . block + row * row_stride]
+ *   MOV_A_T  A = T[r0]           MOV_T_A  T[r0] = round(A)        BIN_A_T  A = A (sub) T[r0]
+ *   BIN_A_S  A = A (sub) S[r0]   BIN_A_I  A = A (sub) imm         UN_A     A = f_sub(A)
+ *   FILL_A   A = imm             ROUND_A  A = round(A)            BCAST_A_S A = S[r0]
+ *   RED_S    S[r0] = round(sum (sub 0) or max (sub 1) of A[col < width])
+ *   MOV_S_I  S[r0] = imm         MOV_S_S  S[r0] = round(S[r1])    BIN_S_S  S[r0] = round(S[r1] (sub) S[r2])
+ *   BIN_S_I  S[r0] = round(S[r1] (sub) imm)                       UN_S     S[r0] = round(f_sub(S[r1]))
+ *   ROPE_A   A[2i] = T[r0][2i] + T[r1][2i+1];  A[2i+1] = T[r2][2i+1] + T[r3][2i]
+ * binary sub: 0 add, 1 sub, 2 mul, 3 div, 4 max; unary sub: 0 sigmoid, 1 exp, 2 rsqrt.
+ * `instrs` and `params` are HOST arrays (params holds device pointers); blocks are numbered x fastest.      */
+#define TL_B200_VM_MAX_INSTR 96
+#define TL_B200_VM_MAX_PARAMS 16
+enum {
+  TL_VM_LD_A = 0, TL_VM_ST_A, TL_VM_LD_S, TL_VM_ST_S, TL_VM_MOV_A_T, TL_VM_MOV_T_A, TL_VM_BIN_A_T, TL_VM_BIN_A_S,
+  TL_VM_BIN_A_I, TL_VM_UN_A, TL_VM_FILL_A, TL_VM_ROUND_A, TL_VM_BCAST_A_S, TL_VM_RED_S, TL_VM_MOV_S_I, TL_VM_MOV_S_S,
+  TL_VM_BIN_S_S, TL_VM_BIN_S_I, TL_VM_UN_S, TL_VM_ROPE_A, TL_VM_OPCODES
+};
+typedef struct {
+  int32_t op, sub;
+  int32_t r0, r1, r2, r3;
+  int32_t dtype, width;
+  int32_t param, row_stride;
+  int32_t vec;
+  float imm;
+  int64_t base;
+  int64_t coef[3];
+} tl_b200_vm_instr;
+int tl_b200_tile_program_registers(int64_t max_width);
+int tl_b200_tile_program(const tl_b200_vm_instr* instrs, int n_instr, const void* const* params, int n_params,
+                         int grid_x, int grid_y, int grid_z, int rows_per_block, int64_t max_width, void* stream);
+
 /* ---- generic entry point ---------------------------------------------------------
  * One symbol with the shape of the reference's generated
  *     extern "C" int tilelang_tpu_run(void** args)

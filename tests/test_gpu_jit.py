@@ -166,8 +166,8 @@ def test_a_call_that_reads_what_an_earlier_call_still_writes_waits_for_it(cuda_d
     """Asynchronous (pinned) calls chained through a host tensor: the second program's upload of `mid` is ordered
     after the first program's download into it, across two adapters."""
     k1 = tilelang.compile(rms_norm_program(256, 512, 32, eps=1e-6), out_idx=-1, target="b200")
-    k2 = tilelang.compile(rms_norm_program(256, 512, 32, eps=1e-6), out_idx=-1, target="b200")
-    assert k1 is not k2
+    k2 = tilelang.compile(rms_norm_program(256, 512, 64, eps=1e-6), out_idx=-1, target="b200")     # another program: another adapter
+    assert k1 is not k2 and k1.adapter is not k2.adapter
     a = torch.randn(256, 512, generator=gen(12)).bfloat16().pin_memory()
     mid = torch.zeros(256, 512, dtype=torch.bfloat16).pin_memory()
     out = torch.zeros(256, 512, dtype=torch.bfloat16).pin_memory()

@@ -8,8 +8,10 @@
 //
 // Persistent warp-specialised kernel: TMA ring (6 stages of 128x128 A and B bytes, 128-byte
 // swizzle) -> tcgen05.mma kind::f8f6f4 into one of four partial accumulators in tensor memory ->
-// two epilogue warpgroups (64 columns each) pull the partial with tcgen05.ld and do the scaled
-// accumulation in registers while the tensor core already fills the next partials.
+// eight promotion warps (64 columns of 32 rows each) pull the partial with tcgen05.ld and do the scaled
+// accumulation in registers while the tensor core already fills the next partials.  The promotion is a
+// dependent chain per warp (wait for the partial, load, hand the buffer back, multiply in), so a partial is
+// fetched with a single 64-column load: one round trip to tensor memory per K block.
 #include "sm100.cuh"
 
 namespace tl {
@@ -17,11 +19,14 @@ using namespace sm100;
 
 constexpr int kF8BM = 128, kF8BN = 128, kF8BK = 128;
 constexpr int kF8Stages = 6;
-constexpr int kF8Threads = 384;       // warp 0 TMA, warp 1 MMA, warp 2 TMEM alloc, warps 4-11 promotion/epilogue
+constexpr int kF8Threads = 320;       // warp 0 TMEM alloc + TMA, warp 1 MMA, warps 2-9 promotion/epilogue
+constexpr int kF8PromoWarp0 = 2;
 constexpr int kF8StageBytes = (kF8BM + kF8BN) * kF8BK;
 constexpr int kF8Smem = kF8Stages * kF8StageBytes + 1024 + 256;
 constexpr int kF8Acc = 4;             // partial accumulators in tensor memory (4 x 128 columns)
 constexpr int kF8TmemCols = kF8Acc * kF8BN;
+
+__device__ __forceinline__ bool aligned16_dev(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct F8Params {
   void* c;
@@ -67,7 +72,7 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     prefetch_tensormap(&tm_a);
     prefetch_tensormap(&tm_b);
   }
-  if (warp == 2) {
+  if (warp == 0) {
     tmem_alloc(smem_u32(tmem_slot), kF8TmemCols);
     tmem_relinquish();
   }
@@ -133,9 +138,9 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
         }
       }
     }
-  } else if (warp >= 4) {
-    const int wg = (warp - 4) / 4;            // column half
-    const int quarter = warp % 4;
+  } else if (warp >= kF8PromoWarp0) {
+    const int wg = (warp - kF8PromoWarp0) / 4;   // column half
+    const int quarter = warp % 4;             // the tensor-memory lanes a warp may touch follow from warp % 4
     const int r = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     TOut* c = reinterpret_cast<TOut*>(p.c);
@@ -152,30 +157,50 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
 #pragma unroll
       for (int j = 0; j < 32; ++j) acc2[j] = make_float2(0.f, 0.f);
       float* acc = reinterpret_cast<float*>(acc2);
-      float scale_next = __ldg(sa_row) * __ldg(sb_row);
-      for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
-        const uint32_t buf = it % kF8Acc;
-        const float scale = scale_next;
-        if (kb + 1 < p.kblocks) scale_next = __ldg(sa_row + kb + 1) * __ldg(sb_row + kb + 1);
-        ok = mbar_wait(bar_tfull + 8 * buf, (it / kF8Acc) & 1, abort_flag);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after_sync();
-        const uint32_t t_addr = tmem_base + buf * kF8BN + wg * 64 + lane_off;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_addr + h * 32, v);
-          tmem_ld_wait();
-          const float2 sc2 = make_float2(scale, scale);
-#pragma unroll
-          for (int j = 0; j < 32; j += 2)
-            acc2[h * 16 + j / 2] = fma2(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), sc2,
-                                        acc2[h * 16 + j / 2]);
+      // Per K block: wait for the partial, ONE 64-column load (a single round trip to tensor memory), hand the
+      // buffer back to the tensor core, then multiply the partial in.  The scales of a row are fetched four K
+      // blocks at a time (16-byte loads, one group ahead): every thread reads its own row of `sa`, so each scalar
+      // load would cost a warp 32 sectors.
+      const bool quads = (p.kblocks % 4 == 0) && aligned16_dev(p.sa) && aligned16_dev(p.sb);
+      auto scales_at = [&](int kb) {
+        float4 a, b;
+        if (quads) {
+          a = __ldg(reinterpret_cast<const float4*>(sa_row + kb));
+          b = __ldg(reinterpret_cast<const float4*>(sb_row + kb));
+        } else {
+          const int n = p.kblocks - kb;
+          a = make_float4(__ldg(sa_row + kb), n > 1 ? __ldg(sa_row + kb + 1) : 0.f, n > 2 ? __ldg(sa_row + kb + 2) : 0.f,
+                          n > 3 ? __ldg(sa_row + kb + 3) : 0.f);
+          b = make_float4(__ldg(sb_row + kb), n > 1 ? __ldg(sb_row + kb + 1) : 0.f, n > 2 ? __ldg(sb_row + kb + 2) : 0.f,
+                          n > 3 ? __ldg(sb_row + kb + 3) : 0.f);
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+        return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w);
+      };
+      float4 sc_next = scales_at(0);
+      for (int kb0 = 0; kb0 < p.kblocks && ok; kb0 += 4) {
+        const float4 sc = sc_next;
+        if (kb0 + 4 < p.kblocks) sc_next = scales_at(kb0 + 4);
+        const float sc_of[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (kb0 + q >= p.kblocks) break;
+          const uint32_t buf = it % kF8Acc;
+          ok = mbar_wait(bar_tfull + 8 * buf, (it / kF8Acc) & 1, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after_sync();
+          uint32_t v[64];
+          tmem_ld_32x64(tmem_base + buf * kF8BN + wg * 64 + lane_off, v);
+          tmem_ld_wait_for(v);
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+          const float2 sc2 = make_float2(sc_of[q], sc_of[q]);
+#pragma unroll
+          for (int j = 0; j < 64; j += 2)
+            acc2[j / 2] = fma2(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), sc2, acc2[j / 2]);
+          ++it;
+        }
       }
       if (!ok) break;
       const int col0 = tn * kF8BN + wg * 64;

@@ -53,6 +53,8 @@ PROTOTYPES = {
     "tl_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_void_p]),
     "tl_b200_gemm_tiled": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "tl_b200_mlp_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "tl_b200_tile_program_registers": (c_int, [c_int64]),
+    "tl_b200_tile_program": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int64, c_void_p]),
     "tl_b200_run": (c_int, [c_int, ctypes.POINTER(c_void_p), ctypes.POINTER(c_int64), c_void_p]),
 }
 

@@ -61,7 +61,9 @@ def validate(func: PrimFunc) -> None:
         for a in op.args:
             if isinstance(a, (Buffer, Region)):
                 b = _buf(a)
-                _need(1 <= len(b.shape) <= 2, f"{op.name}: {b.name} has rank {len(b.shape)}; tiles and tensors of rank 1 or 2 only")
+                if b.scope == "global" and op.name == "ppl.copy":
+                    continue                       # a window of a tensor of any rank; checked against the tile when it is addressed
+                _need(1 <= len(b.shape) <= 2, f"{op.name}: {b.name} has rank {len(b.shape)}; tiles of rank 1 or 2 only")
         if op.name == "ppl.gemm":
             a, b, c = op.args
             _need(not op.attrs["transpose_A"], "ppl.gemm: transpose_A is not supported (the reference's code generator ignores it)")
@@ -126,6 +128,38 @@ def build(func: PrimFunc) -> Callable[..., int]:
             v = t[tuple(idx)]
             return v if v.dim() == 2 else v.reshape(1, -1) if v.is_contiguous() else v.unsqueeze(0)
 
+        def copy_views(src, dst, env):
+            """2-D views of the two sides of a ppl.copy.  A window of a tensor of rank 3 or 4 (or any window that is
+            not a plain 2-D slice) is addressed like the fused path does: evenly strided rows, contiguous columns."""
+            def plain(x):
+                return isinstance(x, Buffer) or len(x.buffer.shape) <= 2
+            if plain(src) and plain(dst):
+                return view(src, env), view(dst, env)
+            from .fuser import NotFusable, _window
+            out = []
+            for x, other in ((src, dst), (dst, src)):
+                if plain(x):
+                    out.append(view(x, env))
+                    continue
+                ob = _buf(other)
+                shape = tuple(ob.shape) if len(ob.shape) == 2 else (1, int(ob.shape[0]))
+                if ob.scope == "global":            # tensor to tensor: rows x last extent of this window
+                    ext = [1 if e is None else int(e) for e in x.extents]
+                    width = ext[-1]
+                    rows = 1
+                    for e in ext[:-1]:
+                        rows *= e
+                    shape = (rows, width)
+                vars_ = [v for v in env]
+                try:
+                    base, coef, row_stride = _window(x, shape[0], shape[1], {}, vars_)
+                except NotFusable as why:
+                    raise InterpreterError(f"ppl.copy: {why}") from None
+                off = base + sum(c * int(env[v]) for c, v in zip(coef, vars_))
+                t = tensor_of(x.buffer)
+                out.append(t.as_strided(shape, (row_stride if shape[0] > 1 else max(shape[1], 1), 1), t.storage_offset() + off))
+            return out[0], out[1]
+
         def execute(lo: int, hi: int, env: dict) -> int:
             i = lo
             while i < hi:
@@ -149,7 +183,7 @@ def build(func: PrimFunc) -> Callable[..., int]:
         def one(op, env) -> int:
             n, a = op.name, op.args
             if n == "ppl.copy":
-                src, dst = view(a[0], env), view(a[1], env)
+                src, dst = copy_views(a[0], a[1], env)
                 if src.numel() != dst.numel():
                     raise ValueError(f"ppl.copy: {a[0]!r} and {a[1]!r} differ in size")
                 if src.shape != dst.shape:             # e.g. a (M, 1) column into a rank-1 tensor

@@ -675,15 +675,22 @@ def bind(func: PrimFunc) -> BoundKernel:
         bound = m(func)
         if bound is not None:
             return bound
-    # not one of the fused programs: run it tile op by tile op on the GPU (engine/interpreter.py)
-    from . import interpreter
+    # not one of the hand-fused programs.  A row-local program runs as ONE launch of the tile-program kernel
+    # (engine/fuser.py); anything else is run tile op by tile op on the GPU (engine/interpreter.py)
+    from . import fuser, interpreter
+    fused = fuser.build(func)
+    if fused is not None:
+        return BoundKernel("generic", "tl_b200_tile_program (one launch)", fused,
+                           dict(ops=len(func.ops), instructions=fused.instructions, grid=[int(const_value(g)) for g in func.grid],
+                                fused=True), full_outputs=False)
     try:
         run = interpreter.build(func)
     except interpreter.InterpreterError as why:
         reason = str(why)
     else:
         return BoundKernel("generic", "tile-op executor (one tl_b200_* launch per op)", run,
-                           dict(ops=len(func.ops), grid=[int(const_value(g)) for g in func.grid]), full_outputs=False)
+                           dict(ops=len(func.ops), grid=[int(const_value(g)) for g in func.grid], fused=False,
+                                why_not_fused=fuser.build.last_reason), full_outputs=False)
     raise UnsupportedProgram(
         f"the generic tile-op executor cannot run it either ({reason}); "
         "this ppl_* program does not match any kernel of the b200 library (matmul, rmsnorm, "
