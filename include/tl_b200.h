@@ -240,6 +240,18 @@ int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, const float* k
                              int q_dtype, int cache_dtype, void* workspace, int64_t workspace_bytes,
                              void* stream);
 
+/* The paged form with several query tokens per sequence and several kv heads
+ * (examples/deepseek_mla/example_mla_decode_paged.py:99-256): q [batch, s_q, h_q, d], kv_cache
+ * [num_pages, page_size, h_kv, d] of the same 16-bit type, out [batch, s_q, h_q, dv]; head h reads kv head
+ * h / (h_q / h_kv); query token i of a sequence sees its keys up to len - s_q + i (the example's causal rule,
+ * :266-274).  d 576, dv 512, s_q * (h_q / h_kv) <= 128 (and h_q / h_kv a multiple of 8 when s_q > 1),
+ * page_size % 64 == 0 run on tcgen05 tensor cores (also what tl_b200_mla_decode_paged and
+ * tl_b200_mla_decode_dense use for 16-bit caches at that shape); other shapes use the FMA kernel.       */
+int tl_b200_mla_decode_paged_gqa(const void* q, const void* kv_cache, const int32_t* block_table,
+                                 const int32_t* cache_seqlens, void* out, int64_t batch, int64_t s_q, int64_t h_q,
+                                 int64_t h_kv, int64_t d, int64_t dv, int64_t page_size, int64_t max_pages_per_seq,
+                                 int64_t num_pages, float softmax_scale, int dtype, void* stream);
+
 /* Same computation as tl_b200_mla_decode_paged on its tensor-core configuration (e4m3 cache with
  * per-token scales, d 576, dv 512, heads <= 128, page_size % 64 == 0), for callers that must not
  * allocate device memory when they decode (a pool already handed out to the KV cache, code that

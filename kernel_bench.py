@@ -225,6 +225,55 @@ def small_ops(dev, rank, world, peaks, rows=8192, cols=4096):
     return out
 
 
+def tile_program(dev, rank, world, peaks, rows=8192, cols=4096):
+    """A row-local `ppl_*` program that no hand-written kernel matches, y = exp(x) * rsqrt(mean(x^2) + 1) + 0.5 on
+    bf16 [rows, cols] in fp32 tiles (13 tile ops), run as ONE launch of the tile-program kernel; beside it the fused
+    RMSNorm kernel on the same tensor (same bytes) and the op-by-op executor (one launch per tile op)."""
+    import tilelang.language as T
+    from tilelang.engine import fuser, interpreter
+    bm = 32
+
+    @T.prim_func
+    def program(X: T.Tensor((rows, cols), "bfloat16"), Y: T.Tensor((rows, cols), "bfloat16")):
+        with T.Kernel(rows // bm, is_cpu=True) as (bx,):
+            x16 = T.alloc_shared((bm, cols), "bfloat16")
+            x = T.alloc_shared((bm, cols), "float32")
+            sq = T.alloc_shared((bm, cols), "float32")
+            acc = T.alloc_shared((bm, 1), "float32")
+            w0 = T.alloc_shared((bm, cols), "float32")
+            coeff = T.alloc_shared((64, 32), "float32")
+            table = T.alloc_shared((64, 192), "float32")
+            T.ppl_copy(X[bx * bm, 0], x16)
+            T.ppl_copy(x16, x)
+            T.ppl_mul(sq, x, x)
+            T.ppl_reduce_sum(sq, acc, dim=1)
+            T.ppl_mul_C(acc, acc, T.float32(1.0 / cols))
+            T.ppl_add_C(acc, acc, T.float32(1.0))
+            T.ppl_rsqrt(acc, acc)
+            T.ppl_exp2(x, w0, w0, coeff, table)
+            T.ppl_mul(x, x, acc)
+            T.ppl_add_C(x, x, T.float32(0.5))
+            T.ppl_copy(x, x16)
+            T.ppl_copy(x16, Y[bx * bm, 0])
+
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = torch.randn(rows, cols, generator=g, device=dev).bfloat16()
+    y = torch.empty_like(x)
+    fused = fuser.build(program)
+    ms = _time(lambda: fused(x, y), 1, reps=10)
+    ms_norm = _time(lambda: ops.rmsnorm(x, y, None, 1e-6), 1, reps=10)
+    by_op = interpreter.build(program)
+    small = rows // bm <= 64
+    ms_ops = _time(lambda: by_op(x, y), 1, reps=1, warmup=1) if small else None
+    e = _entry("tile_vm_kernel", f"13-op row-local program on bf16 [{rows}, {cols}], {fused.instructions} instructions", 2.0 * x.numel() * 2,
+               1e9, "GB/s", ms, ms, peaks["hbm_gbs"], peaks["note"], "none", 1)
+    e["ms_fused_rmsnorm_same_tensor"] = ms_norm
+    e["ratio_to_fused_rmsnorm"] = ms / ms_norm
+    if ms_ops is not None:
+        e["ms_op_by_op"] = ms_ops
+    return e
+
+
 def run_all(dev, rank, world, peaks):
     out = []
     plain_fp8 = None
@@ -257,6 +306,7 @@ SMALL = {      # reduced shapes for profiler captures: inputs above the 126 MB L
     "flash_attn": dict(b=2, s=4096, h=16, d=128),
     "mla_decode": dict(batch=32),
     "small_ops": dict(rows=2048),
+    "tile_program": dict(rows=2048),
 }
 
 

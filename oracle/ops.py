@@ -286,3 +286,29 @@ def mla_decode_paged(q: torch.Tensor, kv_pages: torch.Tensor, kv_scale: torch.Te
         w = torch.softmax(w, dim=-1, dtype=torch.float32)
         out[i] = (w @ kf[:, :dv]).to(out.dtype)
     return out
+
+
+def mla_decode_paged_gqa(q: torch.Tensor, kv_pages: torch.Tensor, block_table: torch.Tensor, cache_seqlens: torch.Tensor,
+                         dv: int) -> torch.Tensor:
+    """Paged decode with several query tokens per sequence and several kv heads: q (b, s_q, h_q, d), kv_pages
+    (num_pages, page, h_kv, d), out (b, s_q, h_q, dv).  Follows `run_torch_mla` / `scaled_dot_product_attention` of
+    examples/deepseek_mla/example_mla_decode_paged.py:259-308 with causal=True: kv heads repeated h_q / h_kv times,
+    scale 1/sqrt(d), mask tril(diagonal = s_k - s_q) (query token i sees keys up to len - s_q + i), V = first dv
+    columns; the keys of a sequence are gathered through its page list."""
+    b, s_q, h_q, d = q.shape
+    page, h_kv = kv_pages.shape[1], kv_pages.shape[2]
+    out = torch.zeros(b, s_q, h_q, dv, dtype=q.dtype)
+    for i in range(b):
+        n = int(cache_seqlens[i])
+        if n == 0:
+            continue
+        npg = -(-n // page)
+        k = kv_pages[block_table[i, :npg].long()].float().reshape(npg * page, h_kv, d)[:n]       # (n, h_kv, d)
+        k = k.transpose(0, 1).repeat_interleave(h_q // h_kv, dim=0)                              # (h_q, n, d)
+        w = q[i].float().transpose(0, 1) @ k.transpose(-2, -1) / math.sqrt(d)                    # (h_q, s_q, n)
+        keep = torch.ones(s_q, n, dtype=torch.bool).tril(diagonal=n - s_q)
+        w = w.masked_fill(~keep, float("-inf"))
+        w = torch.softmax(w, dim=-1, dtype=torch.float32)
+        w = torch.nan_to_num(w)                        # a query token that sees no key at all gives zeros
+        out[i] = (w @ k[..., :dv]).transpose(0, 1).to(q.dtype)
+    return out

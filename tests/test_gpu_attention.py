@@ -150,6 +150,23 @@ def test_mla_dense_golden_and_fp16(cuda_device):
     assert torch.allclose(outh.cpu().float(), ref.float(), **TOL16)
 
 
+@pytest.mark.parametrize("dtype", [BF, torch.float16])
+@pytest.mark.parametrize("batch,heads,seq", [(4, 128, 777), (2, 64, 64), (1, 128, 4096), (3, 20, 130)])
+def test_mla_dense_program_at_the_deepseek_shape_runs_on_tensor_cores(cuda_device, dtype, batch, heads, seq):
+    """The reference's MLA program (tpu_demo/ppl/deepseek_mla/mla_decode.py:9-121: Q, Q_pe, KV, K_pe as four tensors,
+    dense cache) with latent 512 + rope 64: the tcgen05 kernel, the cache addressed without a page table."""
+    g = gen(batch * 7 + heads)
+    q = torch.randn(batch, heads, 1, 512, generator=g).to(dtype)
+    qpe = torch.randn(batch, heads, 1, 64, generator=g).to(dtype)
+    kv = torch.randn(batch, seq, 1, 512, generator=g).to(dtype)
+    kpe = torch.randn(batch, seq, 1, 64, generator=g).to(dtype)
+    out = torch.full_like(q, float("nan"), device=cuda_device)
+    assert ops.mla_decode_dense(q.to(cuda_device), qpe.to(cuda_device), kv.to(cuda_device), kpe.to(cuda_device), out) == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    assert torch.allclose(out.cpu().float(), O.mla_decode_dense(q, qpe, kv, kpe).float(), **TOL16)
+
+
 def test_argument_errors(cuda_device):
     q = torch.zeros(1, 128, 2, 64, dtype=BF, device=cuda_device)
     with pytest.raises(ValueError):

@@ -72,6 +72,68 @@ def test_tensor_core_kernel_fp16_queries_and_empty_sequence(cuda_device):
     assert (out[1] == 0).all()
 
 
+def paged_16bit(batch, heads, lens, page, dtype, seed, d=576):
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.tensor(lens, dtype=torch.int32)
+    pages = (lens + page - 1) // page
+    total = int(pages.sum()) + 3
+    perm = torch.randperm(total, generator=g).to(torch.int32)
+    table = torch.zeros(batch, int(pages.max()) + 1, dtype=torch.int32)
+    cur = 0
+    for i in range(batch):
+        table[i, :int(pages[i])] = perm[cur:cur + int(pages[i])]
+        cur += int(pages[i])
+    cache = torch.randn(total, page, d, generator=g).to(dtype)
+    q = torch.randn(batch, heads, d, generator=g).to(dtype)
+    return dict(q=q, kv_cache=cache, kv_scale=None, block_table=table, cache_seqlens=lens, dv=512, softmax_scale=d ** -0.5)
+
+
+@pytest.mark.parametrize("dtype", [BF, HF])
+@pytest.mark.parametrize("heads,page,lens", [(128, 64, (1, 64, 65, 500, 1000, 2048)), (16, 64, (300, 77, 0)),
+                                             (128, 128, (129, 1024, 640)), (100, 64, (1500,))])
+def test_16bit_cache_on_tensor_cores(cuda_device, dtype, heads, page, lens):
+    """bf16 / fp16 latent caches at the DeepSeek shape (d 576, dv 512) run the tcgen05 kernel of mla_f16.cu (layout of
+    examples/deepseek_mla/example_mla_decode_paged.py:20-97): oracle parity at the stated tolerance, every length class
+    (one token, exactly one tile, a ragged tail, an empty sequence)."""
+    w = paged_16bit(len(lens), heads, lens, page, dtype, seed=heads + page)
+    out = run(w, cuda_device)
+    ref = oracle(w)
+    live = [i for i, n in enumerate(lens) if n > 0]
+    assert torch.allclose(out[live].float(), ref[live].float(), atol=2e-2, rtol=2e-2)
+    for i, n in enumerate(lens):
+        if n == 0:
+            assert (out[i] == 0).all()
+    a = run(w, cuda_device)
+    assert torch.equal(a.view(torch.int16), out.view(torch.int16))              # run-to-run determinism
+
+
+@pytest.mark.parametrize("s_q,h_q,h_kv,d,dv,page", [(1, 128, 1, 576, 512, 64), (2, 64, 2, 576, 512, 64), (4, 32, 1, 576, 512, 64),
+                                                    (3, 16, 2, 576, 512, 128), (2, 8, 2, 64, 32, 16), (3, 4, 1, 96, 64, 16)])
+def test_several_query_tokens_and_kv_heads(cuda_device, s_q, h_q, h_kv, d, dv, page):
+    """s_q > 1 and h_kv > 1 (examples/deepseek_mla/example_mla_decode_paged.py:99-256, checked there against
+    `run_torch_mla`): the DeepSeek-shaped cases run on tensor cores with the (query token, head) pairs of a kv head as
+    the rows of the MMAs, the others on the FMA kernel."""
+    g = torch.Generator().manual_seed(s_q * 100 + h_q)
+    lens = torch.tensor([300, 65, s_q, 1000][:3 if d != 576 else 4], dtype=torch.int32).clamp(max=20 * page)
+    b = lens.numel()
+    pages = (lens + page - 1) // page
+    total = int(pages.sum()) + 2
+    perm = torch.randperm(total, generator=g).to(torch.int32)
+    table = torch.zeros(b, int(pages.max()), dtype=torch.int32)
+    cur = 0
+    for i in range(b):
+        table[i, :int(pages[i])] = perm[cur:cur + int(pages[i])]
+        cur += int(pages[i])
+    cache = torch.randn(total, page, h_kv, d, generator=g).to(BF)
+    q = torch.randn(b, s_q, h_q, d, generator=g).to(BF)
+    out = torch.full((b, s_q, h_q, dv), float("nan"), dtype=BF, device=cuda_device)
+    assert ops.mla_decode_paged_gqa(q.to(cuda_device), cache.to(cuda_device), table.to(cuda_device), lens.to(cuda_device), out) == 0
+    torch.cuda.synchronize()
+    assert ops.device_status() == 0
+    ref = O.mla_decode_paged_gqa(q, cache, table, lens, dv)
+    assert torch.allclose(out.cpu().float(), ref.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_peaked_attention_rows(cuda_device):
     """A query aligned with one cached token: softmax is nearly one-hot, so the output must
     reproduce that token's value row (checks the scale folding and the two-term P split)."""

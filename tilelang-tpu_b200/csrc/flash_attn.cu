@@ -20,6 +20,7 @@
 // Everything else (other dtypes, head dims, tiny shapes) runs a one-thread-per-row FMA kernel,
 // which also serves the dense MLA decode program.
 #include "sm100.cuh"
+#include "mla_common.cuh"
 
 #include <type_traits>
 
@@ -539,6 +540,12 @@ extern "C" int tl_b200_mla_decode_dense(const void* q, const void* q_pe, const v
   if (batch == 0 || heads == 0 || dim == 0) return TL_B200_OK;
   TL_REQUIRE(q && kv && out && (pe_dim == 0 || (q_pe && k_pe)), "mla_decode_dense: null tensor pointer");
   TL_REQUIRE(seq_kv > 0, "mla_decode_dense: no keys");
+  // DeepSeek shape (latent 512 + rope 64, up to 128 heads) in a 16-bit type: the tcgen05 kernel, with the identity
+  // as its page table; Q / Q_pe and KV / K_pe stay separate tensors
+  if ((dtype == TL_BF16 || dtype == TL_F16) && dim == 512 && pe_dim == 64 && heads <= 128 && aligned16(q) && aligned16(q_pe) &&
+      aligned16(kv) && aligned16(k_pe) && aligned16(out) && batch * seq_kv < (1ll << 31))
+    return mla_f16_launch(q, q_pe, kv, k_pe, nullptr, nullptr, out, batch, 1, heads, 1, batch * seq_kv, 0, 0, 0, seq_kv,
+                          scale, dtype, (cudaStream_t)stream);
   RowAttnParams p{};
   p.q = q; p.q2 = pe_dim ? q_pe : nullptr; p.k = kv; p.k2 = pe_dim ? k_pe : nullptr; p.v = kv; p.o = out;
   // Q[b,h,1,dim], Q_pe[b,h,1,pe], KV[b,s,1,dim], K_pe[b,s,1,pe], Out[b,h,1,dim]; one shared kv head

@@ -60,4 +60,12 @@ int mla_persistent_launch(const void* q, const void* kv_cache, const float* kv_s
                           int64_t max_pages_per_seq, int64_t num_pages, float softmax_scale, int q_dtype,
                           void* workspace, cudaStream_t stream);
 
+// 16-bit caches on tcgen05 (mla_f16.cu): q [batch, s_q, h_q, 576] or split (q 512 + q_pe 64 columns); cache
+// [tokens, h_kv, 576] or split; paged (block_table, seqlens) or dense (both nullptr, dense_len tokens each).
+bool mla_f16_shape_ok(int64_t s_q, int64_t h_q, int64_t h_kv, int64_t d, int64_t dv);
+int mla_f16_launch(const void* q, const void* q_pe, const void* kv, const void* k_pe, const int32_t* block_table,
+                   const int32_t* seqlens, void* out, int64_t batch, int64_t s_q, int64_t h_q, int64_t h_kv,
+                   int64_t total_tokens, int64_t page_size, int64_t max_pages, int64_t num_pages, int64_t dense_len,
+                   float softmax_scale, int dtype, cudaStream_t stream);
+
 }  // namespace tl

@@ -489,18 +489,22 @@ struct MlaRowParams {
   void* out;
   int batch, heads, d, dv, page_size, max_pages;
   int len_cap, num_pages;
+  int s_q, h_kv;               // query tokens per sequence and kv heads (1, 1 in the single-token MLA form)
   float scale;
 };
 
 template <typename TQ, typename TC, int MAXDV>
 __global__ void __launch_bounds__(128)
 mla_rows_kernel(const MlaRowParams p) {
+  // one thread per (sequence, query token, head); q and out are [batch, s_q, heads, .], the cache [tokens, h_kv, d]
   const int idx = blockIdx.x * 128 + threadIdx.x;
-  if (idx >= p.batch * p.heads) return;
-  const int b = idx / p.heads;
+  if (idx >= p.batch * p.s_q * p.heads) return;
+  const int b = idx / (p.s_q * p.heads);
+  const int qi = (idx / p.heads) % p.s_q, kvh = (idx % p.heads) / (p.heads / p.h_kv);
   const TQ* q = (const TQ*)p.q + (int64_t)idx * p.d;
   const int* table = p.block_table + (int64_t)b * p.max_pages;
-  const int seqlen = mla_len(p.seqlens, b, p.len_cap);
+  // query token qi of s_q sees the keys up to len - s_q + qi (examples/deepseek_mla/example_mla_decode_paged.py:266-274)
+  const int seqlen = max(mla_len(p.seqlens, b, p.len_cap) - (p.s_q - 1 - qi), 0);
   float acc[MAXDV];
 #pragma unroll
   for (int i = 0; i < MAXDV; ++i) acc[i] = 0.f;
@@ -509,7 +513,7 @@ mla_rows_kernel(const MlaRowParams p) {
     const int page = table[t / p.page_size];
     if (!mla_page_ok(page, p.num_pages)) continue;             // a page id outside the cache: its tokens are masked
     const int64_t row = (int64_t)page * p.page_size + t % p.page_size;
-    const TC* kr = (const TC*)p.cache + row * p.d;
+    const TC* kr = (const TC*)p.cache + (row * p.h_kv + kvh) * p.d;
     const float ts = p.kv_scale ? p.kv_scale[row] : 1.f;
     float s = 0.f;
     for (int i = 0; i < p.d; ++i) s = fmaf(to_f32(q[i]), cache_f32<TC>(kr + i), s);
@@ -533,7 +537,7 @@ mla_rows_kernel(const MlaRowParams p) {
 
 template <typename TQ, typename TC>
 static int launch_mla_rows(const MlaRowParams& p, cudaStream_t s) {
-  const unsigned grid = (unsigned)((p.batch * p.heads + 127) / 128);
+  const unsigned grid = (unsigned)((p.batch * p.s_q * p.heads + 127) / 128);
   if (p.dv <= 64) mla_rows_kernel<TQ, TC, 64><<<grid, 128, 0, s>>>(p);
   else mla_rows_kernel<TQ, TC, 512><<<grid, 128, 0, s>>>(p);
   TL_LAUNCH_CHECK("mla_rows_kernel");
@@ -620,14 +624,50 @@ extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, con
     TL_LAUNCH_CHECK("mla_decode_fp8_kernel");
     return TL_B200_OK;
   }
+  // 16-bit cache of the query's type at the DeepSeek shape: the tcgen05 kernel of mla_f16.cu (no workspace)
+  if (cache_dtype == q_dtype && mla_f16_shape_ok(1, heads, 1, d, dv) && page_size % kMlaBN == 0 && aligned16(q) &&
+      aligned16(out) && aligned16(kv_cache))
+    return mla_f16_launch(q, nullptr, kv_cache, nullptr, block_table, cache_seqlens, out, batch, 1, heads, 1,
+                          num_pages * page_size, page_size, max_pages_per_seq, num_pages, 0, softmax_scale, q_dtype, s);
   TL_REQUIRE(dv <= 512, "mla_decode_paged: dv above 512 is not supported");
   MlaRowParams rp;
   rp.q = q; rp.cache = kv_cache; rp.kv_scale = kv_scale; rp.block_table = block_table; rp.seqlens = cache_seqlens;
   rp.out = out; rp.batch = (int)batch; rp.heads = (int)heads; rp.d = (int)d; rp.dv = (int)dv;
   rp.page_size = (int)page_size; rp.max_pages = (int)max_pages_per_seq; rp.scale = softmax_scale;
   rp.len_cap = mla_len_cap(max_pages_per_seq, num_pages, page_size); rp.num_pages = (int)num_pages;
+  rp.s_q = 1; rp.h_kv = 1;
   if (q_dtype == TL_BF16) return launch_mla_rows_cache<__nv_bfloat16>(rp, cache_dtype, s);
   return launch_mla_rows_cache<__half>(rp, cache_dtype, s);
+}
+
+// Several query tokens per sequence and several kv heads (examples/deepseek_mla/example_mla_decode_paged.py:99-256):
+// q [batch, s_q, h_q, d], cache [num_pages, page_size, h_kv, d] of the same 16-bit type, out [batch, s_q, h_q, dv];
+// head h reads kv head h / (h_q / h_kv); query token i sees the keys up to len - s_q + i.
+extern "C" int tl_b200_mla_decode_paged_gqa(const void* q, const void* kv_cache, const int32_t* block_table,
+                                            const int32_t* cache_seqlens, void* out, int64_t batch, int64_t s_q,
+                                            int64_t h_q, int64_t h_kv, int64_t d, int64_t dv, int64_t page_size,
+                                            int64_t max_pages_per_seq, int64_t num_pages, float softmax_scale, int dtype,
+                                            void* stream) {
+  TL_REQUIRE(batch >= 0 && s_q > 0 && h_q > 0 && h_kv > 0 && d > 0 && dv > 0 && page_size > 0 && max_pages_per_seq >= 0 &&
+                 num_pages >= 0, "mla_decode_paged_gqa: bad size");
+  TL_REQUIRE(h_q % h_kv == 0, "mla_decode_paged_gqa: h_q (%lld) must be a multiple of h_kv (%lld)", (long long)h_q, (long long)h_kv);
+  TL_REQUIRE(dv <= d && dv <= 512, "mla_decode_paged_gqa: dv must not exceed d or 512");
+  if (batch == 0) return TL_B200_OK;
+  TL_REQUIRE(q && kv_cache && block_table && cache_seqlens && out, "mla_decode_paged_gqa: null tensor pointer");
+  TL_REQUIRE(dtype == TL_BF16 || dtype == TL_F16, "mla_decode_paged_gqa: bfloat16 or float16");
+  TL_REQUIRE(batch * s_q * h_q < (1ll << 31) && num_pages * page_size * h_kv < (1ll << 31), "mla_decode_paged_gqa: size too large");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (mla_f16_shape_ok(s_q, h_q, h_kv, d, dv) && page_size % kMlaBN == 0 && aligned16(q) && aligned16(out) && aligned16(kv_cache))
+    return mla_f16_launch(q, nullptr, kv_cache, nullptr, block_table, cache_seqlens, out, batch, s_q, h_q, h_kv,
+                          num_pages * page_size, page_size, max_pages_per_seq, num_pages, 0, softmax_scale, dtype, s);
+  MlaRowParams rp;
+  rp.q = q; rp.cache = kv_cache; rp.kv_scale = nullptr; rp.block_table = block_table; rp.seqlens = cache_seqlens;
+  rp.out = out; rp.batch = (int)batch; rp.heads = (int)h_q; rp.d = (int)d; rp.dv = (int)dv;
+  rp.page_size = (int)page_size; rp.max_pages = (int)max_pages_per_seq; rp.scale = softmax_scale;
+  rp.len_cap = mla_len_cap(max_pages_per_seq, num_pages, page_size); rp.num_pages = (int)num_pages;
+  rp.s_q = (int)s_q; rp.h_kv = (int)h_kv;
+  if (dtype == TL_BF16) return launch_mla_rows_cache<__nv_bfloat16>(rp, dtype, s);
+  return launch_mla_rows_cache<__half>(rp, dtype, s);
 }
 
 // =================================================================================

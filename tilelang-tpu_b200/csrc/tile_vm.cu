@@ -40,15 +40,15 @@ __device__ __forceinline__ float vm_binary(float a, float b, int sub) {
     case 0: return a + b;
     case 1: return a - b;
     case 2: return a * b;
-    case 3: return a / b;
+    case 3: return __fdividef(a, b);        // 2 ulp; the reference's division is a table + polynomial routine
     default: return fmaxf(a, b);
   }
 }
 __device__ __forceinline__ float vm_unary(float a, int sub) {
   switch (sub) {
-    case 0: return 1.0f / (1.0f + expf(-a));
+    case 0: return __fdividef(1.0f, 1.0f + expf(-a));
     case 1: return expf(a);
-    default: return 1.0f / sqrtf(a);
+    default: return rsqrtf(a);
   }
 }
 __device__ __forceinline__ float vm_load(const void* base, long long idx, int dtype) {
@@ -70,7 +70,7 @@ __device__ __forceinline__ void vm_store(void* base, long long idx, int dtype, f
 template <int TPR> __device__ __forceinline__ int vm_col(int t, int e) { return ((e >> 3) * TPR + t) * 8 + (e & 7); }
 
 template <int TPR, int EPT, int NT>
-__global__ void __launch_bounds__(kVmThreads)
+__global__ void __launch_bounds__(kVmThreads, (NT * EPT <= 64) ? 2 : 1)
 tile_vm_kernel(const __grid_constant__ VmProgram prog) {
   constexpr int G = kVmThreads / TPR;              // rows in flight per CTA
   __shared__ float red[kVmThreads / 32];
@@ -197,7 +197,7 @@ tile_vm_kernel(const __grid_constant__ VmProgram prog) {
         case TL_VM_MOV_T_A:
           VM_WITH_TILE(in.r0, {
 #pragma unroll
-            for (int e = 0; e < EPT; ++e) Treg[e] = vm_round(A[e], in.dtype);
+            for (int e = 0; e < EPT; ++e) Treg[e] = A[e] = vm_round(A[e], in.dtype);   // A keeps the stored (rounded) row
           })
           break;
         case TL_VM_BIN_A_T:
@@ -329,6 +329,7 @@ extern "C" int tl_b200_tile_program_registers(int64_t max_width) {
 extern "C" int tl_b200_tile_program(const tl_b200_vm_instr* instrs, int n_instr, const void* const* params, int n_params,
                                     int grid_x, int grid_y, int grid_z, int rows_per_block, int64_t max_width,
                                     void* stream) {
+  int highest_tile = -1;
   TL_REQUIRE(instrs && n_instr > 0 && n_instr <= kVmMaxInstr, "tile_program: 1..%d instructions", kVmMaxInstr);
   TL_REQUIRE(n_params >= 0 && n_params <= kVmMaxParams && (params || n_params == 0), "tile_program: at most %d parameters",
              kVmMaxParams);
@@ -347,6 +348,11 @@ extern "C" int tl_b200_tile_program(const tl_b200_vm_instr* instrs, int n_instr,
     }
     const bool tile_reg = in.op == TL_VM_MOV_A_T || in.op == TL_VM_MOV_T_A || in.op == TL_VM_BIN_A_T;
     if (tile_reg) TL_REQUIRE(in.r0 >= 0 && in.r0 < nt, "tile_program: instruction %d uses tile register %d of %d", i, in.r0, nt);
+    if (tile_reg && in.r0 > highest_tile) highest_tile = in.r0;
+    if (in.op == TL_VM_ROPE_A) {
+      const int m4 = in.r0 > in.r1 ? in.r0 : in.r1, m5 = in.r2 > in.r3 ? in.r2 : in.r3;
+      if ((m4 > m5 ? m4 : m5) > highest_tile) highest_tile = m4 > m5 ? m4 : m5;
+    }
     if (in.op == TL_VM_ROPE_A)
       TL_REQUIRE(in.r0 >= 0 && in.r0 < nt && in.r1 >= 0 && in.r1 < nt && in.r2 >= 0 && in.r2 < nt && in.r3 >= 0 && in.r3 < nt,
                  "tile_program: instruction %d uses a tile register outside 0..%d", i, nt - 1);
@@ -358,9 +364,11 @@ extern "C" int tl_b200_tile_program(const tl_b200_vm_instr* instrs, int n_instr,
   prog.rows_per_block = rows_per_block;
   prog.total_rows = (long long)grid_x * grid_y * grid_z * rows_per_block;
   cudaStream_t s = (cudaStream_t)stream;
-  if (max_width <= 256) return launch_vm<32, 8, 8>(prog, s);
-  if (max_width <= 512) return launch_vm<32, 16, 8>(prog, s);
-  if (max_width <= 2048) return launch_vm<256, 8, 8>(prog, s);
-  if (max_width <= 4096) return launch_vm<256, 16, 8>(prog, s);
+  // a program that needs at most four tile registers runs the variant with half the registers (two CTAs per SM)
+  const bool few = highest_tile < 4;
+  if (max_width <= 256) return few ? launch_vm<32, 8, 4>(prog, s) : launch_vm<32, 8, 8>(prog, s);
+  if (max_width <= 512) return few ? launch_vm<32, 16, 4>(prog, s) : launch_vm<32, 16, 8>(prog, s);
+  if (max_width <= 2048) return few ? launch_vm<256, 8, 4>(prog, s) : launch_vm<256, 8, 8>(prog, s);
+  if (max_width <= 4096) return few ? launch_vm<256, 16, 4>(prog, s) : launch_vm<256, 16, 8>(prog, s);
   return launch_vm<256, 32, 4>(prog, s);
 }

@@ -45,6 +45,8 @@ PROTOTYPES = {
     "tl_b200_mla_decode_paged": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                                          c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_int, c_void_p,
                                          c_int64, c_void_p]),
+    "tl_b200_mla_decode_paged_gqa": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                             c_int64, c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_void_p]),
     "tl_b200_mla_decode_paged_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                                  c_int64, c_int64, c_int64, c_int64, c_float, c_int, c_void_p]),
     "tl_b200_rope_add": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),

@@ -162,6 +162,7 @@ class _Compiler:
         self.last_use = self._liveness()
         self.pos = 0
         self.mem_instrs: List[int] = []
+        self.a_holds = None                      # id of the tile whose row the accumulator currently equals
 
     # ---------------------------------------------------------------- tiles
     @staticmethod
@@ -219,6 +220,7 @@ class _Compiler:
         k = id(tile)
         if k not in self.treg:
             _need(bool(self.free_t), f"more than {self.nt} tiles of width {self.max_width} live at once")
+            self.free_t.sort()                   # lowest free register: programs with few live tiles fit the small variant
             self.treg[k] = self.free_t.pop(0)
         return self.treg[k]
 
@@ -248,7 +250,8 @@ class _Compiler:
             else:
                 setattr(ins, k, v)
         self.ins.append(ins)
-        _need(len(self.ins) <= MAX_INSTR, f"program needs more than {MAX_INSTR} instructions")
+        if op in (LD_A, BIN_A_T, BIN_A_S, BIN_A_I, UN_A, FILL_A, ROUND_A, BCAST_A_S, ROPE_A):
+            self.a_holds = None
         return len(self.ins) - 1
 
     def is_col(self, t: Buffer) -> bool:
@@ -260,11 +263,14 @@ class _Compiler:
     def load_a(self, t: Buffer):
         if self.is_col(t):
             self.emit(BCAST_A_S, r0=self._s(t))
-        else:
+            self.a_holds = None
+        elif self.a_holds != id(t):              # MOV_T_A leaves the stored row in the accumulator
             self.emit(MOV_A_T, r0=self._t(t))
+            self.a_holds = id(t)
 
     def store_a(self, t: Buffer):
         self.emit(MOV_T_A, r0=self._t(t, True), dtype=_DT[t.dtype])
+        self.a_holds = id(t)
 
     def mem(self, op, region: Region, tile_rows, tile_width, env, reg=0):
         buf = region.buffer
@@ -283,7 +289,35 @@ class _Compiler:
         for self.pos, (op, env) in enumerate(self.flat):
             self.one(op, env)
             self._release()
+        self._drop_dead_stores()
+        _need(len(self.ins) <= MAX_INSTR, f"program needs more than {MAX_INSTR} instructions")
         return self
+
+    def _drop_dead_stores(self):
+        """A MOV_T_A whose tile register is overwritten (or never read) before its next use only rounds the
+        accumulator: it becomes ROUND_A, or disappears when the tile is fp32."""
+        live = set()
+        keep = [True] * len(self.ins)
+        for i in range(len(self.ins) - 1, -1, -1):
+            ins = self.ins[i]
+            if ins.op == MOV_T_A:
+                if ins.r0 in live:
+                    live.discard(ins.r0)
+                elif ins.dtype == 0:
+                    keep[i] = False
+                else:
+                    ins.op = ROUND_A
+            elif ins.op in (MOV_A_T, BIN_A_T):
+                live.add(ins.r0)
+            elif ins.op == ROPE_A:
+                live.update((ins.r0, ins.r1, ins.r2, ins.r3))
+        remap, out = {}, []
+        for i, ins in enumerate(self.ins):
+            if keep[i]:
+                remap[i] = len(out)
+                out.append(ins)
+        self.mem_instrs = [remap[i] for i in self.mem_instrs]
+        self.ins = out
 
     def one(self, op, env):
         n, a = op.name, op.args

@@ -73,6 +73,10 @@ def prim_func(fn):
     params = []
     for i, (pname, p) in enumerate(sig.parameters.items()):
         ann = p.annotation
+        if isinstance(ann, str):      # `from __future__ import annotations` in the caller's module: evaluate it there
+            scope = dict(fn.__globals__)
+            scope.update(inspect.getclosurevars(fn).nonlocals)
+            ann = eval(ann, scope)    # noqa: S307 - the annotation text of the user's own function
         if not isinstance(ann, ir.TensorAnnotation):
             raise TypeError(f"{fn.__name__}: parameter {pname} needs a T.Tensor(shape, dtype) annotation")
         for d in ann.shape:

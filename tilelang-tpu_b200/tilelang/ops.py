@@ -363,6 +363,28 @@ def gemm_fp8_blockscale(a8: torch.Tensor, b8: torch.Tensor, scales_a: torch.Tens
                    "tl_b200_gemm_fp8_blockscale")
 
 
+def mla_decode_paged_gqa(q: torch.Tensor, kv_cache: torch.Tensor, block_table: torch.Tensor, cache_seqlens: torch.Tensor,
+                         out: torch.Tensor, softmax_scale: float | None = None) -> int:
+    """Paged decode with s_q query tokens per sequence and h_kv kv heads: q (B, s_q, h_q, D), kv_cache
+    (num_pages, page, h_kv, D) of q's 16-bit dtype, out (B, s_q, h_q, DV); query token i sees keys up to len - s_q + i."""
+    if q.dim() != 4 or kv_cache.dim() != 4 or out.dim() != 4 or kv_cache.shape[-1] != q.shape[-1]:
+        raise ValueError("mla_decode_paged_gqa: q (B, s_q, h_q, D), kv_cache (pages, page, h_kv, D), out (B, s_q, h_q, DV)")
+    b, s_q, h_q, d = q.shape
+    num_pages, page, h_kv, _ = kv_cache.shape
+    dv = out.shape[-1]
+    if tuple(out.shape[:3]) != (b, s_q, h_q) or out.dtype != q.dtype or kv_cache.dtype != q.dtype:
+        raise ValueError("mla_decode_paged_gqa: out must be (B, s_q, h_q, DV); q, cache and out share a 16-bit dtype")
+    if block_table.dtype != torch.int32 or cache_seqlens.dtype != torch.int32 or block_table.shape[0] != b or cache_seqlens.numel() != b:
+        raise ValueError("mla_decode_paged_gqa: block_table (B, max_pages) and cache_seqlens (B,) must be int32")
+    if softmax_scale is None:
+        softmax_scale = d ** -0.5
+    s = _prepare(q, kv_cache, block_table, cache_seqlens, out)
+    return N.check(N.load().tl_b200_mla_decode_paged_gqa(_ptr(q), _ptr(kv_cache), _ptr(block_table), _ptr(cache_seqlens), _ptr(out),
+                                                        b, s_q, h_q, h_kv, d, dv, page, block_table.shape[1], num_pages,
+                                                        float(softmax_scale), dtype_code(q.dtype), s),
+                   "tl_b200_mla_decode_paged_gqa")
+
+
 _workspaces: dict = {}
 
 
