@@ -188,6 +188,48 @@ def mla_decode(dev, rank, world, peaks, batch=128, heads=128, d=576, dv=512, pag
     return e
 
 
+def mla_decode_bf16(dev, rank, world, peaks, batch=128, heads=128, d=576, dv=512, page=64, lo_len=1024, hi_len=8192):
+    """The same decode with a bf16 latent cache (layout of examples/deepseek_mla/example_mla_decode_paged.py): the
+    tcgen05 kernel for 16-bit caches, one CTA pair per sequence, no workspace."""
+    gc = torch.Generator(device="cpu").manual_seed(3)
+    lens_all = torch.randint(lo_len, hi_len + 1, (batch,), generator=gc, dtype=torch.int32)
+    lists = parallel.balance_by_length(lens_all.tolist(), world)
+    mine = lists[rank]
+    lens = lens_all[mine].contiguous()
+    nb = len(mine)
+    pages_per = (lens + page - 1) // page
+    total_pages = int(pages_per.sum()) + 8
+    perm = torch.randperm(total_pages, generator=gc).to(torch.int32)
+    table = torch.zeros(nb, -(-hi_len // page), dtype=torch.int32)
+    cur = 0
+    for i in range(nb):
+        n = int(pages_per[i])
+        table[i, :n] = perm[cur:cur + n]
+        cur += n
+    g = torch.Generator(device=dev).manual_seed(3)
+    cache = torch.empty(total_pages, page, d, dtype=torch.bfloat16, device=dev)
+    for p0 in range(0, total_pages, 1024):
+        p1 = min(total_pages, p0 + 1024)
+        cache[p0:p1] = torch.randn(p1 - p0, page, d, generator=g, device=dev).bfloat16()
+    q = torch.randn(nb, heads, d, generator=g, device=dev).bfloat16()
+    so = parallel.ShardedOutput((batch, heads, dv), 0, torch.bfloat16, dev, index_lists=lists)
+    out = so.local
+    ordered = torch.empty(batch, heads, dv, dtype=torch.bfloat16, device=dev)
+    table, lens_d = table.to(dev), lens.to(dev)
+    fn = lambda: ops.mla_decode_paged(q, cache, None, table, lens_d, out, softmax_scale=d ** -0.5)   # noqa: E731
+    ms = _time(fn, world)
+    ms_g = _time(lambda: (fn(), so.gather(), so.assemble(ordered)), world, reps=3, warmup=2) if world > 1 else ms
+    tokens = int(lens_all.sum())
+    flops = 2.0 * tokens * heads * (d + dv)
+    nbytes = tokens * d * 2 + batch * heads * (d + dv) * 2
+    e = _entry("mla_decode_f16_kernel", f"bf16 paged cache, batch {batch}, {heads} heads, d {d}, dv {dv}, page {page}, "
+               f"lengths U[{lo_len},{hi_len}] ({tokens} tokens)", nbytes, 1e9, "GB/s", ms, ms_g, peaks["hbm_gbs"],
+               peaks["note"], f"sequences / {world} (balanced by length)", 1)
+    e["tflops"] = flops / (ms * 1e-3) / 1e12
+    e["frac_of_bf16_tensor_peak"] = e["tflops"] / peaks["bf16_tflops"]
+    return e
+
+
 def small_ops(dev, rank, world, peaks, rows=8192, cols=4096):
     """The remaining tile-op programs (row reductions, sigmoid, elementwise add, gather, top-k) at sizes well
     above the L2, one entry each: algorithmic bytes / device time against the measured copy bandwidth."""
@@ -277,7 +319,7 @@ def tile_program(dev, rank, world, peaks, rows=8192, cols=4096):
 def run_all(dev, rank, world, peaks):
     out = []
     plain_fp8 = None
-    for fn in (gemm_bf16, gemm_fp8_plain, gemm_fp8, mlp_gate_up, flash_attn, mla_decode):
+    for fn in (gemm_bf16, gemm_fp8_plain, gemm_fp8, mlp_gate_up, flash_attn, mla_decode, mla_decode_bf16):
         try:
             e = fn(dev, rank, world, peaks)
             if fn is gemm_fp8_plain:
@@ -305,6 +347,7 @@ SMALL = {      # reduced shapes for profiler captures: inputs above the 126 MB L
     "mlp_gate_up": dict(m=4096, n=4096, k=4096),
     "flash_attn": dict(b=2, s=4096, h=16, d=128),
     "mla_decode": dict(batch=32),
+    "mla_decode_bf16": dict(batch=32),
     "small_ops": dict(rows=2048),
     "tile_program": dict(rows=2048),
 }
