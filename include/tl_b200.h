@@ -228,7 +228,8 @@ int64_t tl_b200_mla_decode_paged_workspace_bytes(int64_t batch);
  * the query is cut into its two e4m3 terms once per call, the (sequence, 64-token tile) pairs are
  * dealt out in equal contiguous ranges to one CTA pair per two SMs whatever the batch size, and
  * sequences cut by a range boundary are merged from fp32 partials by their log-sum-exp (split-KV
- * as in examples/deepseek_mla/example_mla_decode_paged.py:99-221).  Equals the minimum when the
+ * as in examples/deepseek_mla/example_mla_decode_paged.py:99-221).  With a 16-bit cache the same scratch
+ * lets every sequence be cut into up to 8 shares of its key tiles, merged the same way.  Equals the minimum when the
  * persistent kernel cannot be used (batch above 4096).  max_pages_per_seq and page_size are
  * accepted for symmetry with the call and do not change the size.                              */
 int64_t tl_b200_mla_decode_paged_split_workspace_bytes(int64_t batch, int64_t max_pages_per_seq,

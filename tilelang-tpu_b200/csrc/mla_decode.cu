@@ -26,6 +26,7 @@
 // Other shapes / cache dtypes run a one-thread-per-(sequence, head) FMA kernel.
 #include "mla_common.cuh"
 
+#include <algorithm>
 #include <type_traits>
 
 namespace tl {
@@ -565,10 +566,9 @@ extern "C" int64_t tl_b200_mla_decode_paged_workspace_bytes(int64_t batch) {
 extern "C" int64_t tl_b200_mla_decode_paged_split_workspace_bytes(int64_t batch, int64_t max_pages_per_seq,
                                                                  int64_t page_size) {
   if (batch <= 0 || max_pages_per_seq <= 0 || page_size <= 0) return 0;
-  const int64_t plain = tl_b200_mla_decode_paged_workspace_bytes(batch);
-  if (!mla_persistent_supported(batch)) return plain;
-  const int64_t full = mla_persistent_workspace_bytes(batch);
-  return full > plain ? full : plain;
+  int64_t need = tl_b200_mla_decode_paged_workspace_bytes(batch);
+  if (mla_persistent_supported(batch)) need = std::max(need, mla_persistent_workspace_bytes(batch));   // FP8 cache
+  return std::max(need, mla_f16_workspace_bytes(batch));                                               // 16-bit cache, split-KV
 }
 
 extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, const float* kv_scale,
@@ -628,7 +628,8 @@ extern "C" int tl_b200_mla_decode_paged(const void* q, const void* kv_cache, con
   if (cache_dtype == q_dtype && mla_f16_shape_ok(1, heads, 1, d, dv) && page_size % kMlaBN == 0 && aligned16(q) &&
       aligned16(out) && aligned16(kv_cache))
     return mla_f16_launch(q, nullptr, kv_cache, nullptr, block_table, cache_seqlens, out, batch, 1, heads, 1,
-                          num_pages * page_size, page_size, max_pages_per_seq, num_pages, 0, softmax_scale, q_dtype, s);
+                          num_pages * page_size, page_size, max_pages_per_seq, num_pages, 0, softmax_scale, q_dtype, s,
+                          workspace, workspace_bytes);
   TL_REQUIRE(dv <= 512, "mla_decode_paged: dv above 512 is not supported");
   MlaRowParams rp;
   rp.q = q; rp.cache = kv_cache; rp.kv_scale = kv_scale; rp.block_table = block_table; rp.seqlens = cache_seqlens;

@@ -45,6 +45,9 @@ struct MlaF16Params {
   int split;                   // 1: the rope columns (512..575) come from the second pair of tensor maps
   int fmt;                     // kFmtF16 / kFmtBF16
   float scale_log2;
+  int splits;                  // CTA pairs per (sequence, kv head); > 1: each writes a normalised fp32 partial + its log2-sum-exp
+  float* part_o;               // [units * splits][128][512]
+  float* part_lse;             // [units * splits][128]
   int* status;
 };
 
@@ -72,11 +75,16 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int half = blockIdx.x & 1;
-  const int unit = blockIdx.x >> 1;                 // (sequence, kv head)
+  const int piece = blockIdx.x >> 1;                // (sequence, kv head, split)
+  const int unit = piece / p.splits, split = piece % p.splits;
   const int b = unit / p.h_kv, kvh = unit % p.h_kv;
   const int rows_used = p.s_q * p.group;
   const int seqlen = p.seqlens ? min(max(__ldg(p.seqlens + b), 0), p.len_cap) : p.dense_len;
-  const int n_tiles = (seqlen + kFBN - 1) / kFBN;
+  // this CTA pair's contiguous share of the sequence's key tiles
+  const int tiles_all = (seqlen + kFBN - 1) / kFBN;
+  const int per_split = (tiles_all + p.splits - 1) / p.splits;
+  const int t0 = min(split * per_split, tiles_all);
+  const int n_tiles = min(tiles_all - t0, per_split);
   const int* table = p.block_table ? p.block_table + (int64_t)b * p.max_pages : nullptr;
 
   if (threadIdx.x == 0) {
@@ -126,7 +134,7 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1;
         if (!(ok = mbar_wait(bar_kvempty + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag))) break;
-        const int tok = j * kFBN;
+        const int tok = (t0 + j) * kFBN;
         int row;
         if (table) {
           const int page = __ldg(table + tok / p.page_size);
@@ -227,7 +235,7 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
     for (int j = 0; j < n_tiles && ok; ++j) {
       const uint32_t t_s = tmem_base + kFColS + (j & 1) * kFBN + lane_off;
       int page_ok = 1;
-      if (table) page_ok = (unsigned)__ldg(table + j * kFBN / p.page_size) < (unsigned)p.num_pages;
+      if (table) page_ok = (unsigned)__ldg(table + (t0 + j) * kFBN / p.page_size) < (unsigned)p.num_pages;
       ok = mbar_wait(bar_sfull + 8 * (j & 1), (j >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -235,7 +243,7 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       uint32_t sv[64];
       tmem_ld_32x64(t_s, sv);
       tmem_ld_wait_for(sv);
-      const int valid = page_ok ? row_len - j * kFBN : 0;      // tokens of this tile the row may see
+      const int valid = page_ok ? row_len - (t0 + j) * kFBN : 0;      // tokens of this tile the row may see
       float m_tile = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 64; ++c) {
@@ -285,23 +293,35 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_pfull + 8 * (j & 1));
     }
-    // epilogue: 256 output columns of the row
+    // epilogue: 256 output columns of the row; with several splits a normalised fp32 partial and its log2-sum-exp
     T* out = reinterpret_cast<T*>(p.out) + grow * kFDV + half * 256;
+    float* po = p.splits > 1 ? p.part_o + ((int64_t)piece * kFRows + r) * kFDV + half * 256 : nullptr;
     if (n_tiles == 0) {
-      if (row_live)
+      if (p.splits > 1) {
+        if (half == 0) p.part_lse[(int64_t)piece * kFRows + r] = -INFINITY;      // the merge gives this piece no weight
+      } else if (row_live) {
         for (int c = 0; c < 256 / 8; ++c) reinterpret_cast<uint4*>(out)[c] = make_uint4(0, 0, 0, 0);
+      }
     } else if (ok) {
       ok = mbar_wait(bar_pvdone + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, abort_flag);
       ok = __all_sync(0xffffffffu, ok);
       if (ok) {
         tc_fence_after_sync();
         const float inv = row_sum > 0.f ? 1.0f / row_sum : 0.f;
+        if (p.splits > 1 && half == 0)
+          p.part_lse[(int64_t)piece * kFRows + r] = row_sum > 0.f ? m_used + log2f(row_sum) : -INFINITY;
 #pragma unroll 1
         for (int c = 0; c < 256 / 32; ++c) {
           uint32_t ov[32];
           tmem_ld_32x32(t_o + c * 32, ov);
           tmem_ld_wait();
-          if (row_live) {
+          if (p.splits > 1) {
+#pragma unroll
+            for (int e = 0; e < 32; e += 4)
+              *reinterpret_cast<float4*>(po + c * 32 + e) =
+                  make_float4(__uint_as_float(ov[e]) * inv, __uint_as_float(ov[e + 1]) * inv, __uint_as_float(ov[e + 2]) * inv,
+                              __uint_as_float(ov[e + 3]) * inv);
+          } else if (row_live) {
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
               Vec16<T> v;
@@ -327,7 +347,67 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   }
 }
 
+// Merges the `splits` partials of every (sequence, kv head): out = sum_c 2^(lse_c - M) O_c / sum_c 2^(lse_c - M).
+// One warp per row, a lane owns 16 of the 512 columns.
+template <typename T>
+__global__ void __launch_bounds__(256)
+mla_f16_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse, T* __restrict__ out, int splits,
+                     int s_q, int h_q, int h_kv, int group) {
+  const int unit = blockIdx.x, b = unit / h_kv, kvh = unit % h_kv;
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  const int r = blockIdx.y * 8 + warp;
+  if (r >= s_q * group) return;
+  const int64_t grow = ((int64_t)b * s_q + r / group) * h_q + kvh * group + r % group;
+  float m = -INFINITY;
+  for (int c = 0; c < splits; ++c) m = fmaxf(m, part_lse[((int64_t)unit * splits + c) * kFRows + r]);
+  float denom = 0.f;
+  float4 acc[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c = 0; c < splits; ++c) {
+    const int64_t piece = (int64_t)unit * splits + c;
+    const float lse = part_lse[piece * kFRows + r];
+    if (lse == -INFINITY) continue;                      // a piece without visible keys (its partial was not written)
+    const float w = exp2f(lse - m);
+    denom += w;
+    const float4* src = reinterpret_cast<const float4*>(part_o + (piece * kFRows + r) * kFDV) + lane;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float4 v = src[k * 32];
+      acc[k].x = fmaf(w, v.x, acc[k].x); acc[k].y = fmaf(w, v.y, acc[k].y);
+      acc[k].z = fmaf(w, v.z, acc[k].z); acc[k].w = fmaf(w, v.w, acc[k].w);
+    }
+  }
+  const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+  T* o = out + grow * kFDV + lane * 4;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    Vec16<T> v;                                // the first four elements are used: 8 bytes
+    v.e[0] = from_f32<T>(acc[k].x * inv); v.e[1] = from_f32<T>(acc[k].y * inv);
+    v.e[2] = from_f32<T>(acc[k].z * inv); v.e[3] = from_f32<T>(acc[k].w * inv);
+    *reinterpret_cast<uint2*>(o + k * 128) = make_uint2(v.raw.x, v.raw.y);
+  }
+}
+
 // ---- host ---------------------------------------------------------------------------------------
+// Splits per (sequence, kv head): about three CTAs per SM in total (short CTAs even out sequences of different
+// lengths), at most 8; fewer when the scratch is too small.
+int mla_f16_splits(int64_t units, int64_t workspace_bytes) {
+  int splits = (int)((3 * sm_count() + 2 * units - 1) / (2 * units));
+  if (splits > 8) splits = 8;
+  while (splits > 1 && units * splits * kFRows * (kFDV + 1) * 4 + 256 > workspace_bytes) --splits;
+  return splits < 1 ? 1 : splits;
+}
+
+// Scratch that lets mla_f16_splits() choose freely for `units` (sequence, kv head) pairs.
+int64_t mla_f16_workspace_bytes(int64_t units) {
+  if (units <= 0) return 0;
+  int64_t splits = (3 * sm_count() + 2 * units - 1) / (2 * units);
+  if (splits > 8) splits = 8;
+  if (splits <= 1) return 0;
+  return units * splits * kFRows * (kFDV + 1) * 4 + 512;
+}
+
 bool mla_f16_shape_ok(int64_t s_q, int64_t h_q, int64_t h_kv, int64_t d, int64_t dv) {
   if (d != kFD || dv != kFDV || h_kv <= 0 || h_q % h_kv != 0 || s_q <= 0) return false;
   const int64_t group = h_q / h_kv;
@@ -340,7 +420,7 @@ bool mla_f16_shape_ok(int64_t s_q, int64_t h_q, int64_t h_kv, int64_t d, int64_t
 int mla_f16_launch(const void* q, const void* q_pe, const void* kv, const void* k_pe, const int32_t* block_table,
                    const int32_t* seqlens, void* out, int64_t batch, int64_t s_q, int64_t h_q, int64_t h_kv,
                    int64_t total_tokens, int64_t page_size, int64_t max_pages, int64_t num_pages, int64_t dense_len,
-                   float softmax_scale, int dtype, cudaStream_t stream) {
+                   float softmax_scale, int dtype, cudaStream_t stream, void* workspace, int64_t workspace_bytes) {
   const bool split = q_pe != nullptr;
   const int64_t group = h_q / h_kv;
   const CUtensorMapDataType dt = dtype == TL_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -380,7 +460,18 @@ int mla_f16_launch(const void* q, const void* q_pe, const void* kv, const void* 
   p.fmt = dtype == TL_BF16 ? kFmtBF16 : kFmtF16;
   p.scale_log2 = softmax_scale * 1.4426950408889634f;
   p.status = device_status_word();
-  const unsigned grid = (unsigned)(2 * batch * h_kv);
+  // Few (sequence, kv head) units leave SMs idle: with scratch from the caller every unit is cut into `splits`
+  // contiguous shares of its key tiles (split-KV as in examples/deepseek_mla/example_mla_decode_paged.py:99-221) and a
+  // second kernel merges the normalised partials by their log-sum-exp.
+  const int64_t units = batch * h_kv;
+  p.splits = workspace ? mla_f16_splits(units, workspace_bytes) : 1;
+  p.part_o = nullptr; p.part_lse = nullptr;
+  if (p.splits > 1) {
+    char* ws = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~(uintptr_t)255u);
+    p.part_lse = reinterpret_cast<float*>(ws);
+    p.part_o = reinterpret_cast<float*>(ws + ((units * p.splits * kFRows * 4 + 255) / 256) * 256);
+  }
+  const unsigned grid = (unsigned)(2 * units * p.splits);
   if (dtype == TL_BF16) {
     auto kernel = mla_decode_f16_kernel<__nv_bfloat16>;
     TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kFSmem));
@@ -391,6 +482,16 @@ int mla_f16_launch(const void* q, const void* q_pe, const void* kv, const void* 
     kernel<<<grid, kFThreads, kFSmem, stream>>>(tm_q, tm_qpe, tm_kv, tm_kpe, p);
   }
   TL_LAUNCH_CHECK("mla_decode_f16_kernel");
+  if (p.splits > 1) {
+    const dim3 mgrid((unsigned)units, (unsigned)((s_q * group + 7) / 8));
+    if (dtype == TL_BF16)
+      mla_f16_merge_kernel<__nv_bfloat16><<<mgrid, 256, 0, stream>>>(p.part_o, p.part_lse, (__nv_bfloat16*)out, p.splits, (int)s_q,
+                                                                   (int)h_q, (int)h_kv, (int)group);
+    else
+      mla_f16_merge_kernel<__half><<<mgrid, 256, 0, stream>>>(p.part_o, p.part_lse, (__half*)out, p.splits, (int)s_q, (int)h_q,
+                                                           (int)h_kv, (int)group);
+    TL_LAUNCH_CHECK("mla_f16_merge_kernel");
+  }
   return TL_B200_OK;
 }
 
