@@ -2,7 +2,7 @@
 //
 // tcgen05 kernel (bf16 / fp16, head_dim 64 or 128): one CTA owns 256 query rows of one
 // (batch, head) as two 128-row "lanes".  Both lanes share every K/V tile that TMA brings into a
-// 3-stage shared-memory ring, which halves L2 traffic per flop, and they ping-pong on the tensor
+// 4-stage shared-memory ring, which halves L2 traffic per flop, and they ping-pong on the tensor
 // core: while one lane's softmax warpgroup works on its scores, the MMA thread runs the other
 // lane's S = Q K^T or O += P V.  S, P and O all live in tensor memory: every lane has two S
 // buffers, so S runs two key tiles ahead of P V, and the softmax threads write P (16-bit) over the
