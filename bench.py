@@ -463,6 +463,12 @@ def main():
         import kernel_bench
         kernels = kernel_bench.run_all(dev, rank, world, peaks)
 
+    # every rank is done with the GPU: leave the process group first, so that no rank spins in a collective on the
+    # host cores while rank 0 times the CPU baseline
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
     if rank == 0:
         peak, peak_kind = peaks["hbm_gbs"], peaks["note"].replace("of ", "")
         swiglu_bytes = alg["swiglu"] / world                     # bytes one launch moves on one GPU
@@ -501,9 +507,6 @@ def main():
                 "value": cpu_gbs, "unit": "GB/s", "cores": threads, "kind": "port",
                 "sample": f"best of {2 if world > 1 else 3} full passes of the same {tokens}-token workload ({cpu_s:.2f} s per pass)"}
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":
