@@ -10,8 +10,8 @@
 // swizzle) -> tcgen05.mma kind::f8f6f4 into one of four partial accumulators in tensor memory ->
 // eight promotion warps (64 columns of 32 rows each) pull the partial with tcgen05.ld and do the scaled
 // accumulation in registers while the tensor core already fills the next partials.  The promotion is a
-// dependent chain per warp (wait for the partial, load, hand the buffer back, multiply in), so a partial is
-// fetched with a single 64-column load: one round trip to tensor memory per K block.
+// dependent chain per warp (wait for the partial, load, hand the buffer back, multiply in): a warp fetches its
+// share with a single load, one round trip to tensor memory per K block.
 #include "sm100.cuh"
 
 namespace tl {
@@ -19,8 +19,10 @@ using namespace sm100;
 
 constexpr int kF8BM = 128, kF8BN = 128, kF8BK = 128;
 constexpr int kF8Stages = 6;
-constexpr int kF8Threads = 320;       // warp 0 TMEM alloc + TMA, warp 1 MMA, warps 2-9 promotion/epilogue
-constexpr int kF8PromoWarp0 = 2;
+constexpr int kF8Cols = 64;           // columns of a partial per promotion warp (32: sixteen warps, measured 4% slower at the C4 shape)
+constexpr int kF8PromoWarps = 4 * (kF8BN / kF8Cols);        // 8: four lane quarters x two column groups
+constexpr int kF8PromoWarp0 = 4;      // warp 0 TMEM alloc + TMA, warp 1 MMA, warps 4.. promotion/epilogue
+constexpr int kF8Threads = (kF8PromoWarp0 + kF8PromoWarps) * 32;
 constexpr int kF8StageBytes = (kF8BM + kF8BN) * kF8BK;
 constexpr int kF8Smem = kF8Stages * kF8StageBytes + 1024 + 256;
 constexpr int kF8Acc = 4;             // partial accumulators in tensor memory (4 x 128 columns)
@@ -66,7 +68,7 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
     }
     for (int a = 0; a < kF8Acc; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 8);       // one arrival per promotion warp
+      mbar_init(bar_tempty + 8 * a, kF8PromoWarps);       // one arrival per promotion warp
     }
     mbar_fence_init();
     prefetch_tensormap(&tm_a);
@@ -139,7 +141,7 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       }
     }
   } else if (warp >= kF8PromoWarp0) {
-    const int wg = (warp - kF8PromoWarp0) / 4;   // column half
+    const int wg = (warp - kF8PromoWarp0) / 4;   // column group
     const int quarter = warp % 4;             // the tensor-memory lanes a warp may touch follow from warp % 4
     const int r = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
@@ -153,9 +155,9 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
       const int row = tm * kF8BM + r;
       const float* sa_row = p.sa + (int64_t)(row < p.m ? row : 0) * p.kblocks;
       const float* sb_row = p.sb + (int64_t)tn * p.kblocks;
-      float2 acc2[32];                         // 64 fp32 accumulators, updated two at a time
+      float2 acc2[kF8Cols / 2];                // fp32 accumulators, updated two at a time
 #pragma unroll
-      for (int j = 0; j < 32; ++j) acc2[j] = make_float2(0.f, 0.f);
+      for (int j = 0; j < kF8Cols / 2; ++j) acc2[j] = make_float2(0.f, 0.f);
       float* acc = reinterpret_cast<float*>(acc2);
       // Per K block: wait for the partial, ONE 64-column load (a single round trip to tensor memory), hand the
       // buffer back to the tensor core, then multiply the partial in.  The scales of a row are fetched four K
@@ -189,32 +191,33 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after_sync();
-          uint32_t v[64];
-          tmem_ld_32x64(tmem_base + buf * kF8BN + wg * 64 + lane_off, v);
+          uint32_t v[kF8Cols];
+          if constexpr (kF8Cols == 64) tmem_ld_32x64(tmem_base + buf * kF8BN + wg * kF8Cols + lane_off, reinterpret_cast<uint32_t(&)[64]>(v));
+          else tmem_ld_32x32(tmem_base + buf * kF8BN + wg * kF8Cols + lane_off, reinterpret_cast<uint32_t(&)[32]>(v));
           tmem_ld_wait_for(v);
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
           const float2 sc2 = make_float2(sc_of[q], sc_of[q]);
 #pragma unroll
-          for (int j = 0; j < 64; j += 2)
+          for (int j = 0; j < kF8Cols; j += 2)
             acc2[j / 2] = fma2(make_float2(__uint_as_float(v[j]), __uint_as_float(v[j + 1])), sc2, acc2[j / 2]);
           ++it;
         }
       }
       if (!ok) break;
-      const int col0 = tn * kF8BN + wg * 64;
+      const int col0 = tn * kF8BN + wg * kF8Cols;
       if (row < p.m && col0 < p.n) {
         TOut* dst = c + (int64_t)row * p.n + col0;
-        const int valid = min(64, p.n - col0);
-        if (vec_ok && valid == 64) {
+        const int valid = min(kF8Cols, p.n - col0);
+        if (vec_ok && valid == kF8Cols) {
           if constexpr (sizeof(TOut) == 4) {
 #pragma unroll
-            for (int j = 0; j < 64; j += 4)
+            for (int j = 0; j < kF8Cols; j += 4)
               *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
           } else {
 #pragma unroll
-            for (int j = 0; j < 64; j += 8) {
+            for (int j = 0; j < kF8Cols; j += 8) {
               Vec16<TOut> o;
 #pragma unroll
               for (int e = 0; e < 8; ++e) o.e[e] = from_f32<TOut>(acc[j + e]);
@@ -223,7 +226,7 @@ gemm_fp8_blockscale_kernel(const __grid_constant__ CUtensorMap tm_a, const __gri
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 64; ++j)
+          for (int j = 0; j < kF8Cols; ++j)
             if (j < valid) dst[j] = from_f32<TOut>(acc[j]);
         }
       }
