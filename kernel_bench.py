@@ -279,13 +279,18 @@ def small_ops(dev, rank, world, peaks, rows=8192, cols=4096):
     k = 8
     tv = torch.empty(4 * rows, k, device=dev)
     ti = torch.empty(4 * rows, k, dtype=torch.int32, device=dev)
-    xt = xf.view(4 * rows * 4, cols // 4)             # 1024-wide rows: the warp kernel
+    xt = xf.view(4 * rows * 4, cols // 4)             # 1024-wide rows: 8 cells per lane
     tv4 = torch.empty(xt.shape[0], k, device=dev)
     ti4 = torch.empty(xt.shape[0], k, dtype=torch.int32, device=dev)
-    add("topk_warp_kernel", f"top-{k} of fp32 rows [{xt.shape[0]}, {xt.shape[1]}]", xt.numel() * 4 + xt.shape[0] * k * 8,
+    add("topk_cells_kernel", f"top-{k} of fp32 rows [{xt.shape[0]}, {xt.shape[1]}]", xt.numel() * 4 + xt.shape[0] * k * 8,
         lambda: ops.topk(xt, tv4, ti4, k))
-    add("topk_cta_kernel", f"top-{k} of fp32 rows [{4 * rows}, {cols}]", xf.numel() * 4 + 4 * rows * k * 8,
+    add("topk_cells_kernel", f"top-{k} of fp32 rows [{4 * rows}, {cols}]", xf.numel() * 4 + 4 * rows * k * 8,
         lambda: ops.topk(xf, tv, ti, k))
+    k32 = 32
+    tv32 = torch.empty(4 * rows, k32, device=dev)
+    ti32 = torch.empty(4 * rows, k32, dtype=torch.int32, device=dev)
+    add("topk_cells_kernel", f"top-{k32} of fp32 rows [{4 * rows}, {cols}]", xf.numel() * 4 + 4 * rows * k32 * 8,
+        lambda: ops.topk(xf, tv32, ti32, k32))
     return out
 
 

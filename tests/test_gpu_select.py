@@ -94,6 +94,57 @@ def test_topk_ties_lower_index_first(cuda_device, dtype):
             assert torch.equal(idx.cpu(), ri) and torch.equal(vals.cpu(), rv)
 
 
+@pytest.mark.parametrize("desc", [True, False])
+@pytest.mark.parametrize("dtype", [torch.int32, torch.float32])
+@pytest.mark.parametrize("rows,length,k,levels", [(64, 1024, 8, 3), (33, 1000, 32, 5), (16, 2048, 16, 2), (8, 1537, 8, 1),
+                                                  (40, 255, 32, 40), (7, 31, 20, 4), (16, 1024, 32, 2000)])
+def test_topk_many_equal_values(cuda_device, dtype, rows, length, k, levels, desc):
+    """Few distinct values: the candidate set of the threshold selection overflows its 32 slots (the round-by-round
+    path runs), and every tie must still come out lower position first; 2000 levels gives a mix of both paths."""
+    g = gen(rows + length * 7 + k + levels)
+    src = torch.randint(-levels, levels + 1, (rows, length), generator=g).to(dtype)
+    rv, ri = O.topk(src, k, desc)
+    vals = torch.zeros(rows, k, dtype=dtype, device=cuda_device)
+    idx = torch.zeros(rows, k, dtype=torch.int32, device=cuda_device)
+    ops.topk(src.to(cuda_device), vals, idx, k, desc)
+    assert torch.equal(idx.cpu(), ri.reshape(rows, k))
+    assert torch.equal(vals.cpu(), rv.reshape(rows, k))
+
+
+@pytest.mark.parametrize("desc", [True, False])
+@pytest.mark.parametrize("rows,length,k,levels", [(600, 4096, 8, 0), (600, 2501, 32, 0), (640, 4096, 8, 3), (600, 3001, 5, 50),
+                                                  (592, 16384, 16, 100000), (600, 8192, 32, 0)])
+def test_topk_many_long_rows(cuda_device, rows, length, k, levels, desc):
+    """Enough rows of 2049..16384 elements for the one-warp-per-row streaming kernel; levels 0 = distinct values."""
+    g = gen(rows + length + k + levels)
+    if levels:
+        src = torch.randint(-levels, levels + 1, (rows, length), generator=g).float()
+    else:
+        src = torch.stack([torch.randperm(length, generator=g).float() for _ in range(8)]).repeat(rows // 8, 1) * 0.25 - 100.0
+    src = src.contiguous()
+    ref = torch.sort(src, dim=1, descending=desc, stable=True)
+    rv, ri = O.topk(src[:16], k, desc)
+    assert torch.equal(ri.reshape(16, k).long(), ref.indices[:16, :k])       # the oracle's order = a stable sort's
+    vals = torch.zeros(rows, k, device=cuda_device)
+    idx = torch.zeros(rows, k, dtype=torch.int32, device=cuda_device)
+    ops.topk(src.to(cuda_device), vals, idx, k, desc)
+    assert torch.equal(idx.cpu().long(), ref.indices[:, :k])
+    assert torch.equal(vals.cpu(), ref.values[:, :k])
+
+
+def test_topk_row_base_not_16_byte_aligned(cuda_device):
+    """A view that starts 4 bytes into an allocation takes the scalar-load form of the kernel."""
+    g = gen(77)
+    base = torch.randn(4 * 1024 + 1, generator=g)
+    src = base[1:].view(4, 1024)
+    rv, ri = O.topk(src.contiguous(), 8, True)
+    dev = base.to(cuda_device)[1:].view(4, 1024)
+    vals = torch.zeros(4, 8, device=cuda_device)
+    idx = torch.zeros(4, 8, dtype=torch.int32, device=cuda_device)
+    ops.topk(dev, vals, idx, 8, True)
+    assert torch.equal(idx.cpu(), ri.reshape(4, 8)) and torch.equal(vals.cpu(), rv.reshape(4, 8))
+
+
 def test_topk_negative_and_special_floats(cuda_device):
     src = torch.tensor([[-1.5, float("-inf"), 2.0, float("inf"), -0.25, 1e-38, -1e-38, 3.5]])
     rv, ri = O.topk(src, 8, True)

@@ -128,6 +128,328 @@ topk_warp_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ out_va
   }
 }
 
+
+// ---- threshold selection (k <= 32, one warp per row) -------------------------------------------------------------
+// The k-th largest of the 32 lane maxima, T, is a lower bound of the k-th largest element (k lanes hold an element
+// >= T), so only elements >= T can be winners: about k of them for small k, about 120 for k = 32 on random data.  They
+// are appended to the warp's 256 slots of shared memory and sorted there (one rank count or one bitonic network over
+// the lanes), instead of k rounds of arg-max over the whole row.  Rows with more than 256 candidates (many equal
+// values) fall back to k rounds over the row.  Candidates compare by (image, position): larger image first, lower
+// position on ties, as everywhere in this file.
+constexpr int kSlots = 256;
+
+__device__ __forceinline__ bool pair_before(uint32_t o, uint32_t p, uint32_t o2, uint32_t p2) {     // (o, p) sorts before (o2, p2)
+  return o > o2 || (o == o2 && p < p2);
+}
+
+// Bitonic sort of E (image, position) pairs per lane, element lane * E + e of the sequence in o[e]; best pair first.
+template <int E>
+__device__ __forceinline__ void warp_sort_pairs(uint32_t (&o)[E], uint32_t (&p)[E], int lane) {
+#pragma unroll
+  for (int size = 2; size <= 32 * E; size <<= 1) {
+#pragma unroll
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      if (stride >= E) {                                   // partner in another lane
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const uint32_t o2 = __shfl_xor_sync(0xffffffffu, o[e], stride / E);
+          const uint32_t p2 = __shfl_xor_sync(0xffffffffu, p[e], stride / E);
+          const int at = lane * E + e;
+          const bool lower = (at & stride) == 0;           // this side keeps the pair that sorts first ...
+          const bool forward = (at & size) == 0;           // ... when its block sorts forward
+          const bool mine_first = pair_before(o[e], p[e], o2, p2);
+          const bool keep = (lower == forward) ? mine_first : !mine_first;
+          o[e] = keep ? o[e] : o2;
+          p[e] = keep ? p[e] : p2;
+        }
+      } else {                                             // partner in this lane
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          if ((e & stride) == 0) {
+            const int f = e | stride;
+            const bool forward = ((lane * E + e) & size) == 0;
+            const bool in_order = pair_before(o[e], p[e], o[f], p[f]);
+            const bool swap = forward ? !in_order : in_order;
+            const uint32_t oe = o[e], pe = p[e];
+            o[e] = swap ? o[f] : oe;  p[e] = swap ? p[f] : pe;
+            o[f] = swap ? oe : o[f];  p[f] = swap ? pe : p[f];
+          }
+        }
+      }
+    }
+  }
+}
+
+// The k-th largest (with multiplicity) of one value per lane.  Small k: rounds of a warp-wide maximum that retire
+// every lane holding it; larger k: one sort.  Lanes without elements pass 0 and can only lower the result, which
+// keeps it a valid threshold.
+__device__ __forceinline__ uint32_t kth_largest_of_lanes(uint32_t v, int k, int lane) {
+  if (k <= 10) {
+    bool alive = true;
+    int seen = 0;
+    uint32_t m = 0;
+    for (int r = 0; r < k; ++r) {
+      m = __reduce_max_sync(0xffffffffu, alive ? v : 0u);
+      const uint32_t hit = __ballot_sync(0xffffffffu, alive && v == m);
+      seen += __popc(hit);
+      if (seen >= k || hit == 0u) break;
+      alive = alive && v != m;
+    }
+    return m;
+  }
+  uint32_t so[1] = {v}, sp[1] = {(uint32_t)lane};
+  warp_sort_pairs<1>(so, sp, lane);
+  return __shfl_sync(0xffffffffu, so[0], k - 1);
+}
+
+template <int DTYPE, int E>
+__device__ __noinline__ void sort_slots_and_write(const uint32_t* slot_o, const uint32_t* slot_p, int total, int k, int lane,
+                                                     bool descending, uint32_t* out_vals, int32_t* out_idx) {
+  // an empty slot (image 0, position kNoPos) sorts after every real element: kNoPos is above every real position
+  uint32_t o[E], p[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const int at = lane * E + e;
+    o[e] = at < total ? slot_o[at] : 0u;
+    p[e] = at < total ? slot_p[at] : kNoPos;
+  }
+  warp_sort_pairs<E>(o, p, lane);
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const int at = lane * E + e;
+    if (at < k) {
+      out_idx[at] = (int32_t)p[e];
+      out_vals[at] = value_bits<DTYPE>(descending ? o[e] : ~o[e]);
+    }
+  }
+}
+
+// The image of the k-th best of a warp's kSlots full slots: at least k elements of the row reach it, so it is a
+// valid (and higher) threshold when the first one let too many candidates through.
+__device__ __noinline__ uint32_t kth_image_of_full_slots(const uint32_t* slot_o, const uint32_t* slot_p, int k, int lane) {
+  constexpr int E = kSlots / 32;
+  uint32_t o[E], p[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) { o[e] = slot_o[lane * E + e]; p[e] = slot_p[lane * E + e]; }
+  warp_sort_pairs<E>(o, p, lane);
+  uint32_t v = 0;
+#pragma unroll
+  for (int e = 0; e < E; ++e) v = ((k - 1) % E == e) ? o[e] : v;
+  return __shfl_sync(0xffffffffu, v, (k - 1) / E);
+}
+
+// The best k of `total` <= kSlots candidates in a warp's slots, written in order.  Few candidates: every lane ranks
+// its own candidate against all of them (positions are distinct, so ranks are); more: one sort.
+template <int DTYPE>
+__device__ __forceinline__ void write_best_of_slots(const uint32_t* slot_o, const uint32_t* slot_p, int total, int k, int lane,
+                                                    bool descending, uint32_t* out_vals, int32_t* out_idx) {
+  if (total <= 16) {
+    const uint32_t o = lane < total ? slot_o[lane] : 0u, p = lane < total ? slot_p[lane] : kNoPos;
+    int rank = 0;
+#pragma unroll 4
+    for (int i = 0; i < total; ++i) rank += pair_before(slot_o[i], slot_p[i], o, p) ? 1 : 0;
+    if (lane < total && rank < k) {
+      out_idx[rank] = (int32_t)p;
+      out_vals[rank] = value_bits<DTYPE>(descending ? o : ~o);
+    }
+  } else if (total <= 32) {
+    sort_slots_and_write<DTYPE, 1>(slot_o, slot_p, total, k, lane, descending, out_vals, out_idx);
+  } else if (total <= 128) {
+    sort_slots_and_write<DTYPE, 4>(slot_o, slot_p, total, k, lane, descending, out_vals, out_idx);
+  } else {
+    sort_slots_and_write<DTYPE, 8>(slot_o, slot_p, total, k, lane, descending, out_vals, out_idx);
+  }
+}
+
+// A warp's view of one row: lane L reads cells of 4 consecutive elements, cell c at position (c * 32 + L) * 4, as one
+// 16-byte load when the row allows it.
+template <int DTYPE, bool VEC>
+struct RowCells {
+  const uint32_t* in;
+  int length, lane;
+  uint32_t flip;                                           // ascending order: complemented images
+  __device__ __forceinline__ int pos0(int cell) const { return (cell * 32 + lane) * 4; }
+  __device__ __forceinline__ void load(int cell, uint32_t (&raw)[4]) const {
+    const int at = pos0(cell);
+    if constexpr (VEC) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (at < length) v = __ldg(reinterpret_cast<const uint4*>(in + at));
+      raw[0] = v.x; raw[1] = v.y; raw[2] = v.z; raw[3] = v.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) raw[e] = at + e < length ? __ldg(in + at + e) : 0u;
+    }
+  }
+  __device__ __forceinline__ uint32_t image(uint32_t raw) const { return order_bits<DTYPE>(raw) ^ flip; }
+  // visit(cell, images[4]) for every cell of the row, 8 cells per lane in flight; elements past the end of the row have
+  // image 0 and must be told apart by position (`exists`)
+  __device__ __forceinline__ bool exists(int cell, int e) const { return pos0(cell) + e < length; }
+  template <class F>
+  __device__ __forceinline__ void for_each_cell(F&& visit) const {
+    for (int base = 0; base * 128 < length; base += 8) {
+      uint32_t raw[8][4];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) load(base + u, raw[u]);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) raw[u][e] = exists(base + u, e) ? image(raw[u][e]) : 0u;
+        visit(base + u, raw[u]);
+      }
+    }
+  }
+};
+
+// More than kSlots candidates: k rounds, each one pass over the row that picks the best element strictly after the
+// previous winner in the (image, position) order, so no "taken" state is kept.
+template <int DTYPE, bool VEC>
+__device__ __noinline__ void topk_by_rounds(const RowCells<DTYPE, VEC>& row, int k, bool descending, uint32_t* out_vals,
+                                            int32_t* out_idx) {
+  uint32_t prev_o = 0, prev_p = 0, res_o = 0, res_p = kNoPos;
+  for (int r = 0; r < k; ++r) {
+    uint32_t bo = 0, bp = kNoPos;
+    row.for_each_cell([&](int cell, const uint32_t (&o)[4]) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t pos = (uint32_t)(row.pos0(cell) + e);
+        const bool after = r == 0 || pair_before(prev_o, prev_p, o[e], pos);
+        const bool better = row.exists(cell, e) && after && (bp == kNoPos || pair_before(o[e], pos, bo, bp));
+        bo = better ? o[e] : bo;
+        bp = better ? pos : bp;
+      }
+    });
+    warp_argmax(bo, bp);
+    prev_o = bo; prev_p = bp;
+    if (row.lane == (r & 31)) { res_o = bo; res_p = bp; }
+  }
+  if (row.lane < k) {
+    out_idx[row.lane] = (int32_t)res_p;
+    out_vals[row.lane] = value_bits<DTYPE>(descending ? res_o : ~res_o);
+  }
+}
+
+struct WarpSlots {
+  uint32_t o[kThreads / 32][kSlots], p[kThreads / 32][kSlots];
+};
+// Every lane of the warp calls this together; lanes with `hit` append (o, pos) behind the `count` pairs already there.
+// The count is the same in every lane, so no shared counter and no atomics are needed.
+__device__ __forceinline__ void append_slots(WarpSlots& sl, int warp, int lane, int& count, bool hit, uint32_t o, uint32_t pos) {
+  const uint32_t m = __ballot_sync(0xffffffffu, hit);
+  if (m == 0u) return;
+  const int slot = count + __popc(m & ((1u << lane) - 1u));
+  if (hit && slot < kSlots) { sl.o[warp][slot] = o; sl.p[warp][slot] = pos; }
+  count += __popc(m);
+}
+
+// Rows of up to 128 * CELLS elements, read from memory ONCE: a lane keeps the maximum of each of its cells, and after T
+// is known reads again (from L1 / L2) only the cells whose maximum reaches T.  Above 32 cells only the upper 16 bits
+// of a maximum are kept, two per register: comparing them with T's upper bits selects a superset of the cells.
+template <int DTYPE, int CELLS, bool VEC>
+__global__ void __launch_bounds__(kThreads, CELLS > 32 ? 2 : CELLS == 32 ? 3 : 4)
+topk_cells_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ out_vals, int32_t* __restrict__ out_idx,
+                  int64_t rows, int length, int k, bool descending, int64_t out_stride) {
+  __shared__ WarpSlots sl;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x / 32;
+  const int64_t r = (int64_t)blockIdx.x * (kThreads / 32) + warp;
+  if (r >= rows) return;
+  const RowCells<DTYPE, VEC> row{src + r * length, length, lane, descending ? 0u : ~0u};
+  constexpr bool kPacked = CELLS > 32;
+  static_assert(CELLS <= 64 && (CELLS % 2 == 0), "one 64-bit mask of cells per lane");
+  uint32_t cell_max[kPacked ? CELLS / 2 : CELLS], lm = 0;
+  constexpr int kBatch = CELLS < 8 ? CELLS : 8;
+#pragma unroll
+  for (int c0 = 0; c0 < CELLS; c0 += kBatch) {
+    uint32_t raw[kBatch][4];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) row.load(c0 + u, raw[u]);
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      uint32_t m = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (row.pos0(c0 + u) + e < length) m = max(m, row.image(raw[u][e]));
+      if constexpr (!kPacked) cell_max[c0 + u] = m;
+      else if ((c0 + u) % 2 == 0) cell_max[(c0 + u) / 2] = m >> 16;
+      else cell_max[(c0 + u) / 2] |= m & 0xffff0000u;
+      lm = max(lm, m);
+    }
+  }
+  // candidates >= T into the slots; every lane walks its own list of cells that reach T, all lanes in step: one load
+  // latency per step, not per cell
+  auto collect = [&](uint32_t T) {
+    unsigned long long need = 0;
+#pragma unroll
+    for (int c = 0; c < CELLS; ++c) {
+      bool reaches;
+      if constexpr (!kPacked) reaches = cell_max[c] >= T;
+      else reaches = (c % 2 == 0 ? cell_max[c / 2] & 0xffffu : cell_max[c / 2] >> 16) >= (T >> 16);
+      need |= (unsigned long long)(reaches ? 1u : 0u) << c;
+    }
+    int total = 0;
+    while (__any_sync(0xffffffffu, need != 0ull)) {
+      const bool active = need != 0ull;
+      const int c = active ? __ffsll((long long)need) - 1 : 0;
+      need &= need - 1ull;
+      uint32_t raw[4] = {0u, 0u, 0u, 0u};
+      if (active) row.load(c, raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t o = row.image(raw[e]);
+        append_slots(sl, warp, lane, total, active && row.exists(c, e) && o >= T, o, (uint32_t)(row.pos0(c) + e));
+      }
+    }
+    __syncwarp();
+    return total;
+  };
+  int total = collect(kth_largest_of_lanes(lm, k, lane));
+  if (total > kSlots) {                                    // a loose threshold (one lane with a low maximum): tighten it once
+    const uint32_t T2 = kth_image_of_full_slots(sl.o[warp], sl.p[warp], k, lane);
+    __syncwarp();
+    total = collect(T2);
+  }
+  if (total <= kSlots)
+    write_best_of_slots<DTYPE>(sl.o[warp], sl.p[warp], total, k, lane, descending, out_vals + r * out_stride, out_idx + r * out_stride);
+  else
+    topk_by_rounds<DTYPE, VEC>(row, k, descending, out_vals + r * out_stride, out_idx + r * out_stride);
+}
+
+// Longer rows: the row is streamed twice (the second pass from L2), with nothing kept per cell.
+template <int DTYPE, bool VEC>
+__global__ void __launch_bounds__(kThreads, 4)
+topk_stream_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ out_vals, int32_t* __restrict__ out_idx,
+                   int64_t rows, int length, int k, bool descending, int64_t out_stride) {
+  __shared__ WarpSlots sl;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x / 32;
+  const int64_t r = (int64_t)blockIdx.x * (kThreads / 32) + warp;
+  if (r >= rows) return;
+  const RowCells<DTYPE, VEC> row{src + r * length, length, lane, descending ? 0u : ~0u};
+  uint32_t lm = 0;
+  row.for_each_cell([&](int, const uint32_t (&o)[4]) { lm = max(max(lm, max(o[0], o[1])), max(o[2], o[3])); });
+  auto collect = [&](uint32_t T) {
+    int total = 0;
+    row.for_each_cell([&](int cell, const uint32_t (&o)[4]) {
+      const uint32_t top = max(max(o[0], o[1]), max(o[2], o[3]));
+      if (__any_sync(0xffffffffu, top >= T)) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          append_slots(sl, warp, lane, total, row.exists(cell, e) && o[e] >= T, o[e], (uint32_t)(row.pos0(cell) + e));
+      }
+    });
+    __syncwarp();
+    return total;
+  };
+  int total = collect(kth_largest_of_lanes(lm, k, lane));
+  if (total > kSlots) {                                    // a loose threshold: tighten it once
+    const uint32_t T2 = kth_image_of_full_slots(sl.o[warp], sl.p[warp], k, lane);
+    __syncwarp();
+    total = collect(T2);
+  }
+  if (total <= kSlots)
+    write_best_of_slots<DTYPE>(sl.o[warp], sl.p[warp], total, k, lane, descending, out_vals + r * out_stride, out_idx + r * out_stride);
+  else
+    topk_by_rounds<DTYPE, VEC>(row, k, descending, out_vals + r * out_stride, out_idx + r * out_stride);
+}
+
 // One CTA per row of up to 256 * ITEMS elements, images in registers (element j of a thread sits at
 // position thread + 256 j); longer rows are re-read from L1/L2 on every round (ITEMS == 0).
 template <int DTYPE, int ITEMS>
@@ -206,7 +528,25 @@ static int topk_dispatch(const void* src, void* vals, int32_t* idx, int64_t rows
                          bool desc, int64_t out_stride, cudaStream_t s) {
   const uint32_t* in = (const uint32_t*)src;
   uint32_t* ov = (uint32_t*)vals;
-  if (length <= 1024) {
+  const int64_t warp_grid = (rows + kThreads / 32 - 1) / (kThreads / 32);
+  const bool vec = aligned16(src) && length % 4 == 0;
+  // one warp per row: rows short enough for it to be the better split, or enough rows to fill the machine
+  if (k <= 32 && (length <= 1024 || (length <= 16384 && rows >= 4 * sm_count()))) {
+    TL_REQUIRE(warp_grid < (1ll << 31), "topk: too many rows");
+#define TL_TOPK_CELLS(CELLS)                                                                                                  \
+    if (vec) topk_cells_kernel<DTYPE, CELLS, true><<<(unsigned)warp_grid, kThreads, 0, s>>>(in, ov, idx, rows, (int)length, k, desc, out_stride); \
+    else topk_cells_kernel<DTYPE, CELLS, false><<<(unsigned)warp_grid, kThreads, 0, s>>>(in, ov, idx, rows, (int)length, k, desc, out_stride)
+    if (length <= 256) { TL_TOPK_CELLS(2); }
+    else if (length <= 512) { TL_TOPK_CELLS(4); }
+    else if (length <= 1024) { TL_TOPK_CELLS(8); }
+    else if (length <= 2048) { TL_TOPK_CELLS(16); }
+    else if (length <= 4096) { TL_TOPK_CELLS(32); }
+    else if (length <= 8192) { TL_TOPK_CELLS(64); }
+    else if (vec) topk_stream_kernel<DTYPE, true><<<(unsigned)warp_grid, kThreads, 0, s>>>(in, ov, idx, rows, (int)length, k, desc, out_stride);
+    else topk_stream_kernel<DTYPE, false><<<(unsigned)warp_grid, kThreads, 0, s>>>(in, ov, idx, rows, (int)length, k, desc, out_stride);
+#undef TL_TOPK_CELLS
+    TL_LAUNCH_CHECK("topk_cells_kernel");
+  } else if (length <= 1024) {
     int64_t grid = (rows + kThreads / 32 - 1) / (kThreads / 32);
     TL_REQUIRE(grid < (1ll << 31), "topk: too many rows");
     if (length <= 256)
