@@ -159,7 +159,8 @@ int tl_b200_topk(const void* src, void* out_vals, int32_t* out_idx, int64_t rows
 int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
                  int in_dtype, int out_dtype, void* stream);
 /* The same with the width of the C tile chosen by the caller: tile_n 64, 128 or 256 columns (0 = the
- * library's own rule, the widest tile that still gives every SM one).  For a shape -> tile table kept by
+ * library's own rule, the widest tile that still gives every SM one), or 512 = tiles of 256 x 256 computed
+ * by pairs of CTAs on neighbouring SMs (each loads half of the tile's B).  For a shape -> tile table kept by
  * the host (role of the reference's tuner, tilelang/autotuner/__init__.py:90-345).  Results do not depend
  * on the choice.                                                                                        */
 int tl_b200_gemm_tiled(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,

@@ -85,7 +85,7 @@ def gemm_bf16(dev, rank, world, peaks, m=8192, n=28672, k=8192):
     c = so.local
     ms = _time(lambda: ops.gemm(a, b, c), world)
     ms_g = _time(lambda: (ops.gemm(a, b, c), so.gather()), world, reps=3, warmup=2) if world > 1 else ms
-    return _entry("gemm_tcgen05_kernel", f"bf16 M{m} K{k} N{n}, B row-major [K,N]", 2.0 * m * n * k, 1e12, "TFLOP/s",
+    return _entry("gemm_pair_kernel", f"bf16 M{m} K{k} N{n}, B row-major [K,N]", 2.0 * m * n * k, 1e12, "TFLOP/s",
                   ms, ms_g, peaks["bf16_tflops"], peaks["note"], f"N columns / {world}", 1)
 
 
@@ -100,7 +100,7 @@ def gemm_fp8_plain(dev, rank, world, peaks, m=8192, n=28672, k=8192):
     c = so.local
     ms = _time(lambda: ops.gemm(a8, b8, c, True), world)
     ms_g = _time(lambda: (ops.gemm(a8, b8, c, True), so.gather()), world, reps=3, warmup=2) if world > 1 else ms
-    return _entry("gemm_tcgen05_kernel (e4m3 operands)", f"e4m3 M{m} K{k} N{n}, B [N,K], no scales, bf16 out", 2.0 * m * n * k,
+    return _entry("gemm_pair_kernel (e4m3 operands)", f"e4m3 M{m} K{k} N{n}, B [N,K], no scales, bf16 out", 2.0 * m * n * k,
                   1e12, "TFLOP/s", ms, ms_g, 2 * peaks["bf16_tflops"], "2 x " + peaks["note"] + " (no FP8 peak was measured)",
                   f"N columns / {world}", 1)
 

@@ -15,11 +15,11 @@ def gen(seed):
     return torch.Generator(device="cpu").manual_seed(seed)
 
 
-def run(a, b, out_dtype, transpose_b, dev):
+def run(a, b, out_dtype, transpose_b, dev, tile_n=None):
     m = a.shape[0]
     n = b.shape[0] if transpose_b else b.shape[1]
     c = torch.full((m, n), float("nan"), dtype=out_dtype, device=dev)
-    assert ops.gemm(a.to(dev), b.to(dev), c, transpose_b) == 0
+    assert ops.gemm(a.to(dev), b.to(dev), c, transpose_b, tile_n=tile_n) == 0
     torch.cuda.synchronize()
     assert ops.device_status() == 0
     return c.cpu()
@@ -164,3 +164,45 @@ def test_gemm_e4m3_operands(cuda_device, transpose_b, m, n, k):
     ai = torch.randint(-3, 4, (m, k), generator=g).float().to(F8)
     bi = torch.randint(-3, 4, (n, k) if transpose_b else (k, n), generator=g).float().to(F8)
     assert torch.equal(run(ai, bi, F32, transpose_b, cuda_device), O.matmul(ai.float(), bi.float(), F32, transpose_b))
+
+
+PAIR = 512          # tile_n value of the CTA-pair kernel: 256 x 256 tiles of C, each on two SMs (cta_group::2)
+
+
+@pytest.mark.parametrize("transpose_b", [False, True])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (256, 256, 1024), (512, 768, 256), (200, 136, 72), (129, 264, 200),
+                                   (1, 8, 8), (384, 1288, 520), (2048, 4096, 512), (5000, 2304, 640)])
+def test_gemm_cta_pair_tiles(cuda_device, transpose_b, m, n, k):
+    """The CTA-pair kernel against the oracle on full, ragged and tiny shapes (rows and columns past the edge are
+    zero-filled by the loads and masked by the stores), and bit-exact on small integers in every operand type."""
+    g = gen(m * 5 + n * 3 + k + 1)
+    for dtype in (BF, HF):
+        a = torch.randn(m, k, generator=g).to(dtype)
+        b = (torch.randn(n, k, generator=g) if transpose_b else torch.randn(k, n, generator=g)).to(dtype)
+        ref32 = O.matmul(a, b, F32, transpose_b)
+        c = run(a, b, dtype, transpose_b, cuda_device, PAIR)
+        assert torch.allclose(c.float(), ref32.to(dtype).float(), **TOL16)
+        c32 = run(a, b, F32, transpose_b, cuda_device, PAIR)
+        assert ((c32.double() - ref32.double()).abs() <= 1e-3 * k ** 0.5 + 1e-4 * ref32.double().abs()).all()
+    ai = torch.randint(-4, 5, (m, k), generator=g).to(BF)
+    bi = torch.randint(-4, 5, (n, k) if transpose_b else (k, n), generator=g).to(BF)
+    refi = O.matmul(ai, bi, F32, transpose_b)
+    assert torch.equal(run(ai, bi, F32, transpose_b, cuda_device, PAIR), refi)
+    # the pair kernel and the one-CTA kernel add the same products in the same order per output element
+    assert torch.equal(run(a, b, F32, transpose_b, cuda_device, PAIR), run(a, b, F32, transpose_b, cuda_device, 256))
+
+
+@pytest.mark.parametrize("transpose_b", [False, True])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 128), (512, 768, 384), (200, 144, 80), (1024, 1024, 1024), (384, 1296, 528)])
+def test_gemm_cta_pair_tiles_e4m3(cuda_device, transpose_b, m, n, k):
+    F8 = torch.float8_e4m3fn
+    g = gen(m + 3 * n + 7 * k)
+    a = torch.randn(m, k, generator=g).to(F8)
+    b = (torch.randn(n, k, generator=g) if transpose_b else torch.randn(k, n, generator=g)).to(F8)
+    ref = O.matmul(a.float(), b.float(), F32, transpose_b)
+    c = run(a, b, F32, transpose_b, cuda_device, PAIR)
+    assert ((c.double() - ref.double()).abs() <= 1e-4 * k ** 0.5 + 1e-5 * ref.double().abs()).all()
+    assert torch.allclose(run(a, b, BF, transpose_b, cuda_device, PAIR).float(), ref.to(BF).float(), **TOL16)
+    ai = torch.randint(-3, 4, (m, k), generator=g).float().to(F8)
+    bi = torch.randint(-3, 4, (n, k) if transpose_b else (k, n), generator=g).float().to(F8)
+    assert torch.equal(run(ai, bi, F32, transpose_b, cuda_device, PAIR), O.matmul(ai.float(), bi.float(), F32, transpose_b))

@@ -1,5 +1,8 @@
 // Dense GEMM  C[M,N] = A[M,K] * B  with fp32 accumulation.
 //
+// Large products run on CTA pairs (`gemm_pair_kernel` below: 256 x 256 tiles, cta_group::2); smaller ones on the
+// one-CTA kernel described first.
+//
 // The 16-bit path is a persistent, warp-specialised tcgen05 kernel: TMA brings 128xBK tiles of A
 // and BNxBK tiles of B into a shared-memory ring (128-byte swizzle), one thread issues
 // tcgen05.mma into a double-buffered fp32 accumulator in tensor memory, and four epilogue warps
@@ -24,6 +27,7 @@ constexpr int kRowBytes = 128;   // K bytes per stage row: one 128-byte swizzle 
 constexpr int kUmmaBytes = 32;  // K bytes of one tcgen05.mma (16 16-bit or 32 8-bit elements)
 constexpr int kGemmThreads = 256;
 constexpr int kEpiWarp0 = 4;    // warps 4..7 form the epilogue (warp%4 selects the TMEM lane quarter)
+constexpr int kTilePair = 512;  // tile_n value that selects 256 x 256 tiles on CTA pairs
 
 template <int BN> struct GemmCfg {
   static constexpr int kStageA = kBM * kRowBytes;
@@ -251,6 +255,198 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   }
 }
 
+
+// =================================================================================
+// The same kernel on CTA pairs: one 256 x 256 tile of C per two SMs
+// =================================================================================
+// Two CTAs of a cluster (neighbouring SMs) own rows [0,128) and [128,256) of the tile.  Each loads its 128 rows of A
+// and only HALF of the tile's B (128 of the 256 N rows); the MMAs (cta_group::2, M = 256, N = 256), issued by one
+// thread of the even CTA, read B from both shared memories.  Per SM that halves the B bytes fetched from L2 and read
+// from shared memory per flop, and leaves room for six stages.  Barriers: the even CTA's `full` barrier counts the
+// bytes of both CTAs' loads; `empty` and `tfull` exist in both CTAs and the issuing thread commits to each; the even
+// CTA's `tempty` collects the eight epilogue warps of both.
+struct GemmPairCfg {
+  static constexpr int kBN = 256;                    // columns of the pair's tile
+  static constexpr int kHalfN = kBN / 2;             // B rows held by one CTA
+  static constexpr int kStageA = kBM * kRowBytes;
+  static constexpr int kStageB = kHalfN * kRowBytes;
+  static constexpr int kStages = 6;
+  static constexpr int kTmemCols = 2 * kBN;
+  static constexpr int kSmemBytes = kStages * (kStageA + kStageB) + 1024 + 256;
+};
+
+template <bool B_MN_MAJOR, typename TOut, int EB>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 const GemmParams p) {
+  using Cfg = GemmPairCfg;
+  constexpr int STAGES = Cfg::kStages;
+  constexpr int BN = Cfg::kBN;
+  constexpr int kBK = kRowBytes / EB;
+  constexpr int kSlabCols = kRowBytes / EB;
+  constexpr int kSlabBytes = kBK * kRowBytes;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw_addr);
+  const uint32_t smem_a = base;
+  const uint32_t smem_b = base + STAGES * Cfg::kStageA;
+  uint8_t* tail = base_ptr + STAGES * (Cfg::kStageA + Cfg::kStageB);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(tail);         // full[S], empty[S], tfull[2], tempty[2]
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * STAGES;
+  const uint32_t bar_tempty = bar_tfull + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x / 32;
+  const int lane = threadIdx.x % 32;
+  const uint32_t rank = cluster_ctarank();                    // 0: issues the MMAs
+  const int pair = blockIdx.x / 2, num_pairs = gridDim.x / 2;
+  const int num_kb = (p.k + kBK - 1) / kBK;
+  const int num_tiles = p.tiles_m * p.tiles_n;                // tiles of 256 x 256
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 8);      // one arrival per epilogue warp of both CTAs (used in the even CTA)
+    }
+    mbar_fence_init();
+    prefetch_tensormap(&tm_a);
+    prefetch_tensormap(&tm_b);
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();                        // both CTAs' barriers and tensor memory exist before anything is signalled
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int row0 = tm * 2 * kBM + (int)rank * kBM;          // this CTA's rows of A
+        const int col0 = tn * BN + (int)rank * Cfg::kHalfN;       // this CTA's rows of B (columns of C)
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag))) break;
+          if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * (Cfg::kStageA + Cfg::kStageB));
+          const uint32_t full = map_to_cta(bar_full + 8 * stage, 0);
+          tma_load_2d_pair(smem_a + stage * Cfg::kStageA, &tm_a, full, kb * kBK, row0);
+          if constexpr (B_MN_MAJOR) {
+#pragma unroll
+            for (int j = 0; j < Cfg::kHalfN / kSlabCols; ++j)
+              tma_load_2d_pair(smem_b + stage * Cfg::kStageB + j * kSlabBytes, &tm_b, full, col0 + j * kSlabCols,
+                               kb * kBK);
+          } else {
+            tma_load_2d_pair(smem_b + stage * Cfg::kStageB, &tm_b, full, kb * kBK, col0);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1 && rank == 0) {
+    // ------------------------------------------------------------------ MMA issuer (even CTA only)
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc(p.in_fmt, p.in_fmt, false, B_MN_MAJOR, 2 * kBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!(ok = mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag))) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag))) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_a + stage * Cfg::kStageA;
+          const uint32_t b_addr = smem_b + stage * Cfg::kStageB;
+#pragma unroll
+          for (int kk = 0; kk < kRowBytes / kUmmaBytes; ++kk) {
+            const uint64_t a_desc = smem_desc_sw128(a_addr + kk * kUmmaBytes, 16, 1024);
+            uint64_t b_desc;
+            if constexpr (B_MN_MAJOR)
+              b_desc = smem_desc_sw128(b_addr + kk * (kUmmaBytes / EB * kRowBytes), kSlabBytes, 1024);
+            else
+              b_desc = smem_desc_sw128(b_addr + kk * kUmmaBytes, 16, 1024);
+            if constexpr (EB == 2) mma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            else mma_f8_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          mma_commit_pair(bar_empty + 8 * stage);                        // the stage is free in this CTA ...
+          mma_commit_pair(map_to_cta(bar_empty + 8 * stage, 1));         // ... and in the other
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) {
+          mma_commit_pair(bar_tfull + 8 * acc);
+          mma_commit_pair(map_to_cta(bar_tfull + 8 * acc, 1));
+        }
+      }
+    }
+  } else if (warp >= kEpiWarp0) {
+    // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int quarter = warp - kEpiWarp0;
+    TOut* c = reinterpret_cast<TOut*>(p.c);
+    const bool vec_ok = (p.ldc * sizeof(TOut)) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.c) & 15u) == 0;
+    int local = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+      int tm, tn;
+      tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      ok = mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after_sync();
+      const int row = tm * 2 * kBM + (int)rank * kBM + quarter * 32 + lane;
+      const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int cchunk = 0; cchunk < BN / 32; ++cchunk) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_addr + cchunk * 32, v);
+        tmem_ld_wait();
+        const int col = tn * BN + cchunk * 32;
+        if (row < p.m && col < p.n)
+          store_row_chunk<TOut>(c + (int64_t)row * p.ldc + col, v, min(32, p.n - col), vec_ok);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * acc, 0));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    if (threadIdx.x == 0 && p.status) *p.status = *abort_flag;
+    __syncthreads();
+  }
+  // neither CTA may leave (or free tensor memory) while the other can still read its shared memory or signal its barriers
+  tc_fence_before_sync();
+  cluster_sync_all();
+  if (warp == 2) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+  }
+}
+
 // =================================================================================
 // Plain FMA kernel: any of fp32 / fp16 / bf16, any size and alignment.
 // =================================================================================
@@ -340,6 +536,31 @@ static int launch_tc_f8(const CUtensorMap& ta, const CUtensorMap& tb, const Gemm
   return b_mn ? launch_tc<BN, true, __half, 1>(ta, tb, p, s) : launch_tc<BN, false, __half, 1>(ta, tb, p, s);
 }
 
+
+template <bool B_MN, typename TOut, int EB>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t s) {
+  auto kernel = gemm_pair_kernel<B_MN, TOut, EB>;
+  TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmPairCfg::kSmemBytes));
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+  kernel<<<2 * pairs, kGemmThreads, GemmPairCfg::kSmemBytes, s>>>(ta, tb, p);      // cluster size 2 is a kernel attribute
+  TL_LAUNCH_CHECK("gemm_pair_kernel");
+  return TL_B200_OK;
+}
+template <typename T16>
+static int launch_pair_out(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, bool b_mn, int out_kind,
+                           cudaStream_t s) {
+  if constexpr (std::is_same<T16, uint8_t>::value) {
+    if (out_kind == 0) return b_mn ? launch_pair<true, float, 1>(ta, tb, p, s) : launch_pair<false, float, 1>(ta, tb, p, s);
+    if (out_kind == 1)
+      return b_mn ? launch_pair<true, __nv_bfloat16, 1>(ta, tb, p, s) : launch_pair<false, __nv_bfloat16, 1>(ta, tb, p, s);
+    return b_mn ? launch_pair<true, __half, 1>(ta, tb, p, s) : launch_pair<false, __half, 1>(ta, tb, p, s);
+  } else {
+    if (p.c_is_f32) return b_mn ? launch_pair<true, float, 2>(ta, tb, p, s) : launch_pair<false, float, 2>(ta, tb, p, s);
+    return b_mn ? launch_pair<true, T16, 2>(ta, tb, p, s) : launch_pair<false, T16, 2>(ta, tb, p, s);
+  }
+}
+
 // T16 = uint8_t selects the e4m3 form (out_kind as above); otherwise the 16-bit operand type
 template <typename T16>
 static int gemm_tc(const void* a, const void* b, void* c, int m, int n, int k, bool trans_b, bool c_f32,
@@ -357,6 +578,10 @@ static int gemm_tc(const void* a, const void* b, void* c, int m, int n, int k, b
   if (tiles_for(256) < sm_count()) bn = 128;
   if (bn == 128 && tiles_for(128) < sm_count()) bn = 64;
   if (tile_n == 64 || tile_n == 128 || tile_n == 256) bn = tile_n;     // the caller's choice (a tuned table)
+  // 256 x 256 tiles on CTA pairs: the caller's choice, or the library's whenever every pair of SMs gets a tile
+  const int64_t pair_tiles = (int64_t)((m + 2 * kBM - 1) / (2 * kBM)) * ((n + GemmPairCfg::kBN - 1) / GemmPairCfg::kBN);
+  const bool pair = tile_n == kTilePair || (tile_n == 0 && pair_tiles >= sm_count() / 2);
+  if (pair) bn = GemmPairCfg::kHalfN;                                  // width of the B box one CTA loads
 
   CUtensorMap ta, tb;
   {
@@ -389,6 +614,11 @@ static int gemm_tc(const void* a, const void* b, void* c, int m, int n, int k, b
   p.in_fmt = is_f8 ? kFmtE4M3 : (is_bf16 ? kFmtBF16 : kFmtF16);
   p.status = device_status_word();
   const bool b_mn = !trans_b;
+  if (pair) {
+    p.tiles_m = (m + 2 * kBM - 1) / (2 * kBM);
+    p.tiles_n = (n + GemmPairCfg::kBN - 1) / GemmPairCfg::kBN;
+    return launch_pair_out<T16>(ta, tb, p, b_mn, out_kind, s);
+  }
   if constexpr (is_f8) {
     if (bn < 128 && b_mn) bn = 128;       // an MN-major slab of 8-bit columns is 128 columns wide
     p.tiles_n = (n + bn - 1) / bn;
@@ -417,7 +647,8 @@ extern "C" int tl_b200_gemm(const void* a, const void* b, void* c, int64_t m, in
 
 extern "C" int tl_b200_gemm_tiled(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k, int trans_b,
                                   int in_dtype, int out_dtype, int tile_n, void* stream) {
-  TL_REQUIRE(tile_n == 0 || tile_n == 64 || tile_n == 128 || tile_n == 256, "gemm: tile_n must be 0, 64, 128 or 256");
+  TL_REQUIRE(tile_n == 0 || tile_n == 64 || tile_n == 128 || tile_n == 256 || tile_n == kTilePair,
+             "gemm: tile_n must be 0, 64, 128, 256 or 512 (a 256 x 256 tile on a CTA pair)");
   TL_REQUIRE(m >= 0 && n >= 0 && k >= 0, "gemm: negative size");
   TL_REQUIRE(m < (1ll << 31) && n < (1ll << 31) && k < (1ll << 31), "gemm: dimension exceeds 2^31");
   if (m == 0 || n == 0) return TL_B200_OK;
