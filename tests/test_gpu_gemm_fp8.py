@@ -38,8 +38,11 @@ def test_golden_quantised_operands(cuda_device):
     assert torch.allclose(out16.float(), ref, atol=2e-2, rtol=2e-2)
 
 
+# the shapes of the second line give every pair of SMs a 256 x 128 tile and so run on CTA pairs, with ragged edges in
+# both directions (300 rows: the odd CTA of the last row block has no row at all)
 @pytest.mark.parametrize("m,n,k", [(128, 128, 128), (256, 384, 512), (200, 136, 256), (1, 8, 128), (130, 1000, 384),
-                                   (1024, 2048, 1024)])
+                                   (1024, 2048, 1024),
+                                   (2000, 1300, 256), (2304, 1280, 384), (300, 9600, 128), (4096, 4096, 512)])
 def test_shapes(cuda_device, m, n, k):
     a8, b8, sa, sb = quantised(m, n, k, m + n + k)
     ref = O.gemm_fp8_blockscale(a8, b8, sa, sb, torch.float32)

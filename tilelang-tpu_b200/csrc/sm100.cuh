@@ -242,8 +242,11 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
+// Arrive on a barrier of this or the other CTA.  Default (CTA-scope) release: what is handed over is tensor memory,
+// ordered by the tcgen05 fences on both sides; a cluster-scope release made every arrival wait out the warp's loads
+// in flight (measured: 0.85 us per K block in the block-scaled GEMM).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // One warp of EACH CTA of the pair executes these.
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t slot, uint32_t columns) {
