@@ -39,8 +39,10 @@ def unfused(x, wg, wu, dev):
 
 
 @pytest.mark.parametrize("dtype", [BF, HF])
+# the shapes of the last line give every pair of SMs a 256-row tile and run on CTA pairs, ragged in both directions
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 384, 512), (64, 64, 64), (1024, 1024, 1024), (200, 136, 72),
-                                   (129, 264, 200), (1, 8, 8), (384, 1288, 520)])
+                                   (129, 264, 200), (1, 8, 8), (384, 1288, 520),
+                                   (2000, 1300, 256), (300, 9600, 72), (2304, 1280, 520)])
 def test_tensor_core_shapes(cuda_device, dtype, m, n, k):
     x, wg, wu = make(m, n, k, dtype, m * 7 + n * 3 + k)
     out = fused(x, wg, wu, cuda_device)

@@ -11,10 +11,14 @@
 // The down projection is a plain GEMM (tl_b200_gemm with trans_b).
 //
 // tcgen05 kernel: persistent, warp-specialised like the GEMM of gemm.cu.  A stage of the TMA ring
-// holds a 128x64 tile of x and 128x64 tiles of Wg and Wu (48 KB, 4 stages); one thread issues two
-// 128x128x16 MMAs per K step, into a gate and an up accumulator that sit side by side in tensor
-// memory (256 columns), double-buffered (512 columns) so that the four epilogue warps work on one
-// pair while the next tile's main loop runs.
+// holds a 128x64 tile of x and, one behind the other, 128x64 tiles of Wg and Wu (48 KB, 4 stages): together they
+// are ONE K-major B operand of 256 rows, so one thread issues one 128x256x16 MMA per K step and the gate and up
+// accumulators come out side by side in tensor memory (256 columns), double-buffered (512 columns) so that the
+// four epilogue warps work on one pair while the next tile's main loop runs.
+//
+// PAIR = true: the same on CTA pairs (cta_group::2, tiles of 256 rows x 128 output columns).  The B operand of the
+// pair's MMA (M = 256, N = 256) takes its first 128 rows from the even CTA and the other 128 from the odd one, so
+// the even CTA loads only the Wg tile and the odd CTA only the Wu tile (32 KB per stage and CTA, 6 stages).
 #include "sm100.cuh"
 
 #include <type_traits>
@@ -25,7 +29,6 @@ using namespace sm100;
 constexpr int kMlpBM = 128, kMlpBN = 128, kMlpBK = 64, kMlpStages = 4, kMlpThreads = 256;
 constexpr int kMlpStageA = kMlpBM * kMlpBK * 2, kMlpStageB = kMlpBN * kMlpBK * 2;
 constexpr int kMlpStage = kMlpStageA + 2 * kMlpStageB;
-constexpr int kMlpSmem = kMlpStages * kMlpStage + 1024 /*alignment*/ + 256 /*barriers*/;
 
 struct MlpParams {
   void* out;
@@ -48,35 +51,47 @@ __device__ __forceinline__ void mlp_tile_coords(int tile, int tiles_m, int tiles
 
 template <typename T> __device__ __forceinline__ float round_through(float v) { return to_f32(from_f32<T>(v)); }
 
-template <typename T>
+template <bool PAIR> struct MlpCfg {
+  static constexpr int kStages = PAIR ? 6 : kMlpStages;
+  static constexpr int kStage = PAIR ? kMlpStageA + kMlpStageB : kMlpStage;   // a pair's CTA holds x and ONE weight tile
+  static constexpr int kTileM = PAIR ? 2 * kMlpBM : kMlpBM;
+  static constexpr int kSmem = kStages * kStage + 1024 + 256;
+};
+
+template <typename T, bool PAIR>
 __global__ void __launch_bounds__(kMlpThreads, 1)
 mlp_gate_up_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_g,
                            const __grid_constant__ CUtensorMap tm_u, const MlpParams p) {
+  using Cfg = MlpCfg<PAIR>;
+  constexpr int STAGES = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;          // swizzle atoms need 1024-byte alignment
   uint8_t* base_ptr = smem_raw + (base - raw_addr);
-  uint8_t* tail = base_ptr + kMlpStages * kMlpStage;
+  uint8_t* tail = base_ptr + STAGES * Cfg::kStage;
   const uint32_t bar_full = smem_u32(tail);                   // full[S], empty[S], tfull[2], tempty[2]
-  const uint32_t bar_empty = bar_full + 8 * kMlpStages;
-  const uint32_t bar_tfull = bar_empty + 8 * kMlpStages;
+  const uint32_t bar_empty = bar_full + 8 * STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * STAGES;
   const uint32_t bar_tempty = bar_tfull + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * kMlpStages + 4));
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tail + 8 * (2 * STAGES + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int num_kb = (p.k + kMlpBK - 1) / kMlpBK;
   const int num_tiles = p.tiles_m * p.tiles_n;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;          // pairs: rank 0 issues the MMAs
+  const int unit = PAIR ? blockIdx.x / 2 : blockIdx.x;          // tiles are dealt to CTAs, or to pairs
+  const int units = PAIR ? gridDim.x / 2 : gridDim.x;
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    for (int s = 0; s < kMlpStages; ++s) {
+    for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
-      mbar_init(bar_tempty + 8 * a, 4);      // one arrival per epilogue warp
+      mbar_init(bar_tempty + 8 * a, PAIR ? 8 : 4);      // one arrival per epilogue warp (pairs: of both CTAs)
     }
     mbar_fence_init();
     prefetch_tensormap(&tm_x);
@@ -84,11 +99,17 @@ mlp_gate_up_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
     prefetch_tensormap(&tm_u);
   }
   if (warp == 2) {
-    tmem_alloc(smem_u32(tmem_slot), 512);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(tmem_slot), 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
-  __syncthreads();
+  if constexpr (PAIR) cluster_sync_all();     // both CTAs' barriers and tensor memory exist before anything is signalled
+  else __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -98,51 +119,73 @@ mlp_gate_up_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int tile = unit; tile < num_tiles && ok; tile += units) {
         int tm, tn;
         mlp_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        const int x_row = tm * Cfg::kTileM + (int)rank * kMlpBM;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!(ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag))) break;
-          const uint32_t full = bar_full + 8 * stage;
-          const uint32_t st = base + stage * kMlpStage;
-          mbar_expect_tx(full, kMlpStage);
-          tma_load_2d(st, &tm_x, full, kb * kMlpBK, tm * kMlpBM);
-          tma_load_2d(st + kMlpStageA, &tm_g, full, kb * kMlpBK, tn * kMlpBN);
-          tma_load_2d(st + kMlpStageA + kMlpStageB, &tm_u, full, kb * kMlpBK, tn * kMlpBN);
-          if (++stage == kMlpStages) { stage = 0; phase ^= 1; }
+          const uint32_t st = base + stage * Cfg::kStage;
+          if constexpr (PAIR) {
+            // the even CTA's barrier counts the bytes of both CTAs' loads; the even CTA brings Wg, the odd one Wu
+            if (rank == 0) mbar_expect_tx(bar_full + 8 * stage, 2 * Cfg::kStage);
+            const uint32_t full = map_to_cta(bar_full + 8 * stage, 0);
+            tma_load_2d_pair(st, &tm_x, full, kb * kMlpBK, x_row);
+            tma_load_2d_pair(st + kMlpStageA, rank == 0 ? &tm_g : &tm_u, full, kb * kMlpBK, tn * kMlpBN);
+          } else {
+            const uint32_t full = bar_full + 8 * stage;
+            mbar_expect_tx(full, Cfg::kStage);
+            tma_load_2d(st, &tm_x, full, kb * kMlpBK, x_row);
+            tma_load_2d(st + kMlpStageA, &tm_g, full, kb * kMlpBK, tn * kMlpBN);
+            tma_load_2d(st + kMlpStageA + kMlpStageB, &tm_u, full, kb * kMlpBK, tn * kMlpBN);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 && rank == 0) {
     // ------------------------------------------------------------------ MMA issuer
     if (elect_one()) {
-      const uint32_t idesc = make_idesc(p.in_fmt, p.in_fmt, false, false, kMlpBM, kMlpBN);
+      // N = 256: gate columns [0,128), up columns [128,256) of the accumulator
+      const uint32_t idesc = make_idesc(p.in_fmt, p.in_fmt, false, false, Cfg::kTileM, 2 * kMlpBN);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int tile = unit; tile < num_tiles && ok; tile += units, ++local) {
         const int acc = local & 1;
         if (!(ok = mbar_wait(bar_tempty + 8 * acc, ((local >> 1) & 1) ^ 1, abort_flag))) break;
         tc_fence_after_sync();
-        const uint32_t d_gate = tmem_base + acc * 256, d_up = d_gate + 128;
+        const uint32_t d_tmem = tmem_base + acc * 256;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!(ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag))) break;
           tc_fence_after_sync();
-          const uint32_t st = base + stage * kMlpStage;
+          const uint32_t st = base + stage * Cfg::kStage;
 #pragma unroll
           for (int kk = 0; kk < kMlpBK / 16; ++kk) {
-            // all three operands are K-major: 8-row groups 1024 B apart, a K step of 16 elements is 32 B
+            // K-major operands: 8-row groups 1024 B apart, a K step of 16 elements is 32 B.  B is the Wg tile followed
+            // by the Wu tile (one CTA: 256 rows in this shared memory; pairs: 128 rows in each CTA's)
             const uint64_t a_desc = smem_desc_sw128(st + kk * 32, 16, 1024);
-            const uint64_t g_desc = smem_desc_sw128(st + kMlpStageA + kk * 32, 16, 1024);
-            const uint64_t u_desc = smem_desc_sw128(st + kMlpStageA + kMlpStageB + kk * 32, 16, 1024);
-            mma_f16_ss(d_gate, a_desc, g_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
-            mma_f16_ss(d_up, a_desc, u_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            const uint64_t b_desc = smem_desc_sw128(st + kMlpStageA + kk * 32, 16, 1024);
+            if constexpr (PAIR) mma_f16_ss_pair(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            else mma_f16_ss(d_tmem, a_desc, b_desc, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
-          mma_commit(bar_empty + 8 * stage);          // stage is free once these MMAs retire
-          if (++stage == kMlpStages) { stage = 0; phase ^= 1; }
+          if constexpr (PAIR) {                         // the stage is free in both CTAs once these MMAs retire
+            mma_commit_pair(bar_empty + 8 * stage);
+            mma_commit_pair(map_to_cta(bar_empty + 8 * stage, 1));
+          } else {
+            mma_commit(bar_empty + 8 * stage);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) mma_commit(bar_tfull + 8 * acc);      // both accumulators complete
+        if (ok) {                                       // both accumulators complete
+          if constexpr (PAIR) {
+            mma_commit_pair(bar_tfull + 8 * acc);
+            mma_commit_pair(map_to_cta(bar_tfull + 8 * acc, 1));
+          } else {
+            mma_commit(bar_tfull + 8 * acc);
+          }
+        }
       }
     }
   } else if (warp >= 4) {
@@ -152,7 +195,7 @@ mlp_gate_up_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
     const bool vec_ok = ((int64_t)p.n * sizeof(T)) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
     int local = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+    for (int tile = unit; tile < num_tiles && ok; tile += units, ++local) {
       int tm, tn;
       mlp_tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
       const int acc = local & 1;
@@ -160,7 +203,7 @@ mlp_gate_up_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
       ok = __all_sync(0xffffffffu, ok);             // keep the warp together for the aligned loads
       if (!ok) break;
       tc_fence_after_sync();
-      const int row = tm * kMlpBM + quarter * 32 + lane;
+      const int row = tm * Cfg::kTileM + (int)rank * kMlpBM + quarter * 32 + lane;
       const uint32_t t_gate = tmem_base + acc * 256 + ((uint32_t)(quarter * 32) << 16);
 #pragma unroll 1
       for (int cchunk = 0; cchunk < kMlpBN / 32; ++cchunk) {
@@ -198,7 +241,10 @@ mlp_gate_up_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+      if (lane == 0) {
+        if constexpr (PAIR) mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * acc, 0));
+        else mbar_arrive(bar_tempty + 8 * acc);
+      }
     }
   }
 
@@ -209,9 +255,15 @@ mlp_gate_up_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_x, const __gri
     if (threadIdx.x == 0 && p.status) *p.status = *abort_flag;
     __syncthreads();
   }
+  if constexpr (PAIR) {
+    // neither CTA may leave (or free tensor memory) while the other can still read its shared memory or signal its barriers
+    tc_fence_before_sync();
+    cluster_sync_all();
+  }
   if (warp == 2) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
+    if constexpr (PAIR) tmem_dealloc_pair(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -280,15 +332,37 @@ static int mlp_gate_up_tc(const void* x, const void* wg, const void* wu, void* o
   MlpParams p;
   p.out = out;
   p.m = m; p.n = n; p.k = k;
-  p.tiles_m = (m + kMlpBM - 1) / kMlpBM;
   p.tiles_n = (n + kMlpBN - 1) / kMlpBN;
   p.in_fmt = is_bf16 ? kFmtBF16 : kFmtF16;
   p.status = device_status_word();
-  auto kernel = mlp_gate_up_tcgen05_kernel<T>;
-  TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kMlpSmem));
+  // CTA pairs (tiles of 256 rows) whenever every pair of SMs gets a tile
+  const int64_t pair_tiles = (int64_t)((m + 2 * kMlpBM - 1) / (2 * kMlpBM)) * p.tiles_n;
+  const bool pair = pair_tiles >= sm_count() / 2;
+  const int tile_m = pair ? 2 * kMlpBM : kMlpBM;
+  p.tiles_m = (m + tile_m - 1) / tile_m;
   const int tiles = p.tiles_m * p.tiles_n;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
-  kernel<<<grid, kMlpThreads, kMlpSmem, s>>>(tx, tg, tu, p);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  cfg.blockDim = dim3(kMlpThreads);
+  cfg.stream = s;
+  if (pair) {
+    auto kernel = mlp_gate_up_tcgen05_kernel<T, true>;
+    TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MlpCfg<true>::kSmem));
+    const int pairs = tiles < sm_count() / 2 ? tiles : sm_count() / 2;
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.dynamicSmemBytes = MlpCfg<true>::kSmem;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    TL_CUDA(cudaLaunchKernelEx(&cfg, kernel, tx, tg, tu, p));
+  } else {
+    auto kernel = mlp_gate_up_tcgen05_kernel<T, false>;
+    TL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, MlpCfg<false>::kSmem));
+    cfg.gridDim = dim3(tiles < sm_count() ? tiles : sm_count());
+    cfg.dynamicSmemBytes = MlpCfg<false>::kSmem;
+    TL_CUDA(cudaLaunchKernelEx(&cfg, kernel, tx, tg, tu, p));
+  }
   TL_LAUNCH_CHECK("mlp_gate_up_tcgen05_kernel");
   return TL_B200_OK;
 }

@@ -260,7 +260,7 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t base, uint32_t column
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns) : "memory");
 }
 // Tile load into THIS CTA's shared memory whose completion bytes are counted on a barrier that may live in the
-// other CTA of the pair (`bar_cluster` is a shared::cluster address).  No multicast: every CTA loads its own part.
+// other CTA of the pair (`bar_cluster` is a shared::cluster address).  Every CTA loads its own part; nothing is broadcast.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0,
                                                  int c1) {
   asm volatile(
