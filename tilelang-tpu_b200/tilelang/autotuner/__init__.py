@@ -116,8 +116,8 @@ def _time_ms(fn: Callable[[], Any], warmup: int, rep: int) -> float:
 
 def tune_gemm(m: int, n: int, k: int, dtype: torch.dtype = torch.bfloat16, transpose_b: bool = False,
               out_dtype: Optional[torch.dtype] = None, warmup: int = 3, rep: int = 10, store: bool = True) -> dict:
-    """Measure the C-tile widths of the tensor-core GEMM (64 / 128 / 256 columns) for one shape and record the
-    fastest in the tile table; `tilelang.ops.gemm` (and every matmul program bound to it) uses it from then on."""
+    """Measure the C-tile forms of the tensor-core GEMM (64 / 128 / 256 columns on one CTA, 256 x 256 on a CTA pair)
+    for one shape and record the fastest in the tile table; `tilelang.ops.gemm` (and every matmul program bound to it) uses it from then on."""
     from .. import ops
     from ..cache import set_tile_choice
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -126,7 +126,7 @@ def tune_gemm(m: int, n: int, k: int, dtype: torch.dtype = torch.bfloat16, trans
     b = torch.randn((n, k) if transpose_b else (k, n), generator=g, device=dev).to(dtype)
     c = torch.empty(m, n, dtype=out_dtype or (torch.bfloat16 if dtype == torch.float8_e4m3fn else dtype), device=dev)
     trials = {}
-    for tile_n in (64, 128, 256):
+    for tile_n in (64, 128, 256, 512):            # 512 = 256 x 256 tiles on CTA pairs
         try:
             trials[tile_n] = _time_ms(lambda: ops.gemm(a, b, c, transpose_b, tile_n=tile_n), warmup, rep)
         except RuntimeError as exc:
