@@ -269,7 +269,7 @@ def small_ops(dev, rank, world, peaks, rows=8192, cols=4096):
     yf = torch.empty(4 * rows, 1, device=dev)
     add("reduce_rows_kernel", f"row max fp32 [{4 * rows}, {cols}]", xf.numel() * 4 + 4 * rows * 4, lambda: ops.reduce_rows(xf, yf, "max"))
     zf = torch.empty_like(xf)
-    add("unary_kernel", f"sigmoid fp32 [{4 * rows}, {cols}]", xf.numel() * 8, lambda: ops.unary(xf, zf, "sigmoid"))
+    add("unary_vec_kernel", f"sigmoid fp32 [{4 * rows}, {cols}]", xf.numel() * 8, lambda: ops.unary(xf, zf, "sigmoid"))
     wf = torch.randn(4 * rows, cols, generator=g, device=dev)
     add("binary_kernel", f"add fp32 [{4 * rows}, {cols}]", xf.numel() * 12, lambda: ops.binary(xf, wf, zf, "add"))
     del wf

@@ -221,6 +221,22 @@ def test_sigmoid_golden_and_tile_ops(cuda_device):
     assert torch.equal(o16.cpu(), a.to(BF))
 
 
+def test_sigmoid_whole_range_vector_and_scalar_forms(cuda_device):
+    """fp32 sigmoid at 1e-5 over the whole range where the result is a normal number, on the 16-byte vector form
+    (size a multiple of 4) and on the scalar form (odd size, and a view that starts 4 bytes into an allocation)."""
+    x = torch.cat([torch.linspace(-87.0, 88.0, 8191), torch.tensor([0.0, -0.0, 1e-30, -1e-30, 17.0])])
+    ref = O.sigmoid(x)
+    for n in (x.numel(), x.numel() - 3):
+        y = torch.zeros(n, device=cuda_device)
+        ops.unary(x[:n].to(cuda_device), y, "sigmoid")
+        assert max_rel(y.cpu(), ref[:n]) < 1e-5
+    base = torch.zeros(x.numel() + 1, device=cuda_device)
+    base[1:] = x.to(cuda_device)
+    y = torch.zeros(x.numel(), device=cuda_device)
+    ops.unary(base[1:], y, "sigmoid")
+    assert max_rel(y.cpu(), ref) < 1e-5
+
+
 def test_bad_arguments_raise(cuda_device):
     x = torch.zeros(4, 4, dtype=BF, device=cuda_device)
     with pytest.raises(ValueError):
