@@ -24,7 +24,7 @@ using namespace sm100;
 
 constexpr int kF8BM = 128, kF8BN = 128, kF8BK = 128;
 constexpr int kF8Stages = 6;           // one CTA per tile; pairs: 8 stages of 24 KB
-constexpr int kF8Cols = 64;           // columns of a partial per promotion warp (32: sixteen warps, measured 4% slower at the C4 shape)
+constexpr int kF8Cols = 64;           // columns of a partial per promotion warp (32: sixteen warps, measured 4% slower at the C4 shape, on one CTA and on pairs)
 constexpr int kF8PromoWarps = 4 * (kF8BN / kF8Cols);        // 8: four lane quarters x two column groups
 constexpr int kF8PromoWarp0 = 4;      // warp 0 TMEM alloc + TMA, warp 1 MMA, warps 4.. promotion/epilogue
 constexpr int kF8Threads = (kF8PromoWarp0 + kF8PromoWarps) * 32;
