@@ -148,6 +148,13 @@ def mlp_gate_up(dev, rank, world, peaks, m=8192, n=14336, k=4096):
     e = _entry("mlp_gate_up_tcgen05_kernel", f"bf16 M{m} K{k} N{n}: silu(x Wg^T) * (x Wu^T), weights [N,K]",
                4.0 * m * n * k, 1e12, "TFLOP/s", ms, ms_g, peaks["bf16_tflops"], peaks["note"], f"N columns / {world}", 1)
     e["ms_unfused_two_gemms_plus_swiglu"] = ms_u
+    if world == 1:        # the whole MLP as the two-launch pipeline of ops.mlp (the down GEMM added): 6 M N K flop
+        del gate, up
+        wd = (torch.randn(k, n, generator=g, device=dev) * n ** -0.5).bfloat16()
+        y = torch.empty(m, k, dtype=torch.bfloat16, device=dev)
+        ms_full = _time(lambda: ops.mlp(x, wg, wu, wd, y, hidden=out), world)
+        e["full_mlp"] = {"ms": ms_full, "value": 6.0 * m * n * k / (ms_full * 1e-3) / 1e12, "unit": "TFLOP/s",
+                         "launches_per_call": 2}
     return e
 
 

@@ -204,6 +204,31 @@ def test_library_programs_fp8_gemm_and_paged_mla(cuda_device):
     assert torch.allclose(out[:, 0].float(), ref.float(), atol=2e-2, rtol=2e-2)
 
 
+def test_library_program_full_mlp(cuda_device):
+    """The gated MLP at full size (gate / up GEMM with the SiLU-product as epilogue, then the down GEMM) through the
+    compile / call convention, against the oracle's composition of the pinned matmul and swiglu; one shape on one
+    CTA per tile, one that gives every pair of SMs a tile (CTA pairs in both launches)."""
+    from tilelang import ops, programs as P
+    for (m, hidden, inter) in ((256, 384, 512), (2048, 1280, 1536)):
+        g = gen(m + hidden)
+        x = (torch.randn(m, hidden, generator=g) * 0.5).bfloat16()
+        wg, wu = [(torch.randn(inter, hidden, generator=g) * 0.05).bfloat16() for _ in range(2)]
+        wd = (torch.randn(hidden, inter, generator=g) * 0.05).bfloat16()
+        out = torch.zeros(m, hidden, dtype=torch.bfloat16)
+        kern = tilelang.compile(P.mlp(m, hidden, inter), out_idx=0, target="b200")
+        assert kern(out, x, wg, wu, wd) == 0
+        ref = O.mlp(x, wg, wu, wd)
+        assert torch.allclose(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
+        # the same two launches by hand give the same bits
+        dev = cuda_device
+        h = torch.empty(m, inter, dtype=torch.bfloat16, device=dev)
+        od = torch.empty(m, hidden, dtype=torch.bfloat16, device=dev)
+        ops.mlp_gate_up(x.to(dev), wg.to(dev), wu.to(dev), h)
+        ops.gemm(h, wd.to(dev), od, transpose_b=True)
+        assert torch.equal(out.view(torch.int16), od.cpu().view(torch.int16))
+        assert torch.allclose(h.cpu().float(), O.mlp_gate_up(x, wg, wu).float(), atol=2e-2, rtol=2e-2)
+
+
 def test_autotuner_and_tile_table(cuda_device, tmp_path, monkeypatch):
     """The tuner times program configurations on the GPU; `tune_gemm` fills the shape -> tile table that
     `ops.gemm` reads, and the result does not depend on the tile."""

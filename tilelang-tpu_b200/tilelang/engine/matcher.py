@@ -662,6 +662,9 @@ def _match_library_program(func: PrimFunc):
             def run(q, kv, table, lens, out):
                 return native.mla_decode_paged(q, kv, None, table, lens, out, dv=dv, softmax_scale=scale)
         return BoundKernel("mla_decode_paged", "tl_b200_mla_decode_paged", run, facts)
+    if kernel == "mlp":
+        return BoundKernel("mlp", "tl_b200_mlp_gate_up + tl_b200_gemm",
+                           lambda out, x, wg, wu, wd: native.mlp(x, wg, wu, wd, out), facts)
     raise UnsupportedProgram(f"unknown library kernel {kernel!r}")
 
 

@@ -299,6 +299,34 @@ def mlp_gate_up(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, out: 
 _MASK_MODES = {False: 0, None: 0, "none": 0, True: 1, "causal": 1, "block": 2}
 
 
+_mlp_hidden: dict = {}
+
+
+def mlp(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, out: torch.Tensor,
+        hidden: torch.Tensor | None = None) -> int:
+    """The gated MLP as one pipeline of two launches: hidden = silu(x Wg^T) * (x Wu^T) (SiLU-product in the epilogue of
+    the gate and up GEMMs), out = hidden Wd^T.  x (M, K); w_gate, w_up (N, K); w_down (K_out, N); out (M, K_out).
+    The only intermediate is `hidden` (M, N): the caller's buffer, or one kept per (device, stream, shape, dtype).
+    Roundings are where the reference program has them (tpu_demo/ppl/mlp/mlp_bf16.py:100-131)."""
+    if x.dim() != 2 or w_gate.dim() != 2 or w_down.dim() != 2:
+        raise ValueError("mlp: x (M, K), w_gate and w_up (N, K), w_down (K_out, N)")
+    m, n = x.shape[0], w_gate.shape[0]
+    if w_down.shape[1] != n:
+        raise ValueError("gemm K shape check failed")          # message of ppl_gemm's assert
+    if tuple(out.shape) != (m, w_down.shape[0]):
+        raise ValueError(f"mlp: out must be ({m}, {w_down.shape[0]})")
+    if hidden is None:
+        key = (x.device, torch.cuda.current_stream(x.device).cuda_stream, m, n, x.dtype)
+        hidden = _mlp_hidden.get(key)
+        if hidden is None:
+            _mlp_hidden.clear()                               # one shape at a time: no growth without bound
+            hidden = _mlp_hidden[key] = torch.empty(m, n, dtype=x.dtype, device=x.device)
+    elif tuple(hidden.shape) != (m, n) or hidden.dtype != x.dtype:
+        raise ValueError(f"mlp: hidden must be ({m}, {n}) of x's dtype")
+    rc = mlp_gate_up(x, w_gate, w_up, hidden)
+    return rc or gemm(hidden, w_down, out, transpose_b=True)
+
+
 def flash_attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, scale: float | None = None,
                    causal=False, block_m: int = 0, block_n: int = 0) -> int:
     """Attention forward on bshd tensors.  causal: False / True (key <= query) / "block" (the

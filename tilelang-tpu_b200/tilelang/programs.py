@@ -137,6 +137,16 @@ def gemm_fp8_blockscale(M: int, N: int, K: int, out_dtype: str = "bfloat16") -> 
         "gemm_fp8_blockscale", M=M, N=N, K=K)
 
 
+def mlp(M: int, hidden_size: int, intermediate_size: int, dtype: str = "bfloat16") -> PrimFunc:
+    """The gated MLP at full size: Out = (silu(X Wg^T) * (X Wu^T)) Wd^T with the roundings of the reference's per-tile
+    program (tpu_demo/ppl/mlp/mlp_bf16.py:57-136; same parameter order: output first)."""
+    return _library_program(
+        "mlp",
+        [("Out", (M, hidden_size), dtype), ("X", (M, hidden_size), dtype), ("Wg", (intermediate_size, hidden_size), dtype),
+         ("Wu", (intermediate_size, hidden_size), dtype), ("Wd", (hidden_size, intermediate_size), dtype)],
+        "mlp", M=M, hidden_size=hidden_size, intermediate_size=intermediate_size)
+
+
 def mla_decode_paged(batch: int, heads: int, d: int, dv: int, num_pages: int, page_size: int, max_pages: int,
                      dtype: str = "bfloat16", cache_dtype: str = "float8_e4m3", softmax_scale: float | None = None) -> PrimFunc:
     """Paged MLA decode, one query token per sequence (tensor layout of
