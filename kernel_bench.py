@@ -269,9 +269,10 @@ def small_ops(dev, rank, world, peaks, rows=8192, cols=4096):
         ms = _time(fn, 1, reps=10)
         out.append(_entry(name, config, nbytes, 1e9, "GB/s", ms, ms, peaks["hbm_gbs"], peaks["note"], "none", 1))
 
-    xb = torch.randn(rows, cols, generator=g, device=dev).bfloat16()
-    yb = torch.empty(rows, 1, dtype=torch.bfloat16, device=dev)
-    add("reduce_rows_kernel", f"row sum bf16 [{rows}, {cols}]", xb.numel() * 2 + rows * 2, lambda: ops.reduce_rows(xb, yb, "sum"))
+    xb = torch.randn(4 * rows, cols, generator=g, device=dev).bfloat16()        # 268 MB at the default size: above the L2
+    yb = torch.empty(4 * rows, 1, dtype=torch.bfloat16, device=dev)
+    add("reduce_rows_kernel", f"row sum bf16 [{4 * rows}, {cols}]", xb.numel() * 2 + 4 * rows * 2, lambda: ops.reduce_rows(xb, yb, "sum"))
+    del xb, yb
     xf = torch.randn(4 * rows, cols, generator=g, device=dev)
     yf = torch.empty(4 * rows, 1, device=dev)
     add("reduce_rows_kernel", f"row max fp32 [{4 * rows}, {cols}]", xf.numel() * 4 + 4 * rows * 4, lambda: ops.reduce_rows(xf, yf, "max"))

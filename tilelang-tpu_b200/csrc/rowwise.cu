@@ -451,13 +451,22 @@ reduce_rows_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int
     if constexpr (VEC) {
       const int64_t nvec = cols / VN;
       const uint4* xv = reinterpret_cast<const uint4*>(xr);
-      for (int64_t c = lane_in_row; c < nvec; c += TPR) {
-        Vec16<T> v;
-        v.raw = ld_stream16(xv + c);
+      // four independent 16-byte loads in flight per thread, then their elements
+      constexpr int U = 4;
+      for (int64_t c = lane_in_row; c < nvec; c += (int64_t)TPR * U) {
+        Vec16<T> v[U];
 #pragma unroll
-        for (int j = 0; j < VN; ++j) {
-          float f = to_f32(v.e[j]);
-          acc = IS_MAX ? fmaxf(acc, f) : acc + f;
+        for (int u = 0; u < U; ++u)
+          if (c + (int64_t)u * TPR < nvec) v[u].raw = ld_stream16(xv + c + (int64_t)u * TPR);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (c + (int64_t)u * TPR < nvec) {
+#pragma unroll
+            for (int j = 0; j < VN; ++j) {
+              float f = to_f32(v[u].e[j]);
+              acc = IS_MAX ? fmaxf(acc, f) : acc + f;
+            }
+          }
         }
       }
       done = nvec * VN;
