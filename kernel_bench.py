@@ -279,10 +279,10 @@ def small_ops(dev, rank, world, peaks, rows=8192, cols=4096):
     zf = torch.empty_like(xf)
     add("unary_vec_kernel", f"sigmoid fp32 [{4 * rows}, {cols}]", xf.numel() * 8, lambda: ops.unary(xf, zf, "sigmoid"))
     wf = torch.randn(4 * rows, cols, generator=g, device=dev)
-    add("binary_kernel", f"add fp32 [{4 * rows}, {cols}]", xf.numel() * 12, lambda: ops.binary(xf, wf, zf, "add"))
+    add("binary_vec_kernel", f"add fp32 [{4 * rows}, {cols}]", xf.numel() * 12, lambda: ops.binary(xf, wf, zf, "add"))
     del wf
     idx = torch.randint(0, 4 * rows, (4 * rows,), generator=g, device=dev, dtype=torch.int32)
-    add("gather_vec_kernel", f"gather {4 * rows} rows of {cols} fp32 from a [{4 * rows}, {cols}] table",
+    add("gather_rows_kernel", f"gather {4 * rows} rows of {cols} fp32 from a [{4 * rows}, {cols}] table",
         2 * 4 * rows * cols * 4 + 4 * rows * 4, lambda: ops.gather_rows(xf, idx, zf))
     k = 8
     tv = torch.empty(4 * rows, k, device=dev)

@@ -32,12 +32,13 @@ def test_gather_shapes(cuda_device, dtype, rows, hidden, n):
     assert torch.equal(out.cpu().view(torch.uint8), ref.view(torch.uint8))
 
 
-def test_gather_out_of_range_index_writes_zeros(cuda_device):
-    param = torch.ones(4, 8, device=cuda_device)
+@pytest.mark.parametrize("width", [8, 136, 520])         # 520 fp32 = 130 vectors: the warp-per-row form, ragged
+def test_gather_out_of_range_index_writes_zeros(cuda_device, width):
+    param = torch.ones(4, width, device=cuda_device)
     idx = torch.tensor([[0], [4], [3], [2 ** 31 - 1]], dtype=torch.int32, device=cuda_device)
-    out = torch.full((4, 8), 7.0, device=cuda_device)
+    out = torch.full((4, width), 7.0, device=cuda_device)
     ops.gather_rows(param, idx, out)
-    assert out.cpu().tolist() == [[1.0] * 8, [0.0] * 8, [1.0] * 8, [0.0] * 8]
+    assert out.cpu().tolist() == [[1.0] * width, [0.0] * width, [1.0] * width, [0.0] * width]
 
 
 def test_gather_empty(cuda_device):

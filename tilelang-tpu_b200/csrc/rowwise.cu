@@ -602,6 +602,37 @@ binary_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ 
   }
 }
 
+// fp32 tensors of equal shape (or a scalar second operand) on 16-byte aligned memory: four elements per access
+template <int OP, bool SCALAR>
+__global__ void __launch_bounds__(kThreads)
+binary_vec_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ out, int64_t n4,
+                  float scalar) {
+  const int64_t stride = (int64_t)gridDim.x * kThreads;
+  auto op = [](float x, float y) {
+    if constexpr (OP == 0) return x + y;
+    else if constexpr (OP == 1) return x - y;
+    else if constexpr (OP == 2) return x * y;
+    else if constexpr (OP == 3) return x / y;
+    else return fmaxf(x, y);
+  };
+  constexpr int U = 2;
+  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n4; i += stride * U) {
+    float4 av[U], bv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t k = i + u * stride;
+      av[u] = k < n4 ? __ldg(a + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+      if constexpr (SCALAR) bv[u] = make_float4(scalar, scalar, scalar, scalar);
+      else bv[u] = k < n4 ? __ldg(b + k) : make_float4(1.f, 1.f, 1.f, 1.f);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int64_t k = i + u * stride;
+      if (k < n4) out[k] = make_float4(op(av[u].x, bv[u].x), op(av[u].y, bv[u].y), op(av[u].z, bv[u].z), op(av[u].w, bv[u].w));
+    }
+  }
+}
+
 // Strided 2-D copy with a cast (a tile <-> a window of a larger tensor), and a 2-D fill.
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(kThreads)
@@ -706,6 +737,18 @@ static int unary_out(const void* x, void* y, int64_t n, int op, int out_dtype, c
 template <typename T, int OP>
 static int binary_mode(const void* a, const void* b, void* o, int64_t n, int64_t cols, int b_mode, float sc,
                        cudaStream_t s) {
+  if constexpr (std::is_same<T, float>::value) {
+    if ((b_mode == 0 || b_mode == 2) && n % 4 == 0 && aligned16(a) && aligned16(o) && (b_mode == 2 || aligned16(b))) {
+      const int64_t n4 = n / 4;
+      unsigned vgrid = elementwise_grid(n4, kThreads * 2);
+      if (b_mode == 0)
+        binary_vec_kernel<OP, false><<<vgrid, kThreads, 0, s>>>((const float4*)a, (const float4*)b, (float4*)o, n4, sc);
+      else
+        binary_vec_kernel<OP, true><<<vgrid, kThreads, 0, s>>>((const float4*)a, nullptr, (float4*)o, n4, sc);
+      TL_LAUNCH_CHECK("binary_vec_kernel");
+      return TL_B200_OK;
+    }
+  }
   unsigned grid = elementwise_grid(n, kThreads * 4);
   switch (b_mode) {
     case 0: binary_kernel<T, OP, 0><<<grid, kThreads, 0, s>>>((const T*)a, (const T*)b, (T*)o, n, cols, sc); break;

@@ -36,6 +36,33 @@ gather_vec_kernel(const uint4* __restrict__ param, const uint32_t* __restrict__ 
   }
 }
 
+// Rows of at least 32 vectors: one warp per output row (the source row is looked up once and no index arithmetic is
+// done per vector: a 64-bit division per 16 bytes made the kernel above issue-bound), UNROLL loads in flight per lane.
+template <int UNROLL>
+__global__ void __launch_bounds__(kThreads)
+gather_rows_kernel(const uint4* __restrict__ param, const uint32_t* __restrict__ index, uint4* __restrict__ out,
+                   int64_t n_index, int vec_per_row, uint32_t param_rows) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warps = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t r = (int64_t)blockIdx.x * (kThreads / 32) + threadIdx.x / 32; r < n_index; r += warps) {
+    const uint32_t src = __ldg(index + r);
+    const bool ok = src < param_rows;                       // an index outside the table gives a row of zeros
+    const uint4* from = param + (int64_t)(ok ? src : 0) * vec_per_row;
+    uint4* to = out + r * vec_per_row;
+    for (int c = lane; c < vec_per_row; c += 32 * UNROLL) {
+      uint4 v[UNROLL];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        v[u] = make_uint4(0, 0, 0, 0);
+        if (ok && c + 32 * u < vec_per_row) v[u] = ld_stream16(from + c + 32 * u);
+      }
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u)
+        if (c + 32 * u < vec_per_row) st_stream16(to + c + 32 * u, v[u]);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kThreads)
 gather_byte_kernel(const uint8_t* __restrict__ param, const uint32_t* __restrict__ index,
                    uint8_t* __restrict__ out, int64_t total, int64_t row_bytes, uint32_t param_rows) {
@@ -583,6 +610,14 @@ int tl_b200_gather_rows(const void* param, const uint32_t* index, void* out, int
   const int64_t cap = (int64_t)sm_count() * 8;
   if (row_bytes % 16 == 0 && aligned16(param) && aligned16(out) && row_bytes / 16 < (1ll << 31)) {
     constexpr int UNROLL = 4;
+    if (row_bytes / 16 >= 32) {
+      int64_t need = (n_index + kThreads / 32 - 1) / (kThreads / 32);
+      unsigned grid = (unsigned)(need < cap ? need : cap);
+      gather_rows_kernel<UNROLL><<<grid, kThreads, 0, s>>>((const uint4*)param, index, (uint4*)out, n_index,
+                                                          (int)(row_bytes / 16), (uint32_t)param_rows);
+      TL_LAUNCH_CHECK("gather_rows_kernel");
+      return TL_B200_OK;
+    }
     int64_t total = n_index * (row_bytes / 16);
     int64_t need = (total + kThreads * UNROLL - 1) / (kThreads * UNROLL);
     unsigned grid = (unsigned)(need < cap ? need : cap);
