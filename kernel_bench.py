@@ -342,8 +342,12 @@ def tile_program(dev, rank, world, peaks, rows=8192, cols=4096):
     by_op = interpreter.build(program)
     small = rows // bm <= 64
     ms_ops = _time(lambda: by_op(x, y), 1, reps=1, warmup=1) if small else None
-    e = _entry("tile_vm_kernel", f"13-op row-local program on bf16 [{rows}, {cols}], {fused.instructions} instructions", 2.0 * x.numel() * 2,
+    generated = bool(getattr(fused, "generated", False))
+    e = _entry("tile_program (generated kernel)" if generated else "tile_vm_kernel",
+               f"13-op row-local program on bf16 [{rows}, {cols}], {fused.instructions} instructions", 2.0 * x.numel() * 2,
                1e9, "GB/s", ms, ms, peaks["hbm_gbs"], peaks["note"], "none", 1)
+    if generated:              # the interpreter kernel on the same instruction list
+        e["ms_interpreter_kernel"] = _time(lambda: fused.interpreted(x, y), 1, reps=10)
     e["ms_fused_rmsnorm_same_tensor"] = ms_norm
     e["ratio_to_fused_rmsnorm"] = ms / ms_norm
     if ms_ops is not None:

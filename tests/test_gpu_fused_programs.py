@@ -20,13 +20,23 @@ def gen(seed):
 
 
 def run_fused(func, tensors, dev):
+    """The program as ONE launch: by the kernel generated for it and by the interpreter kernel, which must agree bit
+    for bit (the same instruction list, the same arithmetic)."""
     run = fuser.build(func)
     assert run is not None, fuser.build.last_reason
+    assert run.generated, fuser.build.last_reason             # NVRTC is part of the CUDA toolkit of this image
     d = [t.to(dev) for t in tensors]
     before = ops.launch_count()
     assert run(*d) == 0
     torch.cuda.synchronize()
     assert ops.launch_count() - before == 1                   # the whole program is one launch
+    di = [t.to(dev) for t in tensors]
+    before = ops.launch_count()
+    assert run.interpreted(*di) == 0
+    torch.cuda.synchronize()
+    assert ops.launch_count() - before == 1
+    for a, b in zip(d, di):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
     return [t.cpu() for t in d]
 
 

@@ -46,8 +46,9 @@ __device__ __forceinline__ float vm_binary(float a, float b, int sub) {
 }
 __device__ __forceinline__ float vm_unary(float a, int sub) {
   switch (sub) {
-    case 0: return __fdividef(1.0f, 1.0f + expf(-a));
-    case 1: return expf(a);
+    // ex2-based exponential: error 2 + |1.16 a| ulp, inside the 1e-5 of the fp32 path up to the overflow of exp
+    case 0: return __fdividef(1.0f, 1.0f + __expf(-a));
+    case 1: return __expf(a);
     default: return rsqrtf(a);
   }
 }

@@ -16,6 +16,7 @@ A program with an op that is not row-local (gemm, gather, top-k) is left to the 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Callable, Dict, List, Optional
 
 import torch
@@ -445,6 +446,19 @@ def build(func: PrimFunc) -> Optional[Callable[..., int]]:
     run.instructions = n
     run.rows_per_block = c.bm
     run.max_width = c.max_width
+    run.generated = False
+    # The same instruction list as a kernel generated for this program (engine/codegen.py); the interpreter above stays
+    # the path when NVRTC cannot be used, or when TILELANG_B200_TILE_PROGRAM=interpreter asks for it.
+    if os.environ.get("TILELANG_B200_TILE_PROGRAM", "generated") != "interpreter":
+        from . import codegen
+        try:
+            gen = codegen.build(c.ins, c.mem_instrs, n_params, grid, c.bm, c.max_width)
+        except codegen.Unavailable as why:
+            build.last_reason = f"generated kernel unavailable ({why}); interpreted"
+        else:
+            gen.instructions, gen.rows_per_block, gen.max_width, gen.generated = n, c.bm, c.max_width, True
+            gen.interpreted = run
+            return gen
     return run
 
 

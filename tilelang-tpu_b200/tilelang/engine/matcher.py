@@ -683,9 +683,11 @@ def bind(func: PrimFunc) -> BoundKernel:
     from . import fuser, interpreter
     fused = fuser.build(func)
     if fused is not None:
-        return BoundKernel("generic", "tl_b200_tile_program (one launch)", fused,
+        entry = ("kernel generated for the program (NVRTC, one launch)" if getattr(fused, "generated", False)
+                 else "tl_b200_tile_program (one launch)")
+        return BoundKernel("generic", entry, fused,
                            dict(ops=len(func.ops), instructions=fused.instructions, grid=[int(const_value(g)) for g in func.grid],
-                                fused=True), full_outputs=False)
+                                fused=True, generated=bool(getattr(fused, "generated", False))), full_outputs=False)
     try:
         run = interpreter.build(func)
     except interpreter.InterpreterError as why:

@@ -59,8 +59,12 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
+generated_launches = 0          # launches of kernels generated for a program (engine/codegen.py), counted here
+
+
 def launch_count() -> int:
-    return int(N.load().tl_b200_launch_count())
+    """Kernels this process has launched from the library and from generated programs."""
+    return int(N.load().tl_b200_launch_count()) + generated_launches
 
 
 def rmsnorm(x: torch.Tensor, y: torch.Tensor, weight: torch.Tensor | None = None, eps: float = 1e-12) -> int:
