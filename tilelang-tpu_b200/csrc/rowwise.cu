@@ -638,22 +638,34 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(kThreads)
 copy2d_kernel(const TI* __restrict__ src, TO* __restrict__ dst, int64_t rows, int64_t cols, int64_t src_ld,
               int64_t dst_ld) {
-  const int64_t stride = (int64_t)gridDim.x * kThreads, n = rows * cols;
-  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
-    const int64_t r = i / cols, c = i - r * cols;
-    if constexpr (std::is_same<TI, TO>::value) dst[r * dst_ld + c] = src[r * src_ld + c];
-    else dst[r * dst_ld + c] = from_f32<TO>(to_f32(src[r * src_ld + c]));
+  // grid.y walks the rows, grid.x the columns: no division per element
+  for (int64_t r = blockIdx.y; r < rows; r += gridDim.y) {
+    const TI* sr = src + r * src_ld;
+    TO* dr = dst + r * dst_ld;
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < cols; c += (int64_t)gridDim.x * kThreads) {
+      if constexpr (std::is_same<TI, TO>::value) dr[c] = sr[c];
+      else dr[c] = from_f32<TO>(to_f32(sr[c]));
+    }
   }
+}
+
+// Launch shape of the 2-D kernels: up to 64 CTAs across a row, as many row walkers as fill the machine.
+static dim3 grid2d(int64_t rows, int64_t cols) {
+  int64_t gx = (cols + kThreads - 1) / kThreads;
+  if (gx > 64) gx = 64;
+  int64_t gy = ((int64_t)sm_count() * 8 + gx - 1) / gx;
+  if (gy > rows) gy = rows;
+  if (gy > 65535) gy = 65535;
+  if (gy < 1) gy = 1;
+  return dim3((unsigned)gx, (unsigned)gy);
 }
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 fill2d_kernel(T* __restrict__ dst, int64_t rows, int64_t cols, int64_t ld, T value) {
-  const int64_t stride = (int64_t)gridDim.x * kThreads, n = rows * cols;
-  for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += stride) {
-    const int64_t r = i / cols, c = i - r * cols;
-    dst[r * ld + c] = value;
-  }
+  for (int64_t r = blockIdx.y; r < rows; r += gridDim.y)
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < cols; c += (int64_t)gridDim.x * kThreads)
+      dst[r * ld + c] = value;
 }
 
 // out[:, 2i] = e1[:, 2i] + e2[:, 2i+1];  out[:, 2i+1] = o1[:, 2i+1] + o2[:, 2i]   (contiguous tiles)
@@ -681,7 +693,7 @@ static int rope_add_launch(void* out, const void* e1, const void* e2, const void
 template <typename TI>
 static int copy2d_out(const void* src, void* dst, int64_t rows, int64_t cols, int64_t sld, int64_t dld, int out_dtype,
                       cudaStream_t s) {
-  const unsigned grid = elementwise_grid(rows * cols, kThreads * 4);
+  const dim3 grid = grid2d(rows, cols);
   switch (out_dtype) {
     case TL_F32: copy2d_kernel<TI, float><<<grid, kThreads, 0, s>>>((const TI*)src, (float*)dst, rows, cols, sld, dld); break;
     case TL_F16: copy2d_kernel<TI, __half><<<grid, kThreads, 0, s>>>((const TI*)src, (__half*)dst, rows, cols, sld, dld); break;
@@ -857,7 +869,7 @@ int tl_b200_copy2d(const void* src, void* dst, int64_t rows, int64_t cols, int64
   TL_REQUIRE(src_ld >= cols && dst_ld >= cols, "copy2d: a leading dimension is smaller than the row length");
   cudaStream_t s = (cudaStream_t)stream;
   if ((src_dtype == TL_I32 || src_dtype == TL_U32) && (dst_dtype == TL_I32 || dst_dtype == TL_U32)) {   // index tiles: bits
-    copy2d_kernel<uint32_t, uint32_t><<<elementwise_grid(rows * cols, kThreads * 4), kThreads, 0, s>>>(
+    copy2d_kernel<uint32_t, uint32_t><<<grid2d(rows, cols), kThreads, 0, s>>>(
         (const uint32_t*)src, (uint32_t*)dst, rows, cols, src_ld, dst_ld);
     TL_LAUNCH_CHECK("copy2d_kernel");
     return TL_B200_OK;
@@ -871,7 +883,7 @@ int tl_b200_fill(void* dst, int64_t rows, int64_t cols, int64_t ld, float value,
   TL_REQUIRE(dst, "fill: null tensor pointer");
   TL_REQUIRE(ld >= cols, "fill: the leading dimension is smaller than the row length");
   cudaStream_t s = (cudaStream_t)stream;
-  const unsigned grid = elementwise_grid(rows * cols, kThreads * 4);
+  const dim3 grid = grid2d(rows, cols);
   switch (dtype) {
     case TL_F32: fill2d_kernel<float><<<grid, kThreads, 0, s>>>((float*)dst, rows, cols, ld, value); break;
     case TL_F16: fill2d_kernel<__half><<<grid, kThreads, 0, s>>>((__half*)dst, rows, cols, ld, __float2half_rn(value)); break;
