@@ -64,6 +64,7 @@ int mla_persistent_launch(const void* q, const void* kv_cache, const float* kv_s
 // [tokens, h_kv, 576] or split; paged (block_table, seqlens) or dense (both nullptr, dense_len tokens each).
 int64_t mla_f16_workspace_bytes(int64_t units);
 bool mla_f16_shape_ok(int64_t s_q, int64_t h_q, int64_t h_kv, int64_t d, int64_t dv);
+int mla_order_launch(const int* seqlens, int* order, int batch, cudaStream_t s);
 int mla_f16_launch(const void* q, const void* q_pe, const void* kv, const void* k_pe, const int32_t* block_table,
                    const int32_t* seqlens, void* out, int64_t batch, int64_t s_q, int64_t h_q, int64_t h_kv,
                    int64_t total_tokens, int64_t page_size, int64_t max_pages, int64_t num_pages, int64_t dense_len,

@@ -56,6 +56,13 @@ __global__ void mla_order_kernel(const int* __restrict__ seqlens, int* __restric
   }
 }
 
+// order[rank] = sequence, longest first (ties: lower index first); every entry of order[0, batch) is written
+int mla_order_launch(const int* seqlens, int* order, int batch, cudaStream_t s) {
+  mla_order_kernel<<<(unsigned)((batch + 255) / 256), 256, 0, s>>>(seqlens, order, batch);
+  TL_LAUNCH_CHECK("mla_order_kernel");
+  return TL_B200_OK;
+}
+
 template <typename TQ>
 __global__ void __launch_bounds__(kMlaThreads, 1)
 mla_decode_fp8_kernel(const __grid_constant__ CUtensorMap tm_kv, const MlaParams p) {

@@ -10,7 +10,7 @@
 // One CTA pair per (sequence, kv head); each CTA owns 256 of the 512 output columns (the fp32 O accumulator of
 // 128 rows x 512 columns alone would fill tensor memory) and both compute S.  The M = 128 rows of the MMAs are
 // the (query token, head of the group) pairs of the kv head.  A key tile is 64 tokens: nine 128-byte column
-// slabs (72 KB) per stage, two stages.  The same shared-memory image is the K-major operand of S = Q K^T and the
+// slabs (72 KB) per stage, two stages (the MMA thread issues S and P V in the order they become ready, see there).  The same shared-memory image is the K-major operand of S = Q K^T and the
 // MN-major operand of O += P V.  Q does not fit beside two stages in shared memory (147 KB), so its first 256
 // columns live in tensor memory (128 columns, the A operand comes from there) and the other 320 in shared
 // memory (80 KB).  Tensor memory: S/P buffers [0,64) and [64,128), Q [128,256), O [256,512).
@@ -20,6 +20,8 @@
 
 namespace tl {
 using namespace sm100;
+
+int mla_order_launch(const int* seqlens, int* order, int batch, cudaStream_t s);     // mla_decode.cu
 
 constexpr int kFD = 576, kFDV = 512, kFRows = 128, kFBN = 64;
 constexpr int kFSlabs = 9;                        // 64-column slabs of a 576-column row
@@ -48,6 +50,7 @@ struct MlaF16Params {
   int splits;                  // CTA pairs per (sequence, kv head); > 1: each writes a normalised fp32 partial + its log2-sum-exp
   float* part_o;               // [units * splits][128][512]
   float* part_lse;             // [units * splits][128]
+  const int* order;            // sequences, longest first (nullptr: batch order)
   int* status;
 };
 
@@ -75,9 +78,12 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
 
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   const int half = blockIdx.x & 1;
-  const int piece = blockIdx.x >> 1;                // (sequence, kv head, split)
-  const int unit = piece / p.splits, split = piece % p.splits;
-  const int b = unit / p.h_kv, kvh = unit % p.h_kv;
+  const int slot = blockIdx.x >> 1;                 // which (sequence, kv head, split) this CTA pair takes
+  // CTAs are dealt the sequences longest first when the launch had scratch for the order: the long ones start early
+  const int rank = slot / p.splits, split = slot % p.splits;
+  const int b = p.order ? __ldg(p.order + rank / p.h_kv) : rank / p.h_kv, kvh = rank % p.h_kv;
+  const int unit = b * p.h_kv + kvh;
+  const int piece = unit * p.splits + split;        // where its partial goes
   const int rows_used = p.s_q * p.group;
   const int seqlen = p.seqlens ? min(max(__ldg(p.seqlens + b), 0), p.len_cap) : p.dense_len;
   // this CTA pair's contiguous share of the sequence's key tiles
@@ -156,17 +162,18 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer: S one tile ahead of P V
+    // ------------------------------------------------------------------ MMA issuer
+    // Two chains share the tensor pipe: S(t) needs the load of tile t, which can only start when P V(t-2) has retired
+    // (two stages), and P V(t) needs the softmax of tile t.  Issued in a fixed order (S(t+1) before P V(t)) every P V
+    // queues behind an S that is still waiting for its load, and a tile costs the load latency plus all its MMAs.
+    // Here the thread issues whichever of the two is ready (P V first), so the chains of even and odd tiles interleave.
     if (elect_one() && n_tiles > 0) {
       const uint32_t idesc_s = make_idesc(p.fmt, p.fmt, false, false, kFRows, kFBN);
       const uint32_t idesc_o = make_idesc(p.fmt, p.fmt, false, true, kFRows, 256);
       const uint64_t q_desc = smem_desc_sw128(sm_q, 16, 1024), k_desc = smem_desc_sw128(sm_kv, 16, 1024);
       const uint64_t v_desc = smem_desc_sw128(sm_kv, kFBN * 128, 1024);
-      bool ok = true;
-      auto issue_s = [&](int j) {
+      auto issue_s = [&](int j) {               // the stage of tile j has landed
         const int st = j & 1;
-        if (!(ok = mbar_wait(bar_kvfull + 8 * st, (j >> 1) & 1, abort_flag))) return;
-        tc_fence_after_sync();
         const uint64_t kd = desc_at(k_desc, st * kFStageBytes);
         const uint32_t d = tmem_base + kFColS + (j & 1) * kFBN;
         // columns 0..255: Q from tensor memory (8 columns of packed pairs per 16-element step)
@@ -181,17 +188,7 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
                      desc_at(kd, (kk / 4) * (kFBN * 128) + (kk % 4) * 32), idesc_s, 1u);
         mma_commit(bar_sfull + 8 * (j & 1));
       };
-      ok = mbar_wait(bar_qfull, 0, abort_flag) && mbar_wait(bar_qtmem, 0, abort_flag);
-      if (ok) issue_s(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        // S(j+1) goes first: its stage was loaded while S(j) ran, and its S buffer was freed by P V(j-1)
-        if (j + 1 < n_tiles) {
-          if (j >= 1 && !(ok = mbar_wait(bar_pvdone + 8 * ((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag))) break;
-          issue_s(j + 1);
-          if (!ok) break;
-        }
-        if (!(ok = mbar_wait(bar_pfull + 8 * (j & 1), (j >> 1) & 1, abort_flag))) break;
-        tc_fence_after_sync();
+      auto issue_pv = [&](int j) {              // P(j) is in tensor memory
         // V: this CTA's 256 columns = slabs [4 half, 4 half + 4) of the stage, MN-major (slabs 8 KB apart)
         const uint64_t vd = desc_at(v_desc, (j & 1) * kFStageBytes + (4 * half) * (kFBN * 128));
         const uint32_t pa = tmem_base + kFColS + (j & 1) * kFBN;
@@ -200,6 +197,25 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           mma_f16_ts(tmem_base + kFColO, pa + kk * 8, desc_at(vd, kk * 2048), idesc_o, (j | kk) ? 1u : 0u);
         mma_commit(bar_pvdone + 8 * (j & 1));
         mma_commit(bar_kvempty + 8 * (j & 1));
+      };
+      bool ok = mbar_wait(bar_qfull, 0, abort_flag) && mbar_wait(bar_qtmem, 0, abort_flag);
+      int next_s = 0, next_pv = 0;              // S(t) goes into the buffer and stage of t - 2: at most two ahead of P V
+      uint32_t spins = 0;
+      unsigned long long t_idle = 0;
+      while (ok && next_pv < n_tiles) {
+        if (next_pv < next_s && mbar_try_wait(bar_pfull + 8 * (next_pv & 1), (next_pv >> 1) & 1)) {
+          tc_fence_after_sync();
+          issue_pv(next_pv++);
+          spins = 0;
+        } else if (next_s < n_tiles && next_s < next_pv + 2 && mbar_try_wait(bar_kvfull + 8 * (next_s & 1), (next_s >> 1) & 1)) {
+          tc_fence_after_sync();
+          issue_s(next_s++);
+          spins = 0;
+        } else if ((++spins & 63u) == 0) {      // nothing ready: a bounded wait, as everywhere
+          if (*abort_flag) ok = false;
+          else if (spins == 64u) t_idle = global_timer_ns();
+          else if (global_timer_ns() - t_idle > kWaitBudgetNs) { *abort_flag = kStatusWaitTimeout; ok = false; }
+        }
       }
     }
   } else if (warp >= 4) {
@@ -395,7 +411,7 @@ mla_f16_merge_kernel(const float* __restrict__ part_o, const float* __restrict__
 int mla_f16_splits(int64_t units, int64_t workspace_bytes) {
   int splits = (int)((3 * sm_count() + 2 * units - 1) / (2 * units));
   if (splits > 8) splits = 8;
-  while (splits > 1 && units * splits * kFRows * (kFDV + 1) * 4 + 256 > workspace_bytes) --splits;
+  while (splits > 1 && units * splits * kFRows * (kFDV + 1) * 4 + units * 4 + 768 > workspace_bytes) --splits;
   return splits < 1 ? 1 : splits;
 }
 
@@ -405,7 +421,7 @@ int64_t mla_f16_workspace_bytes(int64_t units) {
   int64_t splits = (3 * sm_count() + 2 * units - 1) / (2 * units);
   if (splits > 8) splits = 8;
   if (splits <= 1) return 0;
-  return units * splits * kFRows * (kFDV + 1) * 4 + 512;
+  return units * splits * kFRows * (kFDV + 1) * 4 + units * 4 + 1024;      // partials, their log-sum-exp, the sequence order
 }
 
 bool mla_f16_shape_ok(int64_t s_q, int64_t h_q, int64_t h_kv, int64_t d, int64_t dv) {
@@ -465,11 +481,17 @@ int mla_f16_launch(const void* q, const void* q_pe, const void* kv, const void* 
   // second kernel merges the normalised partials by their log-sum-exp.
   const int64_t units = batch * h_kv;
   p.splits = workspace ? mla_f16_splits(units, workspace_bytes) : 1;
-  p.part_o = nullptr; p.part_lse = nullptr;
+  p.part_o = nullptr; p.part_lse = nullptr; p.order = nullptr;
   if (p.splits > 1) {
     char* ws = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(workspace) + 255u) & ~(uintptr_t)255u);
     p.part_lse = reinterpret_cast<float*>(ws);
     p.part_o = reinterpret_cast<float*>(ws + ((units * p.splits * kFRows * 4 + 255) / 256) * 256);
+    if (seqlens) {             // sequences of different lengths: the longest first
+      int* order = reinterpret_cast<int*>(reinterpret_cast<char*>(p.part_o) + units * p.splits * kFRows * kFDV * 4);
+      rc = mla_order_launch(seqlens, order, (int)batch, stream);
+      if (rc) return rc;
+      p.order = order;
+    }
   }
   const unsigned grid = (unsigned)(2 * units * p.splits);
   if (dtype == TL_BF16) {
