@@ -296,7 +296,12 @@ def compile_cubin(source: str) -> bytes:
     key = hashlib.sha256((f"nvrtc {major}.{minor}\n" + source).encode()).hexdigest()[:32]
     path = cache_dir() / f"gen_{key}.cubin"
     if is_cache_enabled() and path.exists():
-        return path.read_bytes()
+        try:
+            cached = path.read_bytes()
+        except OSError:
+            cached = b""
+        if cached[:4] == b"\x7fELF":                          # anything else (a torn write) is compiled again
+            return cached
     err, prog = nvrtc.nvrtcCreateProgram(source.encode(), b"tile_program.cu", 0, [], [])
     if int(err) != 0:
         raise Unavailable(f"nvrtcCreateProgram failed: {err}")
