@@ -10,7 +10,8 @@
 // One CTA pair per (sequence, kv head); each CTA owns 256 of the 512 output columns (the fp32 O accumulator of
 // 128 rows x 512 columns alone would fill tensor memory) and both compute S.  The M = 128 rows of the MMAs are
 // the (query token, head of the group) pairs of the kv head.  A key tile is 64 tokens: nine 128-byte column
-// slabs (72 KB) per stage, two stages (the MMA thread issues S and P V in the order they become ready, see there).  The same shared-memory image is the K-major operand of S = Q K^T and the
+// slabs (72 KB) per stage, two stages (loaded in two parts, and the MMA thread issues S and P V in the order they
+// become ready: see there).  The same shared-memory image is the K-major operand of S = Q K^T and the
 // MN-major operand of O += P V.  Q does not fit beside two stages in shared memory (147 KB), so its first 256
 // columns live in tensor memory (128 columns, the A operand comes from there) and the other 320 in shared
 // memory (80 KB).  Tensor memory: S/P buffers [0,64) and [64,128), Q [128,256), O [256,512).
@@ -96,7 +97,7 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     for (int i = 0; i < 2; ++i) {
-      mbar_init(bar_kvfull + 8 * i, 1);
+      mbar_init(bar_kvfull + 8 * i, 2);         // a stage arrives in two parts
       mbar_init(bar_kvempty + 8 * i, 1);
       mbar_init(bar_sfull + 8 * i, 1);
       mbar_init(bar_pfull + 8 * i, 4);
@@ -137,9 +138,11 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           else tma_load_2d(dst, &tm_q, bar_qfull, 256 + 64 * s, qrow);
         }
       }
+      // A stage is loaded in two parts.  The five slabs that P V of this CTA does not read (the other CTA's half of the
+      // V columns and the rope slab) are free as soon as S of the tile before last has retired, the four V slabs only
+      // when its P V has: the first part's transfer runs under that tile's softmax and P V.
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1;
-        if (!(ok = mbar_wait(bar_kvempty + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag))) break;
         const int tok = (t0 + j) * kFBN;
         int row;
         if (table) {
@@ -150,15 +153,22 @@ mla_decode_f16_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_con
           row = b * p.dense_len + tok;
         }
         const uint32_t full = bar_kvfull + 8 * st;
-        mbar_expect_tx(full, kFStageBytes);
         // the cache row of (token, kv head) starts at column kvh * 576 of the flattened [tokens, h_kv * 576] view
         const int col0 = kvh * (p.split ? kFDV : kFD);
+        auto load_slab = [&](int sl) {
+          const uint32_t dst = stage_addr(st) + sl * (kFBN * 128);
+          if (p.split && sl == 8) tma_load_2d(dst, &tm_kpe, full, kvh * 64, row);
+          else tma_load_2d(dst, &tm_kv, full, col0 + 64 * sl, row);
+        };
+        if (j >= 2 && !(ok = mbar_wait(bar_sfull + 8 * st, ((j - 2) >> 1) & 1, abort_flag))) break;   // S(j - 2) has retired
+        mbar_expect_tx(full, 5 * kFBN * 128);
 #pragma unroll
-        for (int s = 0; s < kFSlabs; ++s) {
-          const uint32_t dst = stage_addr(st) + s * (kFBN * 128);
-          if (p.split && s == 8) tma_load_2d(dst, &tm_kpe, full, kvh * 64, row);
-          else tma_load_2d(dst, &tm_kv, full, col0 + 64 * s, row);
-        }
+        for (int sl = 0; sl < kFSlabs; ++sl)
+          if (sl < 4 * half || sl >= 4 * half + 4) load_slab(sl);
+        if (!(ok = mbar_wait(bar_kvempty + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag))) break;           // P V(j - 2) has retired
+        mbar_expect_tx(full, 4 * kFBN * 128);
+#pragma unroll
+        for (int sl = 0; sl < 4; ++sl) load_slab(4 * half + sl);
       }
     }
   } else if (warp == 1) {
